@@ -1,0 +1,140 @@
+"""GPU parity tests: the CUDA engine, called through the C ABI, against the
+reference's known answers, the golden fixtures made by the unmodified
+reference CPU path, and the CPU restatement on the same seeded inputs.
+Integers (i, j, S) must match bit for bit after canonical sorting; d and D
+within 1e-12 relative (fp64)."""
+
+import hashlib
+
+import numpy as np
+import pytest
+
+import known_answers as KA
+from gpu_utils import gpu_compute
+from oracle import oracle as O
+from vesin_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+RTOL_FP64 = 1e-12
+
+
+def _gpu(points, box, periodic, cutoff, full, quantities):
+    return gpu_compute(points, box, periodic, cutoff, full, quantities)
+
+
+@pytest.mark.parametrize("name", sorted(KA.EXACT_CASES))
+def test_known_answers(name):
+    KA.check_known_answer(KA.EXACT_CASES[name], _gpu)
+
+
+def test_slanted_box():
+    KA.check_known_answer(KA.SLANTED, _gpu)
+
+
+def test_golden_fixtures(golden):
+    """Every fixture produced by the reference CPU library."""
+    for name in [str(n) for n in golden["names"]]:
+        _, cutoff, full = name.split("|")
+        points, box, periodic = golden[name + "/points"], golden[name + "/box"], golden[name + "/periodic"]
+        res = O.canonical(_gpu(points, box, periodic, float(cutoff), bool(int(full)), "ijSdD"))
+        assert len(res["i"]) == int(golden[name + "/n_pairs"]), name
+        table = np.concatenate([res["i"][:, None], res["j"][:, None], res["S"].astype(np.int64)], axis=1)
+        sha = hashlib.sha256(np.ascontiguousarray(table).tobytes()).hexdigest()
+        assert sha == str(golden[name + "/sha256"]), name
+        scale = max(float(golden[name + "/sum_d"]), 1.0)
+        assert abs(res["d"].sum() - float(golden[name + "/sum_d"])) <= 1e-12 * scale, name
+        if name + "/d" in golden.files and len(res["i"]):
+            assert np.max(np.abs(res["d"] - golden[name + "/d"])) <= RTOL_FP64 * float(cutoff), name
+            assert np.max(np.abs(res["D"] - golden[name + "/D"])) <= RTOL_FP64 * float(cutoff), name
+
+
+@pytest.mark.parametrize("full", [True, False])
+@pytest.mark.parametrize(
+    "system,cutoff",
+    [("diamond5", 5.0), ("triclinic64", 9.0), ("diamond12", 5.0), ("diamond3_big_cutoff", 12.0)],
+)
+def test_against_restatement(system, cutoff, full):
+    points, box, periodic = {
+        "diamond5": lambda: W.diamond(5),
+        "triclinic64": lambda: W.small_triclinic(),
+        "diamond12": lambda: W.diamond(12, seed=11),
+        "diamond3_big_cutoff": lambda: W.diamond(3, seed=5),
+    }[system]()
+    got = _gpu(points, box, periodic, cutoff, full, "ijSdD")
+    expected = O.restated_neighbors(points, box, periodic, cutoff, full, "ijSdD")
+    O.assert_same(got, expected, RTOL_FP64, f"{system} full={full}")
+    # the arithmetic is the reference's, operation for operation
+    got, expected = O.canonical(got), O.canonical(expected)
+    assert np.array_equal(got["d"], expected["d"])
+    assert np.array_equal(got["D"], expected["D"])
+
+
+@pytest.mark.parametrize("bits", range(8))
+def test_mixed_periodicity(bits):
+    periodic = [bool((bits >> 2) & 1), bool((bits >> 1) & 1), bool(bits & 1)]
+    points, box, periodic = W.skewed_random(periodic, seed=40 + bits, n=300)
+    for cutoff in (0.2, 0.35, 0.8):
+        got = _gpu(points, box, periodic, cutoff, True, "ijSdD")
+        expected = O.restated_neighbors(points, box, periodic, cutoff, True, "ijSdD")
+        O.assert_same(got, expected, RTOL_FP64, f"periodic={periodic} cutoff={cutoff}")
+
+
+def test_quantities_subsets_and_reuse():
+    """Re-use of one list across option changes (vesin/tests/memory.cpp)."""
+    import vesin_b200
+
+    points, box, periodic = KA.FCC["points"], KA.FCC["box"], KA.FCC["periodic"]
+    for (cutoff, full), length in KA.REUSE_LENGTHS:
+        res = _gpu(points, box, periodic, cutoff, full, "ij")
+        assert len(res["i"]) == length
+    calculator = vesin_b200.NeighborList(cutoff=3.4, full_list=False)
+    res = gpu_compute(points, box, periodic, 3.4, False, "ijd", calculator=calculator)
+    assert len(res["i"]) == 9
+    lst = calculator._neighbors
+    assert lst.pairs and lst.distances and not lst.shifts and not lst.vectors
+    calculator.cutoff = 6.0
+    calculator.full_list = True
+    res = gpu_compute(points, box, periodic, 6.0, True, "ijd", calculator=calculator)
+    assert len(res["i"]) == 134
+    assert lst.pairs and lst.distances and not lst.shifts and not lst.vectors
+    calculator.cutoff = 4.5
+    calculator.full_list = False
+    res = gpu_compute(points, box, periodic, 4.5, False, "ijS", calculator=calculator)
+    assert len(res["i"]) == 27
+    assert lst.pairs and lst.shifts and not lst.distances and not lst.vectors
+
+
+def test_sorted_rows_and_empty():
+    points, box, periodic = W.diamond(4, seed=9)
+    res = _gpu(points, box, periodic, 4.0, True, "ij")
+    assert np.all(np.diff(res["i"]) >= 0), "rows come out ordered by the first index"
+    res = _gpu(points, box, periodic, 0.3, True, "ijSdD")
+    assert len(res["i"]) == 0
+    res = _gpu(np.zeros((0, 3)), box, periodic, 4.0, True, "ijSdD")
+    assert len(res["i"]) == 0
+
+
+def test_errors():
+    import torch
+
+    import vesin_b200
+
+    device = torch.device("cuda", 0)
+    points = torch.zeros((2, 3), dtype=torch.float64, device=device)
+    box = torch.eye(3, dtype=torch.float64, device=device)
+    with pytest.raises(RuntimeError, match="cutoff must be a finite, positive number"):
+        vesin_b200.NeighborList(cutoff=-1.0, full_list=True).compute(points, box, True, "ij")
+    with pytest.raises(RuntimeError, match="cutoff is too small"):
+        vesin_b200.NeighborList(cutoff=1e-7, full_list=True).compute(points, box, True, "ij")
+    with pytest.raises(RuntimeError, match="the box matrix is not invertible"):
+        vesin_b200.NeighborList(cutoff=1.0, full_list=True).compute(points, torch.zeros_like(box), True, "ij")
+    bad = points.clone()
+    bad[1, 2] = float("inf")
+    with pytest.raises(RuntimeError, match="point 1 has non-finite coordinate along axis 2: inf"):
+        vesin_b200.NeighborList(cutoff=1.0, full_list=True).compute(bad, box, True, "ij")
+    with pytest.raises(RuntimeError, match="Invalid cutoff: too large for box dimensions"):
+        vesin_b200.NeighborList(cutoff=0.6, full_list=True, algorithm="brute_force").compute(points, box, True, "ij")
+    # a zero box is fine when nothing is periodic
+    res = vesin_b200.NeighborList(cutoff=1.0, full_list=True).compute(points, torch.zeros_like(box), False, "ij")
+    assert len(res[0]) == 2

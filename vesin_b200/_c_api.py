@@ -1,0 +1,107 @@
+"""ctypes declarations of the C ABI (include/vesin.h, include/vesin_b200.h)
+and the loader of the in-tree shared library. There is no fallback: when the
+library is missing, loading fails with instructions to build it."""
+
+import ctypes
+import os
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.path.join(HERE, "lib", "libvesin.so")
+
+VesinUnknownDevice = 0
+VesinCPU = 1
+VesinCUDA = 2
+
+VesinAutoAlgorithm = 0
+VesinBruteForce = 1
+VesinCellList = 2
+
+N_STAGES = 7
+STAGE_NAMES = ("bounds", "bin", "scan_cells", "scatter", "count", "scan_rows", "emit")
+
+
+class VesinDevice(ctypes.Structure):
+    _fields_ = [("type", ctypes.c_int), ("device_id", ctypes.c_int)]
+
+
+class VesinOptions(ctypes.Structure):
+    _fields_ = [
+        ("cutoff", ctypes.c_double),
+        ("full", ctypes.c_bool),
+        ("sorted", ctypes.c_bool),
+        ("algorithm", ctypes.c_int),
+        ("n_threads", ctypes.c_int32),
+        ("return_shifts", ctypes.c_bool),
+        ("return_distances", ctypes.c_bool),
+        ("return_vectors", ctypes.c_bool),
+        ("skin", ctypes.c_double),
+    ]
+
+
+class VesinNeighborList(ctypes.Structure):
+    _fields_ = [
+        ("length", ctypes.c_size_t),
+        ("device", VesinDevice),
+        ("pairs", ctypes.c_void_p),
+        ("shifts", ctypes.c_void_p),
+        ("distances", ctypes.c_void_p),
+        ("vectors", ctypes.c_void_p),
+        ("opaque", ctypes.c_void_p),
+    ]
+
+
+EXPORTED_SYMBOLS = (
+    "vesin_neighbors",
+    "vesin_free",
+    "vesin_list_libraries",
+    "vesin_b200_set_profiling",
+    "vesin_b200_stage_times",
+    "vesin_b200_version",
+)
+
+
+def build_library(verbose=False):
+    """Compile vesin_b200/lib/libvesin.so with nvcc for sm_100a."""
+    subprocess.run(
+        ["make", "-C", os.path.join(HERE, "csrc")] + ([] if verbose else ["-s"]),
+        check=True,
+    )
+
+
+_LIBRARY = None
+
+
+def get_library():
+    global _LIBRARY
+    if _LIBRARY is not None:
+        return _LIBRARY
+    if not os.path.exists(LIBRARY_PATH):
+        raise ImportError(
+            f"{LIBRARY_PATH} does not exist: build it with `make -C vesin_b200/csrc` "
+            "(needs nvcc; there is no CPU fallback)"
+        )
+    lib = ctypes.CDLL(LIBRARY_PATH)
+    lib.vesin_neighbors.restype = ctypes.c_int
+    lib.vesin_neighbors.argtypes = [
+        ctypes.c_void_p,  # points
+        ctypes.c_size_t,  # n_points
+        ctypes.c_void_p,  # box
+        ctypes.c_void_p,  # periodic
+        VesinDevice,
+        VesinOptions,
+        ctypes.POINTER(VesinNeighborList),
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
+    lib.vesin_free.restype = None
+    lib.vesin_free.argtypes = [ctypes.POINTER(VesinNeighborList)]
+    lib.vesin_list_libraries.restype = None
+    lib.vesin_list_libraries.argtypes = [ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_size_t)]
+    lib.vesin_b200_set_profiling.restype = None
+    lib.vesin_b200_set_profiling.argtypes = [ctypes.c_int]
+    lib.vesin_b200_stage_times.restype = ctypes.c_int
+    lib.vesin_b200_stage_times.argtypes = [ctypes.POINTER(VesinNeighborList), ctypes.POINTER(ctypes.c_double)]
+    lib.vesin_b200_version.restype = ctypes.c_char_p
+    lib.vesin_b200_version.argtypes = []
+    _LIBRARY = lib
+    return lib

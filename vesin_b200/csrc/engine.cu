@@ -1,0 +1,513 @@
+// Host orchestration: workspace (grow-only device scratch + output arrays),
+// the launch sequence of one build, and the host decisions between launches.
+#include "engine.hpp"
+
+#include <atomic>
+#include <cerrno>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <stdexcept>
+#include <string>
+
+#include <cuda_runtime.h>
+
+#include "vesin_b200.h"
+
+#include "kernels.cuh"
+#include "plan.hpp"
+
+namespace vb200 {
+
+namespace {
+
+std::atomic<bool> PROFILING{false};
+
+void check(cudaError_t status, const char* what) {
+    if (status == cudaSuccess) {
+        return;
+    }
+    if (status == cudaErrorMemoryAllocation) {
+        cudaGetLastError(); // clear the sticky-less error
+        throw std::bad_alloc();
+    }
+    throw std::runtime_error(std::string("CUDA error in ") + what + ": " + cudaGetErrorString(status));
+}
+
+#define VB200_CUDA(call) ::vb200::check((call), #call)
+
+/// Makes `device` current for the lifetime of the guard.
+struct DeviceGuard {
+    int previous = -1;
+    explicit DeviceGuard(int device) {
+        VB200_CUDA(cudaGetDevice(&previous));
+        if (previous != device) {
+            VB200_CUDA(cudaSetDevice(device));
+        } else {
+            previous = -1;
+        }
+    }
+    ~DeviceGuard() {
+        if (previous >= 0) {
+            cudaSetDevice(previous);
+        }
+    }
+};
+
+/// Grow-only device allocation; contents are scratch and are not preserved.
+struct DeviceBuffer {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+
+    void reserve(size_t wanted) {
+        if (wanted <= bytes) {
+            return;
+        }
+        release();
+        VB200_CUDA(cudaMalloc(&ptr, wanted));
+        bytes = wanted;
+    }
+
+    void release() {
+        if (ptr != nullptr) {
+            cudaFree(ptr);
+        }
+        ptr = nullptr;
+        bytes = 0;
+    }
+
+    template <typename T>
+    T* as() const {
+        return static_cast<T*>(ptr);
+    }
+};
+
+constexpr int N_STAGES = VesinB200StageCount_;
+
+/// Everything a VesinNeighborList owns besides the four output pointers;
+/// lives behind VesinNeighborList.opaque. Replaces CudaNeighborListExtras +
+/// CellListBuffers (vesin/src/cuda_buffers.cpp:95-136,196-257).
+struct Workspace {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    DeviceHeader* d_header = nullptr;
+    DeviceHeader* h_header = nullptr; // pinned
+
+    DeviceBuffer cell_of, rank, shift, cell_count, cell_start;
+    DeviceBuffer sorted_pos, sorted_index, sorted_shift;
+    DeviceBuffer masks, mask_base, cell_words;
+    DeviceBuffer row_count, row_start, row_fill, scan_tmp;
+
+    // output arrays (capacity in pairs); kept allocated when not requested
+    DeviceBuffer out_pairs, out_shifts, out_distances, out_vectors;
+
+    cudaEvent_t events[2 * N_STAGES] = {};
+    bool events_created = false;
+    bool timed = false;
+    double stage_ms[N_STAGES] = {};
+
+    ~Workspace() {
+        for (DeviceBuffer* buffer :
+             {&cell_of, &rank, &shift, &cell_count, &cell_start, &sorted_pos, &sorted_index, &sorted_shift, &masks, &mask_base,
+              &cell_words, &row_count, &row_start, &row_fill, &scan_tmp, &out_pairs, &out_shifts, &out_distances, &out_vectors}) {
+            buffer->release();
+        }
+        if (d_header != nullptr) {
+            cudaFree(d_header);
+        }
+        if (h_header != nullptr) {
+            cudaFreeHost(h_header);
+        }
+        if (events_created) {
+            for (auto& event : events) {
+                cudaEventDestroy(event);
+            }
+        }
+        if (stream != nullptr) {
+            cudaStreamDestroy(stream);
+        }
+    }
+};
+
+Workspace& workspace_of(VesinNeighborList& list) {
+    if (list.opaque == nullptr) {
+        auto* ws = new Workspace();
+        list.opaque = ws;
+        ws->device = list.device.device_id;
+        // A blocking stream: ordered after work the caller queued on the
+        // legacy default stream, like the reference (which runs on it).
+        VB200_CUDA(cudaStreamCreate(&ws->stream));
+        VB200_CUDA(cudaMalloc(reinterpret_cast<void**>(&ws->d_header), sizeof(DeviceHeader)));
+        VB200_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&ws->h_header), sizeof(DeviceHeader), cudaHostAllocDefault));
+        configure_kernels();
+    }
+    return *static_cast<Workspace*>(list.opaque);
+}
+
+double key_to_double(unsigned long long key) {
+    unsigned long long bits = (key >> 63) ? (key & 0x7fffffffffffffffull) : ~key;
+    double value;
+    std::memcpy(&value, &bits, sizeof(value));
+    return value;
+}
+
+struct PointerInfo {
+    bool resolved = false;
+    bool on_device = false;
+    int device = -1;
+};
+
+PointerInfo inspect(const void* ptr) {
+    PointerInfo info;
+    if (ptr == nullptr) {
+        return info;
+    }
+    cudaPointerAttributes attributes;
+    if (cudaPointerGetAttributes(&attributes, ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return info;
+    }
+    info.resolved = true;
+    info.on_device = attributes.type == cudaMemoryTypeDevice;
+    info.device = info.on_device ? attributes.device : -1;
+    return info;
+}
+
+/// Same checks, order and messages as vesin/src/vesin_cuda.cpp:831-854.
+void validate_pointers(const void* points, const void* box, const void* periodic, const VesinNeighborList& list) {
+    struct Named {
+        const void* ptr;
+        const char* name;
+    };
+    PointerInfo infos[3];
+    const Named named[3] = {{points, "points"}, {box, "box"}, {periodic, "periodic"}};
+    for (int k = 0; k < 3; k++) {
+        infos[k] = inspect(named[k].ptr);
+        if (!infos[k].resolved) {
+            throw std::runtime_error(std::string("failed to resolve attributes for pointer: ") + named[k].name);
+        }
+        if (!infos[k].on_device) {
+            throw std::runtime_error(std::string("`") + named[k].name + "` pointer is not allocated on a CUDA device");
+        }
+    }
+    if (infos[0].device != infos[1].device) {
+        throw std::runtime_error("`points` and `box` do not exist on the same device");
+    }
+    if (infos[0].device != infos[2].device) {
+        throw std::runtime_error("`points` and `periodic` do not exist on the same device");
+    }
+    if (infos[0].device != list.device.device_id) {
+        throw std::runtime_error("`points`, `box` and `periodic` device differs from input neighbors device_id");
+    }
+}
+
+/// The reference sizes its output for max(128, ceil(cutoff^3)) pairs per
+/// point (or VESIN_CUDA_MAX_PAIRS_PER_POINT) and fails beyond that
+/// (vesin/src/vesin_cuda.cpp:866-886,901-919). This engine sizes the output
+/// exactly, but keeps the same limit and message as a check on the total.
+size_t max_pairs_per_point(double cutoff) {
+    size_t result = std::max<size_t>(128, static_cast<size_t>(std::ceil(std::pow(cutoff, 3))));
+    const char* env = std::getenv("VESIN_CUDA_MAX_PAIRS_PER_POINT");
+    if (env != nullptr) {
+        size_t length = std::strlen(env);
+        char* end = nullptr;
+        errno = 0;
+        long long parsed = std::strtoll(env, &end, 10);
+        if (errno != 0 || end != env + length || parsed <= 0) {
+            throw std::runtime_error("Invalid value for VESIN_CUDA_MAX_PAIRS_PER_POINT: '" + std::string(env) + "'");
+        }
+        result = static_cast<size_t>(parsed);
+    }
+    return result;
+}
+
+struct StageTimer {
+    Workspace& ws;
+    bool enabled;
+    StageTimer(Workspace& workspace, bool on): ws(workspace), enabled(on) {
+        if (enabled && !ws.events_created) {
+            for (auto& event : ws.events) {
+                VB200_CUDA(cudaEventCreate(&event));
+            }
+            ws.events_created = true;
+        }
+        for (auto& ms : ws.stage_ms) {
+            ms = 0.0;
+        }
+        ws.timed = false;
+    }
+    void begin(int stage) {
+        if (enabled) {
+            VB200_CUDA(cudaEventRecord(ws.events[2 * stage], ws.stream));
+        }
+    }
+    void end(int stage) {
+        if (enabled) {
+            VB200_CUDA(cudaEventRecord(ws.events[2 * stage + 1], ws.stream));
+        }
+    }
+    /// call after a stream synchronisation that covers `stage`
+    void collect(int stage) {
+        if (enabled) {
+            float ms = 0.0f;
+            VB200_CUDA(cudaEventElapsedTime(&ms, ws.events[2 * stage], ws.events[2 * stage + 1]));
+            ws.stage_ms[stage] += ms;
+        }
+    }
+};
+
+void read_header(Workspace& ws) {
+    VB200_CUDA(cudaMemcpyAsync(ws.h_header, ws.d_header, sizeof(DeviceHeader), cudaMemcpyDeviceToHost, ws.stream));
+    VB200_CUDA(cudaStreamSynchronize(ws.stream));
+}
+
+void set_outputs(VesinNeighborList& list, Workspace& ws, const VesinOptions& options, size_t capacity) {
+    ws.out_pairs.reserve(capacity * 2 * sizeof(size_t));
+    list.pairs = reinterpret_cast<size_t(*)[2]>(ws.out_pairs.ptr);
+    list.shifts = nullptr;
+    list.distances = nullptr;
+    list.vectors = nullptr;
+    if (options.return_shifts) {
+        ws.out_shifts.reserve(capacity * 3 * sizeof(int32_t));
+        list.shifts = reinterpret_cast<int32_t(*)[3]>(ws.out_shifts.ptr);
+    }
+    if (options.return_distances) {
+        ws.out_distances.reserve(capacity * sizeof(double));
+        list.distances = ws.out_distances.as<double>();
+    }
+    if (options.return_vectors) {
+        ws.out_vectors.reserve(capacity * 3 * sizeof(double));
+        list.vectors = reinterpret_cast<double(*)[3]>(ws.out_vectors.ptr);
+    }
+}
+
+} // namespace
+
+void set_profiling(bool enabled) {
+    PROFILING.store(enabled);
+}
+
+bool stage_times(const VesinNeighborList& list, double* stage_ms) {
+    if (list.opaque == nullptr || list.device.type != VesinCUDA) {
+        return false;
+    }
+    const auto& ws = *static_cast<const Workspace*>(list.opaque);
+    if (!ws.timed) {
+        return false;
+    }
+    for (int k = 0; k < N_STAGES; k++) {
+        stage_ms[k] = ws.stage_ms[k];
+    }
+    return true;
+}
+
+void neighbors(
+    const double (*points)[3],
+    size_t n_points,
+    const double box[3][3],
+    const bool periodic[3],
+    VesinOptions options,
+    VesinNeighborList& list
+) {
+    int device_count = 0;
+    if (cudaGetDeviceCount(&device_count) != cudaSuccess || device_count == 0) {
+        cudaGetLastError();
+        throw std::runtime_error("no CUDA device is available to this process");
+    }
+    validate_pointers(points, box, periodic, list);
+    if (n_points >= (1ull << 31) - 1) {
+        throw std::runtime_error("this engine indexes points with 31 bits: too many points");
+    }
+
+    DeviceGuard guard(list.device.device_id);
+    Workspace& ws = workspace_of(list);
+    const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
+    StageTimer timer(ws, PROFILING.load());
+    cudaStream_t stream = ws.stream;
+    const auto* flat_points = reinterpret_cast<const double*>(points);
+
+    // ---- box, periodicity, bounds and finite check: one read-back ----
+    timer.begin(VesinB200StageBounds);
+    launch_header_init(ws.d_header, reinterpret_cast<const double*>(box), periodic, stream);
+    launch_bounds(flat_points, n_points, ws.d_header, stream);
+    timer.end(VesinB200StageBounds);
+    VB200_CUDA(cudaGetLastError());
+    read_header(ws);
+    timer.collect(VesinB200StageBounds);
+    const DeviceHeader& header = *ws.h_header;
+
+    if (header.first_bad != NO_BAD_POINT) {
+        // same text as the CPU path (vesin/src/types.hpp:163-169)
+        double bad[3];
+        VB200_CUDA(cudaMemcpy(bad, flat_points + 3 * header.first_bad, sizeof(bad), cudaMemcpyDeviceToHost));
+        for (int axis = 0; axis < 3; axis++) {
+            if (!std::isfinite(bad[axis])) {
+                throw std::runtime_error(
+                    "point " + std::to_string(header.first_bad) + " has non-finite coordinate along axis " +
+                    std::to_string(axis) + ": " + std::to_string(bad[axis])
+                );
+            }
+        }
+    }
+
+    bool host_periodic[3] = {header.periodic[0] != 0, header.periodic[1] != 0, header.periodic[2] != 0};
+    PointBounds bounds{};
+    for (int c = 0; c < 3; c++) {
+        bounds.min[c] = n_points ? key_to_double(header.min_key[c]) : 0.0;
+        bounds.max[c] = n_points ? key_to_double(header.max_key[c]) : 0.0;
+    }
+    const size_t max_cells = size_t(1) << 27;
+    GridPlan plan = make_plan(header.box, host_periodic, bounds, n_points, options.cutoff, options.full, max_cells);
+
+    if (options.algorithm == VesinBruteForce && 2.0 * options.cutoff > min_periodic_face_distance(plan)) {
+        // vesin/src/vesin_cuda.cpp:404-409
+        throw std::runtime_error("Invalid cutoff: too large for box dimensions");
+    }
+
+    if (n_points == 0) {
+        set_outputs(list, ws, options, 256);
+        list.length = 0;
+        ws.timed = timer.enabled;
+        return;
+    }
+
+    // ---- scratch ----
+    const size_t n_cells = static_cast<size_t>(plan.n_cells_total);
+    ws.cell_of.reserve(n_points * sizeof(int32_t));
+    ws.rank.reserve(n_points * sizeof(int32_t));
+    ws.shift.reserve(n_points * 3 * sizeof(int32_t));
+    ws.cell_count.reserve(n_cells * sizeof(int32_t));
+    ws.cell_start.reserve((n_cells + 1) * sizeof(int32_t));
+    ws.sorted_pos.reserve(n_points * 3 * sizeof(double));
+    ws.sorted_index.reserve(n_points * sizeof(int32_t));
+    ws.sorted_shift.reserve(n_points * 3 * sizeof(int32_t));
+    ws.mask_base.reserve(n_cells * sizeof(unsigned long long));
+    ws.cell_words.reserve(n_cells * sizeof(uint32_t));
+    ws.row_count.reserve(n_points * sizeof(uint32_t));
+    ws.row_start.reserve((n_points + 1) * sizeof(unsigned long long));
+    ws.row_fill.reserve(n_points * sizeof(uint32_t));
+    ws.scan_tmp.reserve(scan_tmp_bytes(std::max(n_points, n_cells)));
+    {
+        // first guess for the hit-mask storage: uniform density
+        double per_cell = static_cast<double>(n_points) / static_cast<double>(n_cells);
+        double words = per_cell * plan.n_stencil / 32.0 + 1.5;
+        double guess = 1.2 * words * static_cast<double>(n_points) * sizeof(uint32_t);
+        guess = std::min(guess, 2.0e9);
+        if (ws.masks.bytes == 0) {
+            ws.masks.reserve(static_cast<size_t>(guess) + 1024);
+        }
+    }
+    SortedPoints sorted{ws.sorted_pos.as<double>(), ws.sorted_index.as<int32_t>(), ws.sorted_shift.as<int32_t>()};
+
+    // ---- cell list ----
+    timer.begin(VesinB200StageBin);
+    VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
+    launch_bin(flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_count.as<int32_t>(), stream);
+    timer.end(VesinB200StageBin);
+
+    timer.begin(VesinB200StageScanCells);
+    launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
+    timer.end(VesinB200StageScanCells);
+
+    timer.begin(VesinB200StageScatter);
+    launch_scatter(flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), sorted, stream);
+    timer.end(VesinB200StageScatter);
+
+    // ---- pass 1: decide every candidate; pairs per point; totals ----
+    for (int attempt = 0;; attempt++) {
+        timer.begin(VesinB200StageCount);
+        VB200_CUDA(cudaMemsetAsync(ws.row_count.ptr, 0, n_points * sizeof(uint32_t), stream));
+        launch_count(
+            plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.masks.bytes / sizeof(uint32_t),
+            ws.mask_base.as<unsigned long long>(), ws.cell_words.as<uint32_t>(), ws.row_count.as<uint32_t>(), ws.d_header, stream
+        );
+        timer.end(VesinB200StageCount);
+
+        timer.begin(VesinB200StageScanRows);
+        launch_scan_rows(
+            ws.row_count.as<uint32_t>(), ws.row_start.as<unsigned long long>(), n_points, ws.scan_tmp.ptr,
+            &ws.d_header->total_pairs, stream
+        );
+        timer.end(VesinB200StageScanRows);
+        VB200_CUDA(cudaGetLastError());
+        read_header(ws);
+        if (attempt == 0) {
+            timer.collect(VesinB200StageBin);
+            timer.collect(VesinB200StageScanCells);
+            timer.collect(VesinB200StageScatter);
+        }
+        timer.collect(VesinB200StageCount);
+        timer.collect(VesinB200StageScanRows);
+
+        if ((header.status & STATUS_MASK_OVERFLOW) == 0) {
+            break;
+        }
+        if (attempt >= 2) {
+            throw std::runtime_error("internal error: hit-mask storage kept overflowing");
+        }
+        // the cursor holds the exact requirement: grow and decide again
+        size_t wanted = static_cast<size_t>(header.mask_cursor) * sizeof(uint32_t);
+        ws.masks.reserve(wanted + wanted / 16 + 1024);
+        size_t offset = offsetof(DeviceHeader, total_pairs);
+        VB200_CUDA(cudaMemsetAsync(reinterpret_cast<char*>(ws.d_header) + offset, 0, offsetof(DeviceHeader, box) - offset, stream));
+    }
+
+    const size_t total = static_cast<size_t>(header.total_pairs);
+    if (total > n_points * pair_limit_per_point) {
+        throw std::runtime_error(
+            "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_points * pair_limit_per_point) +
+            " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_points) + "). " +
+            "Consider reducing the cutoff distance, or explicitly setting " +
+            "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable."
+        );
+    }
+
+    // ---- exactly sized output, then pass 2 ----
+    size_t capacity = std::max<size_t>(total, 256);
+    if (capacity * 2 * sizeof(size_t) > ws.out_pairs.bytes && ws.out_pairs.bytes != 0) {
+        capacity += capacity / 16; // a list that keeps growing gets some headroom
+    }
+    set_outputs(list, ws, options, capacity);
+
+    if (total > 0) {
+        PairOutput out{
+            reinterpret_cast<unsigned long long*>(list.pairs),
+            reinterpret_cast<int32_t*>(list.shifts),
+            list.distances,
+            reinterpret_cast<double*>(list.vectors),
+        };
+        timer.begin(VesinB200StageEmit);
+        VB200_CUDA(cudaMemsetAsync(ws.row_fill.ptr, 0, n_points * sizeof(uint32_t), stream));
+        launch_emit(
+            plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.mask_base.as<unsigned long long>(),
+            ws.cell_words.as<uint32_t>(), ws.row_start.as<unsigned long long>(), ws.row_fill.as<uint32_t>(), out, stream
+        );
+        timer.end(VesinB200StageEmit);
+        VB200_CUDA(cudaGetLastError());
+        VB200_CUDA(cudaStreamSynchronize(stream));
+        timer.collect(VesinB200StageEmit);
+    }
+    list.length = total;
+    ws.timed = timer.enabled;
+}
+
+void free_neighbors(VesinNeighborList& list) {
+    if (list.opaque != nullptr) {
+        auto* ws = static_cast<Workspace*>(list.opaque);
+        int previous = -1;
+        cudaGetDevice(&previous);
+        cudaSetDevice(ws->device);
+        delete ws;
+        if (previous >= 0) {
+            cudaSetDevice(previous);
+        }
+        list.opaque = nullptr;
+    }
+    list.pairs = nullptr;
+    list.shifts = nullptr;
+    list.distances = nullptr;
+    list.vectors = nullptr;
+}
+
+} // namespace vb200

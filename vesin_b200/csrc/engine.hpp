@@ -1,0 +1,33 @@
+// Host orchestration of one neighbor-list build on a CUDA device.
+#ifndef VESIN_B200_ENGINE_HPP
+#define VESIN_B200_ENGINE_HPP
+
+#include <cstddef>
+
+#include "vesin.h"
+
+namespace vb200 {
+
+/// Compute the list for device-resident inputs. Replaces
+/// vesin::cuda::neighbors (vesin/src/vesin_cuda.cpp:819-923). Throws
+/// std::runtime_error / std::bad_alloc; the C entry point turns those into
+/// error strings.
+void neighbors(
+    const double (*points)[3],
+    size_t n_points,
+    const double box[3][3],
+    const bool periodic[3],
+    VesinOptions options,
+    VesinNeighborList& list
+);
+
+/// Release everything a list holds on its device. Replaces
+/// vesin::cuda::free_neighbors (vesin/src/vesin_cuda.cpp:129-138).
+void free_neighbors(VesinNeighborList& list);
+
+void set_profiling(bool enabled);
+bool stage_times(const VesinNeighborList& list, double* stage_ms);
+
+} // namespace vb200
+
+#endif

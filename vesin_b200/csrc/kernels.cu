@@ -1,0 +1,954 @@
+// Kernels of the neighbor-list build (sm_100a).
+//
+// Pipeline of one build (reference stages replaced are cited per kernel):
+//   header_init -> bounds -> [host: grid plan] -> bin -> scan cells -> scatter
+//   -> count (hit masks + pairs per point) -> scan rows -> [host: totals]
+//   -> emit.
+//
+// The pair set is decided ONCE, in the count pass, with the reference's exact
+// fp64 arithmetic wherever an fp32 screen cannot decide; the emit pass only
+// walks the stored hit bits, so the two passes can not disagree.
+#include "kernels.cuh"
+
+#include <cfloat>
+
+namespace vb200 {
+
+namespace {
+
+constexpr int CTA_THREADS = 256;
+constexpr int CTA_WARPS = CTA_THREADS / 32;
+constexpr unsigned FULL_MASK = 0xffffffffu;
+
+// ---------------------------------------------------------------------------
+// small helpers
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned long long double_to_key(double x) {
+    // order-preserving map double -> uint64
+    unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(x));
+    return (bits >> 63) ? ~bits : (bits | 0x8000000000000000ull);
+}
+
+__device__ __forceinline__ int floor_div(int a, int b) {
+    int q = a / b;
+    int r = a - q * b;
+    return (r < 0) ? q - 1 : q;
+}
+
+__device__ __forceinline__ unsigned lanemask_lt() {
+    unsigned mask;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(mask));
+    return mask;
+}
+
+/// Exclusive scan of one value per thread over the whole CTA (256 threads).
+/// `warp_sums` is CTA_WARPS + 1 ints of shared memory; returns the exclusive
+/// prefix and stores the CTA total in warp_sums[CTA_WARPS].
+__device__ __forceinline__ int block_exclusive_scan(int value, int* warp_sums) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    int inclusive = value;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        int up = __shfl_up_sync(FULL_MASK, inclusive, offset);
+        if (lane >= offset) {
+            inclusive += up;
+        }
+    }
+    if (lane == 31) {
+        warp_sums[warp] = inclusive;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int total = (lane < CTA_WARPS) ? warp_sums[lane] : 0;
+        int scan = total;
+#pragma unroll
+        for (int offset = 1; offset < CTA_WARPS; offset <<= 1) {
+            int up = __shfl_up_sync(FULL_MASK, scan, offset);
+            if (lane >= offset) {
+                scan += up;
+            }
+        }
+        if (lane < CTA_WARPS) {
+            warp_sums[lane] = scan - total; // exclusive prefix of the warp
+        }
+        if (lane == CTA_WARPS - 1) {
+            warp_sums[CTA_WARPS] = scan;
+        }
+    }
+    __syncthreads();
+    return warp_sums[warp] + inclusive - value;
+}
+
+// ---------------------------------------------------------------------------
+// header + bounds
+// Replaces compute_bounding_box (vesin/src/cuda/cell_list.cu:69-133, one block
+// for all points) and the finite check of the CPU path
+// (vesin/src/types.hpp:159-178).
+// ---------------------------------------------------------------------------
+
+__global__ void header_init_kernel(DeviceHeader* header, const double* box, const bool* periodic) {
+    int t = threadIdx.x;
+    if (t < 3) {
+        header->min_key[t] = ~0ull;
+        header->max_key[t] = 0ull;
+        header->periodic[t] = periodic[t] ? 1 : 0;
+    }
+    if (t < 9) {
+        header->box[t] = box[t];
+    }
+    if (t == 0) {
+        header->first_bad = NO_BAD_POINT;
+        header->total_pairs = 0;
+        header->mask_cursor = 0;
+        header->status = 0;
+    }
+}
+
+__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const double* __restrict__ points, size_t n, DeviceHeader* header) {
+    double lo[3] = {DBL_MAX, DBL_MAX, DBL_MAX};
+    double hi[3] = {-DBL_MAX, -DBL_MAX, -DBL_MAX};
+    unsigned long long bad = NO_BAD_POINT;
+
+    size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+            double x = points[3 * i + c];
+            if (isfinite(x)) {
+                lo[c] = fmin(lo[c], x);
+                hi[c] = fmax(hi[c], x);
+            } else if (i < bad) {
+                bad = i;
+            }
+        }
+    }
+
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+            lo[c] = fmin(lo[c], __shfl_xor_sync(FULL_MASK, lo[c], offset));
+            hi[c] = fmax(hi[c], __shfl_xor_sync(FULL_MASK, hi[c], offset));
+        }
+        unsigned long long other = __shfl_xor_sync(FULL_MASK, bad, offset);
+        bad = (other < bad) ? other : bad;
+    }
+
+    __shared__ double s_lo[CTA_WARPS][3];
+    __shared__ double s_hi[CTA_WARPS][3];
+    __shared__ unsigned long long s_bad[CTA_WARPS];
+    int lane = threadIdx.x & 31;
+    int warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        for (int c = 0; c < 3; c++) {
+            s_lo[warp][c] = lo[c];
+            s_hi[warp][c] = hi[c];
+        }
+        s_bad[warp] = bad;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < CTA_WARPS; w++) {
+            for (int c = 0; c < 3; c++) {
+                lo[c] = fmin(lo[c], s_lo[w][c]);
+                hi[c] = fmax(hi[c], s_hi[w][c]);
+            }
+            bad = (s_bad[w] < bad) ? s_bad[w] : bad;
+        }
+        for (int c = 0; c < 3; c++) {
+            if (lo[c] <= hi[c]) {
+                atomicMin(&header->min_key[c], double_to_key(lo[c]));
+                atomicMax(&header->max_key[c], double_to_key(hi[c]));
+            }
+        }
+        if (bad != NO_BAD_POINT) {
+            atomicMin(&header->first_bad, bad);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// bin: wrap + cell + histogram
+// Replaces assign_cell_indices + count_particles_per_cell
+// (vesin/src/cuda/cell_list.cu:279-345) and CellList::add_point
+// (vesin/src/cpu_cell_list.cpp:353-374).
+// ---------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
+    const double* __restrict__ points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
+    int32_t* __restrict__ shift, int32_t* __restrict__ cell_count
+) {
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    bool active = i < n;
+    unsigned active_mask = __ballot_sync(FULL_MASK, active);
+    if (!active) {
+        return;
+    }
+
+    double rx = points[3 * i + 0];
+    double ry = points[3 * i + 1];
+    double rz = points[3 * i + 2];
+
+    int cell[3];
+    int wrap[3];
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+        double t = rx * plan.Hinv[0][k] + ry * plan.Hinv[1][k] + rz * plan.Hinv[2][k];
+        double g = floor((t - plan.t0[k]) * plan.scale[k]);
+        g = fmin(fmax(g, -1.0e9), 1.0e9);
+        int gi = static_cast<int>(g);
+        if (plan.periodic[k]) {
+            int q = floor_div(gi, plan.n_cells[k]);
+            wrap[k] = q;
+            cell[k] = gi - q * plan.n_cells[k];
+        } else {
+            wrap[k] = 0;
+            cell[k] = min(max(gi, 0), plan.n_cells[k] - 1);
+        }
+    }
+    int linear = (cell[2] * plan.n_cells[1] + cell[1]) * plan.n_cells[0] + cell[0];
+
+    // warp-aggregated histogram: one atomic per distinct cell in the warp
+    unsigned peers = __match_any_sync(active_mask, linear);
+    int leader = __ffs(peers) - 1;
+    int lane = threadIdx.x & 31;
+    int base = 0;
+    if (lane == leader) {
+        base = atomicAdd(&cell_count[linear], __popc(peers));
+    }
+    base = __shfl_sync(peers, base, leader);
+
+    cell_of[i] = linear;
+    rank[i] = base + __popc(peers & lanemask_lt());
+    shift[3 * i + 0] = wrap[0];
+    shift[3 * i + 1] = wrap[1];
+    shift[3 * i + 2] = wrap[2];
+}
+
+// ---------------------------------------------------------------------------
+// scans
+// Replaces prefix_sum_cells (vesin/src/cuda/cell_list.cu:347-390, a single
+// block whose 8192-cell limit caps the reference's grid) and the pre-sized
+// output + global append counter (vesin/src/vesin_cuda.cpp:866-886,
+// cell_list.cu:643-668): per-point counts are scanned into private rows.
+// Three launches (tile sums, spine, apply) and no inter-CTA waiting.
+// ---------------------------------------------------------------------------
+
+constexpr int SCAN_ITEMS = 8;
+constexpr int SCAN_TILE = CTA_THREADS * SCAN_ITEMS;
+
+template <typename TIn>
+__global__ void __launch_bounds__(CTA_THREADS) scan_tile_sums_kernel(const TIn* __restrict__ in, size_t n, unsigned long long* __restrict__ tile_sums) {
+    size_t base = static_cast<size_t>(blockIdx.x) * SCAN_TILE;
+    unsigned long long sum = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        size_t idx = base + static_cast<size_t>(k) * CTA_THREADS + threadIdx.x;
+        if (idx < n) {
+            sum += static_cast<unsigned long long>(in[idx]);
+        }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        sum += __shfl_xor_sync(FULL_MASK, sum, offset);
+    }
+    __shared__ unsigned long long s_sum[CTA_WARPS];
+    if ((threadIdx.x & 31) == 0) {
+        s_sum[threadIdx.x >> 5] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long total = 0;
+        for (int w = 0; w < CTA_WARPS; w++) {
+            total += s_sum[w];
+        }
+        tile_sums[blockIdx.x] = total;
+    }
+}
+
+/// One CTA turns the tile sums into exclusive tile offsets, in place.
+__global__ void __launch_bounds__(CTA_THREADS) scan_spine_kernel(unsigned long long* tile_sums, size_t n_tiles, unsigned long long* total_out) {
+    __shared__ unsigned long long s_warp[CTA_WARPS];
+    __shared__ unsigned long long s_carry;
+    if (threadIdx.x == 0) {
+        s_carry = 0;
+    }
+    __syncthreads();
+    int lane = threadIdx.x & 31;
+    int warp = threadIdx.x >> 5;
+    for (size_t start = 0; start < n_tiles; start += CTA_THREADS) {
+        size_t idx = start + threadIdx.x;
+        unsigned long long value = (idx < n_tiles) ? tile_sums[idx] : 0;
+        unsigned long long inclusive = value;
+#pragma unroll
+        for (int offset = 1; offset < 32; offset <<= 1) {
+            unsigned long long up = __shfl_up_sync(FULL_MASK, inclusive, offset);
+            if (lane >= offset) {
+                inclusive += up;
+            }
+        }
+        if (lane == 31) {
+            s_warp[warp] = inclusive;
+        }
+        __syncthreads();
+        unsigned long long warp_prefix = 0;
+        for (int w = 0; w < warp; w++) {
+            warp_prefix += s_warp[w];
+        }
+        unsigned long long carry = s_carry;
+        if (idx < n_tiles) {
+            tile_sums[idx] = carry + warp_prefix + inclusive - value;
+        }
+        __syncthreads();
+        if (threadIdx.x == CTA_THREADS - 1) {
+            s_carry = carry + warp_prefix + inclusive;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && total_out != nullptr) {
+        *total_out = s_carry;
+    }
+}
+
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
+    const TIn* __restrict__ in, TOut* __restrict__ out, size_t n, const unsigned long long* __restrict__ tile_offsets
+) {
+    // each thread owns SCAN_ITEMS consecutive elements
+    size_t base = static_cast<size_t>(blockIdx.x) * SCAN_TILE + static_cast<size_t>(threadIdx.x) * SCAN_ITEMS;
+    unsigned long long values[SCAN_ITEMS];
+    unsigned long long local = 0;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        size_t idx = base + k;
+        values[k] = (idx < n) ? static_cast<unsigned long long>(in[idx]) : 0;
+        local += values[k];
+    }
+    // exclusive scan of `local` over the CTA (64-bit)
+    int lane = threadIdx.x & 31;
+    int warp = threadIdx.x >> 5;
+    unsigned long long inclusive = local;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        unsigned long long up = __shfl_up_sync(FULL_MASK, inclusive, offset);
+        if (lane >= offset) {
+            inclusive += up;
+        }
+    }
+    __shared__ unsigned long long s_warp[CTA_WARPS];
+    if (lane == 31) {
+        s_warp[warp] = inclusive;
+    }
+    __syncthreads();
+    unsigned long long prefix = tile_offsets[blockIdx.x] + inclusive - local;
+    for (int w = 0; w < warp; w++) {
+        prefix += s_warp[w];
+    }
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        size_t idx = base + k;
+        if (idx < n) {
+            out[idx] = static_cast<TOut>(prefix);
+        }
+        prefix += values[k];
+        if (idx + 1 == n) {
+            out[n] = static_cast<TOut>(prefix);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// scatter
+// Replaces scatter_particles (vesin/src/cuda/cell_list.cu:392-421); the slot
+// inside the cell was already handed out by the histogram, so there is no
+// second atomic.
+// ---------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(CTA_THREADS) scatter_kernel(
+    const double* __restrict__ points, size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank,
+    const int32_t* __restrict__ shift, const int32_t* __restrict__ cell_start, SortedPoints sorted
+) {
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) {
+        return;
+    }
+    size_t p = static_cast<size_t>(cell_start[cell_of[i]]) + rank[i];
+    sorted.pos[3 * p + 0] = points[3 * i + 0];
+    sorted.pos[3 * p + 1] = points[3 * i + 1];
+    sorted.pos[3 * p + 2] = points[3 * i + 2];
+    sorted.index[p] = static_cast<int32_t>(i);
+    sorted.shift[3 * p + 0] = shift[3 * i + 0];
+    sorted.shift[3 * p + 1] = shift[3 * i + 1];
+    sorted.shift[3 * p + 2] = shift[3 * i + 2];
+}
+
+// ---------------------------------------------------------------------------
+// stencil traversal shared by the count and emit passes
+// Replaces CellList::foreach_pair (vesin/src/cpu_cell_list.cpp:376-451) and
+// the traversal of find_neighbors_cell_list (vesin/src/cuda/cell_list.cu:509-591).
+//
+// One CTA owns one home cell. The cells of its stencil are "segments": runs
+// of cell-sorted points, each with the image shift q picked up by wrapping
+// the cell index. The concatenation of all segments numbers the candidates of
+// every point of the home cell ("slots"); one bit per slot and per home point
+// is the hit mask. Stencils with more than SEG_MAX cells are walked in groups
+// whose slot numbering starts on a fresh 32-slot word.
+// ---------------------------------------------------------------------------
+
+constexpr int SEG_MAX = 128;
+
+struct SegmentTable {
+    int start[SEG_MAX];     // first cell-sorted point of the segment
+    int slot0[SEG_MAX + 1]; // exclusive prefix of the segment lengths
+    int q[3][SEG_MAX];      // image shift of the segment
+    int self_ok[SEG_MAX];   // may a point pair with its own image in this segment?
+    int scan_tmp[CTA_WARPS + 1];
+};
+
+__device__ __forceinline__ bool half_rule(int s0, int s1, int s2) {
+    // which of S / -S a half list keeps for a point paired with its own
+    // image (vesin/src/cpu_cell_list.cpp:107-132)
+    int sum = s0 + s1 + s2;
+    if (sum < 0) {
+        return false;
+    }
+    if (sum == 0 && (s2 < 0 || (s2 == 0 && s1 < 0))) {
+        return false;
+    }
+    return true;
+}
+
+/// Fill the table for segment group `group` of home cell (c0, c1, c2).
+/// Returns the number of slots of the group. Ends with a __syncthreads().
+__device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_t* __restrict__ cell_start, int c0, int c1, int c2, int home, int group, SegmentTable& table) {
+    int t = threadIdx.x;
+    int length = 0;
+    if (t < SEG_MAX) {
+        int global_t = group * SEG_MAX + t;
+        int start = 0;
+        int q0 = 0, q1 = 0, q2 = 0;
+        int self_ok = 0;
+        if (global_t < plan.n_stencil) {
+            int w0 = 2 * plan.n_search[0] + 1;
+            int w1 = 2 * plan.n_search[1] + 1;
+            int nb[3] = {c0 + (global_t % w0) - plan.n_search[0], c1 + ((global_t / w0) % w1) - plan.n_search[1], c2 + (global_t / (w0 * w1)) - plan.n_search[2]};
+            int q[3] = {0, 0, 0};
+            bool valid = true;
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                if (plan.periodic[k]) {
+                    q[k] = floor_div(nb[k], plan.n_cells[k]);
+                    nb[k] -= q[k] * plan.n_cells[k];
+                } else if (nb[k] < 0 || nb[k] >= plan.n_cells[k]) {
+                    valid = false;
+                }
+            }
+            if (valid) {
+                int linear = (nb[2] * plan.n_cells[1] + nb[1]) * plan.n_cells[0] + nb[0];
+                start = cell_start[linear];
+                length = cell_start[linear + 1] - start;
+                q0 = q[0];
+                q1 = q[1];
+                q2 = q[2];
+                bool nonzero = (q0 | q1 | q2) != 0;
+                self_ok = (linear == home) && nonzero && (plan.full || half_rule(q0, q1, q2));
+            }
+        }
+        table.start[t] = start;
+        table.q[0][t] = q0;
+        table.q[1][t] = q1;
+        table.q[2][t] = q2;
+        table.self_ok[t] = self_ok;
+    }
+    int prefix = block_exclusive_scan(length, table.scan_tmp);
+    if (t < SEG_MAX) {
+        table.slot0[t] = prefix;
+    }
+    int total = table.scan_tmp[CTA_WARPS];
+    if (t == 0) {
+        table.slot0[SEG_MAX] = total;
+    }
+    __syncthreads();
+    return total;
+}
+
+/// Segment that holds `slot`: last t with slot0[t] <= slot.
+__device__ __forceinline__ int find_segment(const SegmentTable& table, int slot) {
+    int lo = 0;
+    int hi = SEG_MAX; // slot0[hi] > slot always holds for slot < total
+#pragma unroll
+    for (int step = 0; step < 7; step++) {
+        int mid = (lo + hi) >> 1;
+        if (table.slot0[mid] <= slot) {
+            lo = mid;
+        } else {
+            hi = mid;
+        }
+    }
+    return lo;
+}
+
+/// The reference's pair vector and squared distance, operation for operation:
+/// v = (r_j - r_i) + ((S0*H0 + S1*H1) + S2*H2), d2 = (vx*vx + vy*vy) + vz*vz
+/// (vesin/src/cpu_cell_list.cpp:135-136, types.hpp:232-243,
+/// math.hpp:14-16,111-117). Intrinsics keep the compiler from fusing
+/// multiplies and adds, which x86-64 builds of the reference never do.
+__device__ __forceinline__ double exact_pair(
+    const GridPlan& plan, double rix, double riy, double riz, double rjx, double rjy, double rjz, int s0, int s1, int s2,
+    double& vx, double& vy, double& vz
+) {
+    double f0 = static_cast<double>(s0);
+    double f1 = static_cast<double>(s1);
+    double f2 = static_cast<double>(s2);
+    double shx = __dadd_rn(__dadd_rn(__dmul_rn(f0, plan.H[0][0]), __dmul_rn(f1, plan.H[1][0])), __dmul_rn(f2, plan.H[2][0]));
+    double shy = __dadd_rn(__dadd_rn(__dmul_rn(f0, plan.H[0][1]), __dmul_rn(f1, plan.H[1][1])), __dmul_rn(f2, plan.H[2][1]));
+    double shz = __dadd_rn(__dadd_rn(__dmul_rn(f0, plan.H[0][2]), __dmul_rn(f1, plan.H[1][2])), __dmul_rn(f2, plan.H[2][2]));
+    vx = __dadd_rn(__dsub_rn(rjx, rix), shx);
+    vy = __dadd_rn(__dsub_rn(rjy, riy), shy);
+    vz = __dadd_rn(__dsub_rn(rjz, riz), shz);
+    return __dadd_rn(__dadd_rn(__dmul_rn(vx, vx), __dmul_rn(vy, vy)), __dmul_rn(vz, vz));
+}
+
+__device__ __forceinline__ void cell_coordinates(const GridPlan& plan, int home, int& c0, int& c1, int& c2) {
+    c0 = home % plan.n_cells[0];
+    c1 = (home / plan.n_cells[0]) % plan.n_cells[1];
+    c2 = home / (plan.n_cells[0] * plan.n_cells[1]);
+}
+
+__device__ __forceinline__ int words_of_cell(const GridPlan& plan, const int32_t* __restrict__ cell_start, int c0, int c1, int c2, int home, int n_groups, SegmentTable& table, int& last_total) {
+    int words = 0;
+    for (int g = 0; g < n_groups; g++) {
+        last_total = setup_segments(plan, cell_start, c0, c1, c2, home, g, table);
+        words += (last_total + 31) >> 5;
+        if (n_groups > 1) {
+            __syncthreads();
+        }
+    }
+    return words;
+}
+
+// ---------------------------------------------------------------------------
+// count pass
+// Replaces the distance test of find_neighbors_cell_list
+// (vesin/src/cuda/cell_list.cu:594-641) and the CPU callback
+// (vesin/src/cpu_cell_list.cpp:100-163).
+// ---------------------------------------------------------------------------
+
+constexpr int COUNT_BATCH = 1024; // candidate slots staged at once
+#define FAR_AWAY __int_as_float(0x7f800000) // +inf: never inside any cutoff
+
+__global__ void __launch_bounds__(CTA_THREADS) count_kernel(
+    const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, uint32_t* __restrict__ masks,
+    unsigned long long mask_capacity, unsigned long long* __restrict__ mask_base, uint32_t* __restrict__ cell_words,
+    uint32_t* __restrict__ row_count, DeviceHeader* header
+) {
+    __shared__ SegmentTable table;
+    __shared__ float4 stage[COUNT_BATCH];
+    __shared__ unsigned long long s_base;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int n_groups = (plan.n_stencil + SEG_MAX - 1) / SEG_MAX;
+
+    for (int home = blockIdx.x; home < plan.n_cells_total; home += gridDim.x) {
+        const int cell_begin = cell_start[home];
+        const int n_home = cell_start[home + 1] - cell_begin;
+        if (n_home == 0) {
+            continue;
+        }
+        int c0, c1, c2;
+        cell_coordinates(plan, home, c0, c1, c2);
+
+        // centre of the home cell: origin of the fp32 local frame
+        double centre[3];
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+            centre[c] = plan.origin[c] + (c0 + 0.5) * plan.cell_vec[0][c] + (c1 + 0.5) * plan.cell_vec[1][c] + (c2 + 0.5) * plan.cell_vec[2][c];
+        }
+
+        int group_total = 0;
+        const int words = words_of_cell(plan, cell_start, c0, c1, c2, home, n_groups, table, group_total);
+
+        // claim mask storage for this cell: n_home rows of `words` words
+        if (threadIdx.x == 0) {
+            unsigned long long need = static_cast<unsigned long long>(n_home) * words;
+            unsigned long long base = atomicAdd(&header->mask_cursor, need);
+            if (base + need > mask_capacity) {
+                atomicOr(&header->status, STATUS_MASK_OVERFLOW);
+                base = ~0ull;
+            } else {
+                mask_base[home] = base;
+                cell_words[home] = static_cast<uint32_t>(words);
+            }
+            s_base = base;
+        }
+        __syncthreads();
+        const unsigned long long base = s_base;
+        if (base == ~0ull) {
+            __syncthreads();
+            continue; // the host grows the storage and runs the pass again
+        }
+
+        int word_base = 0;
+        for (int g = 0; g < n_groups; g++) {
+            if (n_groups > 1) {
+                group_total = setup_segments(plan, cell_start, c0, c1, c2, home, g, table);
+            }
+            for (int batch0 = 0; batch0 < group_total; batch0 += COUNT_BATCH) {
+                const int batch_slots = min(COUNT_BATCH, group_total - batch0);
+                const int batch_words = (batch_slots + 31) >> 5;
+
+                // ---- stage the candidates of this batch as fp32 local coordinates ----
+                for (int s = threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
+                    float4 record = make_float4(FAR_AWAY, FAR_AWAY, FAR_AWAY, 0.0f);
+                    if (s < batch_slots) {
+                        int slot = batch0 + s;
+                        int t = find_segment(table, slot);
+                        size_t p = static_cast<size_t>(table.start[t]) + (slot - table.slot0[t]);
+                        double rel0 = static_cast<double>(table.q[0][t] - sorted.shift[3 * p + 0]);
+                        double rel1 = static_cast<double>(table.q[1][t] - sorted.shift[3 * p + 1]);
+                        double rel2 = static_cast<double>(table.q[2][t] - sorted.shift[3 * p + 2]);
+                        double x = sorted.pos[3 * p + 0] + (rel0 * plan.H[0][0] + rel1 * plan.H[1][0] + rel2 * plan.H[2][0]) - centre[0];
+                        double y = sorted.pos[3 * p + 1] + (rel0 * plan.H[0][1] + rel1 * plan.H[1][1] + rel2 * plan.H[2][1]) - centre[1];
+                        double z = sorted.pos[3 * p + 2] + (rel0 * plan.H[0][2] + rel1 * plan.H[1][2] + rel2 * plan.H[2][2]) - centre[2];
+                        unsigned tag = (static_cast<unsigned>(sorted.index[p]) << 1) | static_cast<unsigned>(table.self_ok[t]);
+                        record = make_float4(static_cast<float>(x), static_cast<float>(y), static_cast<float>(z), __uint_as_float(tag));
+                    }
+                    stage[s] = record;
+                }
+                __syncthreads();
+
+                // ---- every warp takes home points in turn; lanes take slots ----
+                for (int il = warp; il < n_home; il += CTA_WARPS) {
+                    const size_t pi = static_cast<size_t>(cell_begin) + il;
+                    const double rix = sorted.pos[3 * pi + 0];
+                    const double riy = sorted.pos[3 * pi + 1];
+                    const double riz = sorted.pos[3 * pi + 2];
+                    const int si0 = sorted.shift[3 * pi + 0];
+                    const int si1 = sorted.shift[3 * pi + 1];
+                    const int si2 = sorted.shift[3 * pi + 2];
+                    const int index_i = sorted.index[pi];
+                    const unsigned tag_i = static_cast<unsigned>(index_i) << 1;
+
+                    const float xi = static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - centre[0]);
+                    const float yi = static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - centre[1]);
+                    const float zi = static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - centre[2]);
+
+                    unsigned my_word = 0;
+                    unsigned hits = 0;
+                    for (int w = 0; w < batch_words; w++) {
+                        const float4 cand = stage[w * 32 + lane];
+                        const float dx = cand.x - xi;
+                        const float dy = cand.y - yi;
+                        const float dz = cand.z - zi;
+                        const float d2 = dx * dx + dy * dy + dz * dz;
+                        const unsigned tag = __float_as_uint(cand.w);
+                        const bool keep = plan.full ? (tag != tag_i) : (tag > tag_i);
+                        bool hit = keep && (d2 < plan.cutoff2_lo);
+                        if (keep && !hit && d2 <= plan.cutoff2_hi) {
+                            // too close to the cutoff for fp32: the exact fp64 predicate decides
+                            int slot = batch0 + w * 32 + lane;
+                            int t = find_segment(table, slot);
+                            size_t pj = static_cast<size_t>(table.start[t]) + (slot - table.slot0[t]);
+                            double vx, vy, vz;
+                            double d2_exact = exact_pair(
+                                plan, rix, riy, riz, sorted.pos[3 * pj + 0], sorted.pos[3 * pj + 1], sorted.pos[3 * pj + 2],
+                                table.q[0][t] + si0 - sorted.shift[3 * pj + 0], table.q[1][t] + si1 - sorted.shift[3 * pj + 1],
+                                table.q[2][t] + si2 - sorted.shift[3 * pj + 2], vx, vy, vz
+                            );
+                            hit = d2_exact < plan.cutoff2;
+                        }
+                        const unsigned ballot = __ballot_sync(FULL_MASK, hit);
+                        hits += __popc(ballot);
+                        if (lane == w) {
+                            my_word = ballot;
+                        }
+                    }
+                    if (lane < batch_words) {
+                        masks[base + static_cast<unsigned long long>(il) * words + word_base + (batch0 >> 5) + lane] = my_word;
+                    }
+                    if (lane == 0 && hits != 0) {
+                        row_count[index_i] += hits;
+                    }
+                }
+                __syncthreads();
+            }
+            word_base += (group_total + 31) >> 5;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// emit pass
+// Replaces the append path of find_neighbors_cell_list
+// (vesin/src/cuda/cell_list.cu:643-703, one global counter) and
+// GrowableNeighborList (vesin/src/cpu_cell_list.cpp:465-632): every point
+// writes its pairs into its own row of the exactly-sized output.
+// ---------------------------------------------------------------------------
+
+constexpr int EMIT_BATCH = 1024;
+
+struct EmitShared {
+    SegmentTable table;
+    double x[EMIT_BATCH];
+    double y[EMIT_BATCH];
+    double z[EMIT_BATCH];
+    int j[EMIT_BATCH];
+    int s[3][EMIT_BATCH];           // q - wrap shift of the candidate
+    int queue[CTA_WARPS][64];       // per-warp ring of hit slots
+    int shift_out[CTA_WARPS][96];   // per-warp transposition buffers
+    double vector_out[CTA_WARPS][96];
+};
+
+/// Write up to 32 queued hits of one home point. Lane l handles the l-th hit;
+/// 12- and 24-byte elements go through shared memory so that every store
+/// instruction covers one contiguous span.
+__device__ __forceinline__ void flush_hits(
+    const GridPlan& plan, EmitShared& sh, int warp, int lane, int head, int n_hits, unsigned long long row, double rix, double riy,
+    double riz, int si0, int si1, int si2, int index_i, const PairOutput& out
+) {
+    double vx = 0, vy = 0, vz = 0, d2 = 0;
+    int s0 = 0, s1 = 0, s2 = 0;
+    const bool valid = lane < n_hits;
+    if (valid) {
+        const int slot = sh.queue[warp][(head + lane) & 63];
+        s0 = sh.s[0][slot] + si0;
+        s1 = sh.s[1][slot] + si1;
+        s2 = sh.s[2][slot] + si2;
+        d2 = exact_pair(plan, rix, riy, riz, sh.x[slot], sh.y[slot], sh.z[slot], s0, s1, s2, vx, vy, vz);
+        ulonglong2 pair = make_ulonglong2(static_cast<unsigned long long>(index_i), static_cast<unsigned long long>(sh.j[slot]));
+        reinterpret_cast<ulonglong2*>(out.pairs)[row + lane] = pair;
+        if (out.distances != nullptr) {
+            out.distances[row + lane] = __dsqrt_rn(d2);
+        }
+    }
+    if (out.shifts != nullptr) {
+        int* buffer = sh.shift_out[warp];
+        buffer[3 * lane + 0] = s0;
+        buffer[3 * lane + 1] = s1;
+        buffer[3 * lane + 2] = s2;
+        __syncwarp();
+        int32_t* dst = out.shifts + 3 * row;
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            int w = k * 32 + lane;
+            if (w < 3 * n_hits) {
+                dst[w] = buffer[w];
+            }
+        }
+    }
+    if (out.vectors != nullptr) {
+        double* buffer = sh.vector_out[warp];
+        buffer[3 * lane + 0] = vx;
+        buffer[3 * lane + 1] = vy;
+        buffer[3 * lane + 2] = vz;
+        __syncwarp();
+        double* dst = out.vectors + 3 * row;
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            int w = k * 32 + lane;
+            if (w < 3 * n_hits) {
+                dst[w] = buffer[w];
+            }
+        }
+    }
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
+    const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, const uint32_t* __restrict__ masks,
+    const unsigned long long* __restrict__ mask_base, const uint32_t* __restrict__ cell_words,
+    const unsigned long long* __restrict__ row_start, uint32_t* __restrict__ row_fill, PairOutput out
+) {
+    extern __shared__ __align__(16) unsigned char emit_smem[];
+    EmitShared& sh = *reinterpret_cast<EmitShared*>(emit_smem);
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int n_groups = (plan.n_stencil + SEG_MAX - 1) / SEG_MAX;
+
+    for (int home = blockIdx.x; home < plan.n_cells_total; home += gridDim.x) {
+        const int cell_begin = cell_start[home];
+        const int n_home = cell_start[home + 1] - cell_begin;
+        if (n_home == 0) {
+            continue;
+        }
+        int c0, c1, c2;
+        cell_coordinates(plan, home, c0, c1, c2);
+        const unsigned long long base = mask_base[home];
+        const int words = static_cast<int>(cell_words[home]);
+
+        int word_base = 0;
+        for (int g = 0; g < n_groups; g++) {
+            const int group_total = setup_segments(plan, cell_start, c0, c1, c2, home, g, sh.table);
+            const bool single_batch = (n_groups == 1) && (group_total <= EMIT_BATCH);
+            for (int batch0 = 0; batch0 < group_total; batch0 += EMIT_BATCH) {
+                const int batch_slots = min(EMIT_BATCH, group_total - batch0);
+                const int batch_words = (batch_slots + 31) >> 5;
+
+                // ---- stage original positions, indices and shift parts ----
+                for (int s = threadIdx.x; s < batch_slots; s += CTA_THREADS) {
+                    int slot = batch0 + s;
+                    int t = find_segment(sh.table, slot);
+                    size_t p = static_cast<size_t>(sh.table.start[t]) + (slot - sh.table.slot0[t]);
+                    sh.x[s] = sorted.pos[3 * p + 0];
+                    sh.y[s] = sorted.pos[3 * p + 1];
+                    sh.z[s] = sorted.pos[3 * p + 2];
+                    sh.j[s] = sorted.index[p];
+                    sh.s[0][s] = sh.table.q[0][t] - sorted.shift[3 * p + 0];
+                    sh.s[1][s] = sh.table.q[1][t] - sorted.shift[3 * p + 1];
+                    sh.s[2][s] = sh.table.q[2][t] - sorted.shift[3 * p + 2];
+                }
+                __syncthreads();
+
+                for (int il = warp; il < n_home; il += CTA_WARPS) {
+                    const size_t pi = static_cast<size_t>(cell_begin) + il;
+                    const int index_i = sorted.index[pi];
+                    const uint32_t* mask_row = masks + base + static_cast<unsigned long long>(il) * words + word_base + (batch0 >> 5);
+
+                    // one 32-slot word per lane; batches hold at most 32 words
+                    const unsigned my_word = (lane < batch_words) ? mask_row[lane] : 0u;
+                    if (__ballot_sync(FULL_MASK, my_word != 0) == 0) {
+                        continue;
+                    }
+
+                    const double rix = sorted.pos[3 * pi + 0];
+                    const double riy = sorted.pos[3 * pi + 1];
+                    const double riz = sorted.pos[3 * pi + 2];
+                    const int si0 = sorted.shift[3 * pi + 0];
+                    const int si1 = sorted.shift[3 * pi + 1];
+                    const int si2 = sorted.shift[3 * pi + 2];
+
+                    unsigned filled = single_batch ? 0u : row_fill[index_i];
+                    unsigned long long row = row_start[index_i] + filled;
+
+                    int head = 0;
+                    int queued = 0;
+                    for (int w = 0; w < batch_words; w++) {
+                        const unsigned word = __shfl_sync(FULL_MASK, my_word, w);
+                        if (word == 0) {
+                            continue;
+                        }
+                        if ((word >> lane) & 1u) {
+                            int position = queued + __popc(word & lanemask_lt());
+                            sh.queue[warp][(head + position) & 63] = w * 32 + lane;
+                        }
+                        queued += __popc(word);
+                        __syncwarp();
+                        if (queued >= 32) {
+                            flush_hits(plan, sh, warp, lane, head, 32, row, rix, riy, riz, si0, si1, si2, index_i, out);
+                            row += 32;
+                            filled += 32;
+                            head = (head + 32) & 63;
+                            queued -= 32;
+                        }
+                    }
+                    if (queued > 0) {
+                        flush_hits(plan, sh, warp, lane, head, queued, row, rix, riy, riz, si0, si1, si2, index_i, out);
+                        filled += queued;
+                    }
+                    if (!single_batch && lane == 0) {
+                        row_fill[index_i] = filled;
+                    }
+                }
+                __syncthreads();
+            }
+            word_base += (group_total + 31) >> 5;
+        }
+    }
+}
+
+int pair_grid(int n_cells_total, int per_sm) {
+    int device = 0;
+    int sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) {
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    }
+    long long cap = static_cast<long long>(sms) * per_sm;
+    return static_cast<int>(n_cells_total < cap ? n_cells_total : cap);
+}
+
+} // namespace
+
+// ---------------------------------------------------------------------------
+// launch wrappers
+// ---------------------------------------------------------------------------
+
+void configure_kernels() {
+    cudaFuncSetAttribute(emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
+}
+
+void launch_header_init(DeviceHeader* header, const double* box, const bool* periodic, cudaStream_t stream) {
+    header_init_kernel<<<1, 32, 0, stream>>>(header, box, periodic);
+}
+
+void launch_bounds(const double* points, size_t n, DeviceHeader* header, cudaStream_t stream) {
+    if (n == 0) {
+        return;
+    }
+    size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
+    if (blocks > 148 * 8) {
+        blocks = 148 * 8;
+    }
+    bounds_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, header);
+}
+
+void launch_bin(
+    const double* points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift, int32_t* cell_count,
+    cudaStream_t stream
+) {
+    size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
+    bin_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, plan, cell_of, rank, shift, cell_count);
+}
+
+size_t scan_tmp_bytes(size_t n) {
+    size_t tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
+    return (tiles + 1) * sizeof(unsigned long long);
+}
+
+template <typename TIn, typename TOut>
+static void launch_scan(const TIn* counts, TOut* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream) {
+    auto* tile_sums = static_cast<unsigned long long*>(tmp);
+    size_t tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
+    scan_tile_sums_kernel<TIn><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, n, tile_sums);
+    scan_spine_kernel<<<1, CTA_THREADS, 0, stream>>>(tile_sums, tiles, total);
+    scan_apply_kernel<TIn, TOut><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, starts, n, tile_sums);
+}
+
+void launch_scan_cells(const int32_t* counts, int32_t* starts, size_t n, void* tmp, cudaStream_t stream) {
+    launch_scan<int32_t, int32_t>(counts, starts, n, tmp, nullptr, stream);
+}
+
+void launch_scan_rows(
+    const uint32_t* counts, unsigned long long* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream
+) {
+    launch_scan<uint32_t, unsigned long long>(counts, starts, n, tmp, total, stream);
+}
+
+void launch_scatter(
+    const double* points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
+    SortedPoints sorted, cudaStream_t stream
+) {
+    size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
+    scatter_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, cell_of, rank, shift, cell_start, sorted);
+}
+
+void launch_count(
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, uint32_t* masks, unsigned long long mask_capacity,
+    unsigned long long* mask_base, uint32_t* cell_words, uint32_t* row_count, DeviceHeader* header, cudaStream_t stream
+) {
+    int grid = pair_grid(plan.n_cells_total, 32);
+    count_kernel<<<grid, CTA_THREADS, 0, stream>>>(plan, cell_start, sorted, masks, mask_capacity, mask_base, cell_words, row_count, header);
+}
+
+void launch_emit(
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks, const unsigned long long* mask_base,
+    const uint32_t* cell_words, const unsigned long long* row_start, uint32_t* row_fill, PairOutput out, cudaStream_t stream
+) {
+    int grid = pair_grid(plan.n_cells_total, 16);
+    emit_kernel<<<grid, CTA_THREADS, sizeof(EmitShared), stream>>>(plan, cell_start, sorted, masks, mask_base, cell_words, row_start, row_fill, out);
+}
+
+} // namespace vb200

@@ -1,0 +1,98 @@
+// Device-side data structures and the launch wrappers of every kernel of the
+// neighbor-list build. All kernels are written for sm_100a; none uses tensor
+// cores: the build is a gather / compare / emit workload bounded by HBM
+// bandwidth.
+#ifndef VESIN_B200_KERNELS_CUH
+#define VESIN_B200_KERNELS_CUH
+
+#include <cstddef>
+#include <cstdint>
+
+#include <cuda_runtime.h>
+
+#include "plan.hpp"
+
+namespace vb200 {
+
+/// Small block of device memory read back by the host (through a pinned
+/// mirror) at the synchronisation points of a build.
+struct DeviceHeader {
+    unsigned long long min_key[3];   // order-preserving keys of the smallest coordinates
+    unsigned long long max_key[3];   // ... and of the largest
+    unsigned long long first_bad;    // smallest index of a point with a non-finite coordinate
+    unsigned long long total_pairs;  // written by the scan over per-point pair counts
+    unsigned long long mask_cursor;  // words of hit-mask storage claimed by the count pass
+    unsigned int status;             // sticky error bits, see STATUS_*
+    unsigned int pad;
+    double box[9];                   // copy of the caller's box
+    unsigned char periodic[8];       // copy of the caller's periodic flags
+};
+
+constexpr unsigned int STATUS_MASK_OVERFLOW = 1u;
+constexpr unsigned long long NO_BAD_POINT = ~0ull;
+
+/// Cell-sorted copy of the points ("records"): original position, original
+/// index and the wrap shift that brings the point into the box.
+struct SortedPoints {
+    double* pos;    // [n][3]
+    int32_t* index; // [n]
+    int32_t* shift; // [n][3]
+};
+
+/// Output arrays of the C ABI; null pointers are not written.
+struct PairOutput {
+    unsigned long long* pairs; // [total][2]
+    int32_t* shifts;           // [total][3]
+    double* distances;         // [total]
+    double* vectors;           // [total][3]
+};
+
+// ---- launch wrappers (all asynchronous on `stream`) ----
+
+void launch_header_init(DeviceHeader* header, const double* box, const bool* periodic, cudaStream_t stream);
+
+/// Min / max of every coordinate and the first non-finite point.
+void launch_bounds(const double* points, size_t n, DeviceHeader* header, cudaStream_t stream);
+
+/// Wrap into the cell, pick the cell, histogram with warp-aggregated atomics.
+void launch_bin(
+    const double* points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift,
+    int32_t* cell_count, cudaStream_t stream
+);
+
+/// Exclusive scan of int32 counts into int32 starts (n + 1 entries).
+void launch_scan_cells(const int32_t* counts, int32_t* starts, size_t n, void* tmp, cudaStream_t stream);
+/// Exclusive scan of uint32 counts into uint64 starts (n + 1 entries); the
+/// grand total also goes to *total.
+void launch_scan_rows(
+    const uint32_t* counts, unsigned long long* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream
+);
+/// Bytes of temporary storage the scans need for n elements.
+size_t scan_tmp_bytes(size_t n);
+
+/// Counting-sort scatter into the cell-sorted records.
+void launch_scatter(
+    const double* points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift,
+    const int32_t* cell_start, SortedPoints sorted, cudaStream_t stream
+);
+
+/// Pass 1: fp32 screen + fp64 decision for every (point, candidate); writes
+/// one hit bit per candidate and the number of pairs of every point.
+void launch_count(
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, uint32_t* masks, unsigned long long mask_capacity,
+    unsigned long long* mask_base, uint32_t* cell_words, uint32_t* row_count, DeviceHeader* header, cudaStream_t stream
+);
+
+/// Pass 2: walks the hit bits and writes i, j, S, d, D with coalesced stores.
+void launch_emit(
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks,
+    const unsigned long long* mask_base, const uint32_t* cell_words, const unsigned long long* row_start,
+    uint32_t* row_fill, PairOutput out, cudaStream_t stream
+);
+
+/// One-time per-device kernel attribute setup (shared-memory opt-in).
+void configure_kernels();
+
+} // namespace vb200
+
+#endif
