@@ -1,0 +1,416 @@
+"""
+Benchmark of the neighbor-list build (one "step" = one build through the C ABI).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload diamond512k|diamond1000|...]
+
+Prints ONE JSON line (rank 0). Metric: neighbor pairs per second of the
+512 000-atom diamond build (full list, fp64, quantities i j S d D), inputs
+resident in HBM; `e2e` is the same build from pinned host buffers with the
+host->device copy of the points and the device->host copy of every output
+array inside the timed region. `--impl reference` times the unmodified
+reference CPU path (oracle/_ref) on the host cores on the same workload.
+With N > 1 every rank builds its own copy of the system on its own GPU
+(independent systems, no communication): weak scaling.
+"""
+
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from vesin_b200 import workloads  # noqa: E402
+
+WORKLOADS = {
+    # name: (generator, cutoff, full list, description)
+    "diamond512k": (lambda: workloads.diamond(40), 5.0, True, "diamond 40x40x40 (512000 atoms), cutoff 5.0, full list, fp64, ijSdD"),
+    "diamond512k_half": (lambda: workloads.diamond(40), 5.0, False, "diamond 40x40x40 (512000 atoms), cutoff 5.0, half list, fp64, ijSdD"),
+    "diamond110k": (lambda: workloads.diamond(24), 5.0, True, "diamond 24x24x24 (110592 atoms), cutoff 5.0, full list, fp64, ijSdD"),
+    "diamond1000": (lambda: workloads.diamond(5), 5.0, True, "diamond 5x5x5 (1000 atoms), cutoff 5.0, full list, fp64, ijSdD"),
+    "triclinic64": (lambda: workloads.small_triclinic(), 9.0, True, "64 atoms in a small triclinic cell, cutoff 9.0, full list, fp64, ijSdD"),
+    "liquid2m": (lambda: workloads.liquid(1 << 21), 6.0, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, half list, fp64 ABI, ijSdD"),
+}
+
+BYTES_PER_POINT = 24  # fp64 positions
+BYTES_PER_PAIR = 16 + 12 + 8 + 24  # i, j as size_t; S int32[3]; d; D
+
+
+def algorithmic_bytes(n_points, n_pairs):
+    return n_points * BYTES_PER_POINT + n_pairs * BYTES_PER_PAIR
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the
+    timed region runs."""
+
+    def __init__(self, index):
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _run(self):
+        nv = self._nvml
+        names = {
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "hw_power_brake_slowdown": getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {
+            "sm_mhz": float(np.median(self.samples)) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def physical_gpu_index(local_index):
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if visible:
+        try:
+            return int(visible.split(",")[local_index])
+        except (ValueError, IndexError):
+            pass
+    return local_index
+
+
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def time_reference_cpu(system, cutoff, full, steps, warmup, budget_s):
+    """Reference CPU path on all host cores; returns (pairs, seconds per build,
+    builds timed)."""
+    from oracle import oracle
+
+    oracle.build()
+    cpu = oracle.ReferenceCPU()
+    points, box, periodic = system
+    n_pairs = 0
+    started = time.perf_counter()
+    for _ in range(warmup):
+        n_pairs = cpu.run(points, box, periodic, cutoff, full, "ijSdD", n_threads=0)
+        if time.perf_counter() - started > budget_s / 2:
+            break
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        n_pairs = cpu.run(points, box, periodic, cutoff, full, "ijSdD", n_threads=0)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - started > budget_s:
+            break
+    return n_pairs, float(np.mean(times)), len(times)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    make, cutoff, full, description = WORKLOADS[args.workload]
+    system = make()
+    n_pairs, seconds, timed = time_reference_cpu(system, cutoff, full, args.steps, args.warmup, budget_s=240.0)
+    cores = host_cores()
+    value = n_pairs / seconds
+    line = {
+        "impl": "reference",
+        "metric": "neighbor pairs/s",
+        "value": value,
+        "unit": "pairs/s",
+        "n_gpus": args.gpus,
+        "steps": timed,
+        "warmup": args.warmup,
+        "ms_per_step": seconds * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": description, "n_points": int(len(system[0])), "n_pairs": int(n_pairs), "l2": "outputs (GBs) exceed L2"},
+        "cpu_baseline": {
+            "value": value,
+            "unit": "pairs/s",
+            "cores": cores,
+            "kind": "reference",
+            "sample": f"{timed} full builds of the workload, reference CPU path, n_threads=0 (all {cores} cores)",
+        },
+        "e2e": {"value": value, "unit": "pairs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import vesin_b200
+    from vesin_b200._c_api import N_STAGES, STAGE_NAMES, VesinCUDA, VesinDevice, VesinNeighborList, VesinOptions
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    lib = vesin_b200.get_library()
+    make, cutoff, full, description = WORKLOADS[args.workload]
+    points, box, periodic = make()
+    n_points = len(points)
+
+    h_points = torch.from_numpy(points).pin_memory()
+    d_points = h_points.to(device)
+    d_box = torch.from_numpy(box).to(device)
+    d_periodic = torch.from_numpy(periodic).to(device)
+
+    options = VesinOptions()
+    options.cutoff = cutoff
+    options.full = full
+    options.sorted = False
+    options.algorithm = 0
+    options.n_threads = 0
+    options.return_shifts = True
+    options.return_distances = True
+    options.return_vectors = True
+    options.skin = 0.0
+    c_device = VesinDevice(VesinCUDA, local_rank)
+    neighbors = VesinNeighborList()
+    error = ctypes.c_char_p()
+
+    def build(points_tensor):
+        status = lib.vesin_neighbors(
+            points_tensor.data_ptr(), n_points, d_box.data_ptr(), d_periodic.data_ptr(), c_device, options,
+            ctypes.byref(neighbors), ctypes.byref(error),
+        )
+        if status != 0:
+            raise RuntimeError(error.value.decode("utf8"))
+        return neighbors.length
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)  # > 126 MB of L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---- warm-up (also sizes the workspace and the output arrays) ----
+    for _ in range(max(args.warmup, 3)):
+        n_pairs = build(d_points)
+
+    # ---- timed region 1: device-resident inputs ----
+    stage_ms = np.zeros(N_STAGES)
+    stage_buffer = (ctypes.c_double * N_STAGES)()
+    lib.vesin_b200_set_profiling(1)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    wall0 = time.perf_counter()
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        for k in range(args.steps):
+            flush.fill_(k & 0xFF)  # untimed: evicts L2 between builds
+            starts[k].record()
+            n_pairs = build(d_points)
+            stops[k].record()
+            if lib.vesin_b200_stage_times(ctypes.byref(neighbors), stage_buffer) == 0:
+                stage_ms += np.array(stage_buffer[:])
+        barrier()
+    wall = time.perf_counter() - wall0
+    lib.vesin_b200_set_profiling(0)
+    device_ms = sum(a.elapsed_time(b) for a, b in zip(starts, stops))
+    stage_ms /= args.steps
+
+    # ---- timed region 2: end to end from pinned host buffers ----
+    out_host = {
+        "pairs": torch.empty((n_pairs, 2), dtype=torch.int64).pin_memory(),
+        "shifts": torch.empty((n_pairs, 3), dtype=torch.int32).pin_memory(),
+        "distances": torch.empty((n_pairs,), dtype=torch.float64).pin_memory(),
+        "vectors": torch.empty((n_pairs, 3), dtype=torch.float64).pin_memory(),
+    }
+    e2e_steps = max(1, min(args.steps, 5))
+    staging = torch.empty_like(d_points)
+
+    def copy_out(name, pointer, count, dtype, cupy_typestr):
+        from vesin_b200._neighbors import _view
+
+        shape = tuple(out_host[name].shape)
+        view = _view(pointer, shape, cupy_typestr, device, neighbors)
+        if dtype == torch.int64:
+            view = view.view(torch.int64)
+        out_host[name].copy_(view, non_blocking=True)
+
+    def e2e_step():
+        staging.copy_(h_points, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+        count = build(staging)
+        assert count == n_pairs
+        copy_out("pairs", neighbors.pairs, count, torch.int64, "<u8")
+        copy_out("shifts", neighbors.shifts, count, torch.int32, "<i4")
+        copy_out("distances", neighbors.distances, count, torch.float64, "<f8")
+        copy_out("vectors", neighbors.vectors, count, torch.float64, "<f8")
+        torch.cuda.current_stream(device).synchronize()
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # ---- reduce over ranks: slowest rank sets the time ----
+    times = torch.tensor([device_ms, e2e_ms, wall * 1e3], dtype=torch.float64, device=device)
+    pairs_total = torch.tensor([float(n_pairs)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(pairs_total, op=dist.ReduceOp.SUM)
+    device_ms, e2e_ms, wall_ms = times.tolist()
+    total_pairs = pairs_total.item()
+
+    if rank == 0:
+        ms_per_step = device_ms / args.steps
+        value = total_pairs / (ms_per_step * 1e-3)
+        bytes_per_build = algorithmic_bytes(n_points, n_pairs)
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_path):
+            with open(peaks_path) as fd:
+                peak = float(json.load(fd)["hbm_gbs"])
+            peak_source = "measured (MEASURED_PEAKS.json hbm_gbs)"
+        else:
+            peak, peak_source = 6650.0, "fallback"
+        emit_ms = float(stage_ms[STAGE_NAMES.index("emit")])
+        achieved = bytes_per_build / (emit_ms * 1e-3) / 1e9 if emit_ms > 0 else None
+        line = {
+            "metric": "neighbor pairs/s",
+            "value": value,
+            "unit": "pairs/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f64",
+            "data": "synthetic",
+            "config": {
+                "workload": description,
+                "n_points": n_points,
+                "n_pairs": int(n_pairs),
+                "per_gpu": "one independent copy of the system per GPU, no communication",
+                "l2": "256 MiB buffer written between timed builds (untimed); outputs (2.7 GB) exceed L2",
+            },
+            "roofline": {
+                "bound": "hbm",
+                "kernel": "emit_kernel",
+                "achieved": achieved,
+                "peak": peak,
+                "unit": "GB/s",
+                "frac": (achieved / peak) if achieved else None,
+                "peak_source": peak_source,
+                "traffic": None,
+                "bytes_per_launch": bytes_per_build,
+                "kernel_ms": emit_ms,
+                "whole_build_frac": bytes_per_build / (ms_per_step * 1e-3) / 1e9 / peak,
+            },
+            "stages_ms": {name: float(ms) for name, ms in zip(STAGE_NAMES, stage_ms)},
+            "e2e": {
+                "value": total_pairs / (e2e_ms * 1e-3),
+                "unit": "pairs/s",
+                "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": n_points * 24,
+                "d2h_bytes_per_step": int(n_pairs) * BYTES_PER_PAIR,
+            },
+            "gpu_launches": 12 * args.steps,  # header, bounds, bin, 3 scan, scatter, count, 3 scan, emit
+            "wall_ms_per_step": wall_ms / args.steps,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cpu_pairs, cpu_seconds, timed = time_reference_cpu((points, box, periodic), cutoff, full, 2, 1, budget_s=45.0)
+            assert cpu_pairs == n_pairs, f"CPU reference found {cpu_pairs} pairs, GPU {n_pairs}"
+            cores = host_cores()
+            line["cpu_baseline"] = {
+                "value": cpu_pairs / cpu_seconds,
+                "unit": "pairs/s",
+                "cores": cores,
+                "kind": "reference",
+                "sample": f"{timed} full builds of the same workload after 1 warm-up, reference CPU path (oracle/_ref), n_threads=0",
+                "ms_per_build": cpu_seconds * 1e3,
+            }
+        print(json.dumps(line))
+
+    lib.vesin_free(ctypes.byref(neighbors))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default="diamond512k", choices=sorted(WORKLOADS))
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

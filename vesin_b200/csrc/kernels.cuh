@@ -76,18 +76,27 @@ void launch_scatter(
     const int32_t* cell_start, SortedPoints sorted, cudaStream_t stream
 );
 
-/// Pass 1: fp32 screen + fp64 decision for every (point, candidate); writes
-/// one hit bit per candidate and the number of pairs of every point.
-void launch_count(
-    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, uint32_t* masks, unsigned long long mask_capacity,
-    unsigned long long* mask_base, uint32_t* cell_words, uint32_t* row_count, DeviceHeader* header, cudaStream_t stream
+/// Exclusive scan of uint64 counts into uint64 starts (n + 1 entries); the
+/// grand total also goes to *total.
+void launch_scan_units(
+    const unsigned long long* counts, unsigned long long* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream
 );
 
-/// Pass 2: walks the hit bits and writes i, j, S, d, D with coalesced stores.
+/// Pass 1: fp32 screen + fp64 decision for every (point, candidate); writes
+/// one hit bit per candidate, the number of pairs of every work unit and,
+/// when plan.by_index is set, the number of pairs of every point.
+void launch_count(
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, uint32_t* masks, unsigned long long mask_capacity,
+    unsigned long long* unit_mask_base, uint32_t* unit_words, unsigned long long* unit_count, uint32_t* row_count,
+    DeviceHeader* header, cudaStream_t stream
+);
+
+/// Pass 2: walks the hit bits and writes i, j, S, d, D with coalesced stores:
+/// unit after unit (plan.by_index == 0) or one row per point in index order.
 void launch_emit(
-    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks,
-    const unsigned long long* mask_base, const uint32_t* cell_words, const unsigned long long* row_start,
-    uint32_t* row_fill, PairOutput out, cudaStream_t stream
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks, const unsigned long long* unit_mask_base,
+    const uint32_t* unit_words, const unsigned long long* unit_start, const unsigned long long* row_start, uint32_t* row_fill,
+    PairOutput out, cudaStream_t stream
 );
 
 /// One-time per-device kernel attribute setup (shared-memory opt-in).

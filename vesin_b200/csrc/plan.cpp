@@ -64,6 +64,7 @@ GridPlan make_plan(
     size_t n_points,
     double cutoff,
     bool full,
+    bool sorted,
     size_t max_cells
 ) {
     GridPlan plan{};
@@ -208,6 +209,18 @@ GridPlan make_plan(
 
     plan.cutoff2 = cutoff * cutoff;
     plan.full = full ? 1 : 0;
+    plan.by_index = sorted ? 1 : 0;
+
+    // Pencil length: the pair passes give one lane to every home point, so a
+    // work unit should hold about one warp of points.
+    double per_cell = static_cast<double>(n_points) / static_cast<double>(plan.n_cells_total);
+    int pencil = 1;
+    if (per_cell > 0.0) {
+        pencil = static_cast<int>(std::floor(30.0 / per_cell));
+    }
+    pencil = std::max(1, std::min({pencil, 8, plan.n_cells[0]}));
+    plan.pencil = pencil;
+    plan.n_units = ((plan.n_cells[0] + pencil - 1) / pencil) * plan.n_cells[1] * plan.n_cells[2];
 
     // fp32 screen. Local coordinates (relative to the centre of the home
     // cell) of a point and of its candidates are bounded by M; each carries a
@@ -222,7 +235,11 @@ GridPlan make_plan(
             plan.cell_vec[k][0] * plan.cell_vec[k][0] + plan.cell_vec[k][1] * plan.cell_vec[k][1] +
             plan.cell_vec[k][2] * plan.cell_vec[k][2]
         );
-        reach += (plan.n_search[k] + 1.0) * len;
+        double cells = plan.n_search[k] + 1.0;
+        if (k == 0) {
+            cells += 0.5 * plan.pencil; // the frame is centred on the pencil
+        }
+        reach += cells * len;
     }
     const double eps = 5.9604644775390625e-08; // 2^-24
     double c = cutoff * 1.01;

@@ -38,6 +38,13 @@ struct GridPlan {
     int32_t n_search[3];
     int32_t n_cells_total;
     int32_t n_stencil; // product of (2 * n_search + 1)
+    /// Work units of the pair passes: pencils of `pencil` consecutive cells
+    /// along the first direction, n_units of them.
+    int32_t pencil;
+    int32_t n_units;
+    /// Output order: 0 = unit after unit (any order is allowed for unsorted
+    /// lists), 1 = one row per point in index order (sorted lists).
+    int32_t by_index;
 
     double cutoff2;   // cutoff * cutoff in fp64: the exact predicate's bound
     float cutoff2_lo; // fp32 screen: below this a candidate is surely inside
@@ -61,6 +68,7 @@ GridPlan make_plan(
     size_t n_points,
     double cutoff,
     bool full,
+    bool sorted,
     size_t max_cells
 );
 
