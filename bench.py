@@ -355,7 +355,7 @@ def run_ours(args):
             },
             "roofline": {
                 "bound": "hbm",
-                "kernel": "emit_kernel",
+                "kernel": "pairs_kernel",
                 "achieved": achieved,
                 "peak": peak,
                 "unit": "GB/s",
@@ -374,7 +374,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": n_points * 24,
                 "d2h_bytes_per_step": int(n_pairs) * BYTES_PER_PAIR,
             },
-            "gpu_launches": 12 * args.steps,  # header, bounds, bin, 3 scan, scatter, count, 3 scan, emit
+            "gpu_launches": 8 * args.steps,  # header, bounds, bin, 3 x scan, scatter, pairs
             "wall_ms_per_step": wall_ms / args.steps,
             "clocks": clocks.summary(),
         }

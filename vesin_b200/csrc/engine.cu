@@ -262,6 +262,21 @@ void read_header(Workspace& ws) {
     VB200_CUDA(cudaStreamSynchronize(ws.stream));
 }
 
+/// Pairs that fit every output array this call needs, as allocated now.
+size_t common_capacity(const Workspace& ws, const VesinOptions& options) {
+    size_t capacity = ws.out_pairs.bytes / (2 * sizeof(size_t));
+    if (options.return_shifts) {
+        capacity = std::min(capacity, ws.out_shifts.bytes / (3 * sizeof(int32_t)));
+    }
+    if (options.return_distances) {
+        capacity = std::min(capacity, ws.out_distances.bytes / sizeof(double));
+    }
+    if (options.return_vectors) {
+        capacity = std::min(capacity, ws.out_vectors.bytes / (3 * sizeof(double)));
+    }
+    return capacity;
+}
+
 void set_outputs(VesinNeighborList& list, Workspace& ws, const VesinOptions& options, size_t capacity) {
     ws.out_pairs.reserve(capacity * 2 * sizeof(size_t));
     list.pairs = reinterpret_cast<size_t(*)[2]>(ws.out_pairs.ptr);
@@ -421,6 +436,84 @@ void neighbors(
     timer.begin(VesinB200StageScatter);
     launch_scatter(flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), sorted, stream);
     timer.end(VesinB200StageScatter);
+
+    const auto pair_limit_message = [&](size_t) {
+        return "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_points * pair_limit_per_point) +
+               " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_points) + "). " +
+               "Consider reducing the cutoff distance, or explicitly setting " +
+               "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable.";
+    };
+
+    if (!plan.by_index) {
+        // ---- unsorted list: one fused pass. The arrays of the previous call
+        // (or a density estimate on the first call) are tried first; when the
+        // pairs do not fit, the pass has still counted them: grow to the
+        // exact total and run it again. ----
+        size_t capacity = common_capacity(ws, options);
+        if (capacity == 0) {
+            double estimate = 0.0;
+            if (plan.periodic[0] && plan.periodic[1] && plan.periodic[2]) {
+                double volume = plan.face_dist[0] * plan.face_dist[1] * plan.face_dist[2];
+                // |det H| from the face distances and the row lengths is not
+                // available cheaply for skewed cells: use the inverse's determinant
+                double det_inv = plan.Hinv[0][0] * (plan.Hinv[1][1] * plan.Hinv[2][2] - plan.Hinv[2][1] * plan.Hinv[1][2]) -
+                                 plan.Hinv[0][1] * (plan.Hinv[1][0] * plan.Hinv[2][2] - plan.Hinv[1][2] * plan.Hinv[2][0]) +
+                                 plan.Hinv[0][2] * (plan.Hinv[1][0] * plan.Hinv[2][1] - plan.Hinv[1][1] * plan.Hinv[2][0]);
+                if (std::abs(det_inv) > 0.0) {
+                    volume = 1.0 / std::abs(det_inv);
+                }
+                double density = static_cast<double>(n_points) / volume;
+                estimate = static_cast<double>(n_points) * density * 4.18879 * options.cutoff * options.cutoff * options.cutoff;
+                if (!options.full) {
+                    estimate *= 0.5;
+                }
+                estimate = estimate * 1.1 + 1024.0;
+                if (estimate > static_cast<double>(n_points) * static_cast<double>(pair_limit_per_point) || estimate * 60.0 > 8.0e9) {
+                    estimate = 0.0; // not worth reserving blindly: count first
+                }
+            }
+            capacity = std::max<size_t>(256, static_cast<size_t>(estimate));
+        }
+        set_outputs(list, ws, options, capacity);
+        capacity = common_capacity(ws, options);
+
+        size_t total = 0;
+        for (int attempt = 0;; attempt++) {
+            PairOutput out{
+                reinterpret_cast<unsigned long long*>(list.pairs),
+                reinterpret_cast<int32_t*>(list.shifts),
+                list.distances,
+                reinterpret_cast<double*>(list.vectors),
+            };
+            timer.begin(VesinB200StageEmit);
+            launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, stream);
+            timer.end(VesinB200StageEmit);
+            VB200_CUDA(cudaGetLastError());
+            read_header(ws);
+            if (attempt == 0) {
+                timer.collect(VesinB200StageBin);
+                timer.collect(VesinB200StageScanCells);
+                timer.collect(VesinB200StageScatter);
+            }
+            timer.collect(VesinB200StageEmit);
+            total = static_cast<size_t>(header.pair_cursor);
+            if (total > n_points * pair_limit_per_point) {
+                throw std::runtime_error(pair_limit_message(total));
+            }
+            if (total <= capacity) {
+                break;
+            }
+            if (attempt >= 2) {
+                throw std::runtime_error("internal error: the pair total kept changing between passes");
+            }
+            set_outputs(list, ws, options, total + total / 16 + 256);
+            capacity = common_capacity(ws, options);
+            VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, sizeof(unsigned long long), stream));
+        }
+        list.length = total;
+        ws.timed = timer.enabled;
+        return;
+    }
 
     // ---- pass 1: decide every candidate; pairs per point; totals ----
     for (int attempt = 0;; attempt++) {

@@ -2,12 +2,14 @@
 //
 // Pipeline of one build (reference stages replaced are cited per kernel):
 //   header_init -> bounds -> [host: grid plan] -> bin -> scan cells -> scatter
-//   -> count (hit masks + pairs per point) -> scan rows -> [host: totals]
-//   -> emit.
+//   -> unsorted lists: pairs (decide + emit in one traversal; output ranges
+//      are claimed with an atomic cursor)
+//   -> sorted lists: count (hit masks + pairs per point) -> scan rows
+//      -> [host: totals] -> emit (one row per point, in index order).
 //
-// The pair set is decided ONCE, in the count pass, with the reference's exact
-// fp64 arithmetic wherever an fp32 screen cannot decide; the emit pass only
-// walks the stored hit bits, so the two passes can not disagree.
+// Every candidate is decided ONCE, with the reference's exact fp64 arithmetic
+// wherever an fp32 screen cannot decide; in the two-pass path the emit pass
+// only walks the stored hit bits, so the passes can not disagree.
 #include "kernels.cuh"
 
 #include <cfloat>
@@ -102,6 +104,7 @@ __global__ void header_init_kernel(DeviceHeader* header, const double* box, cons
         header->first_bad = NO_BAD_POINT;
         header->total_pairs = 0;
         header->mask_cursor = 0;
+        header->pair_cursor = 0;
         header->status = 0;
     }
 }
@@ -1014,6 +1017,431 @@ __global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
     }
 }
 
+// ---------------------------------------------------------------------------
+// fused pass (unsorted lists): decide and emit in one traversal
+//
+// Unsorted lists may come in any order, so a block of pairs does not need a
+// position computed by a scan: it claims its output range with one atomicAdd
+// on a global cursor once it knows how many pairs it holds. That removes the
+// hit masks in global memory, the scan and the second traversal.
+//
+// Half-shell stencil: a unit only looks at the cells "above" its own (rows
+// with oz > 0, or oz == 0 and oy > 0, and in its own row the cells at or after
+// each home cell), so every unordered pair of images is evaluated once. A
+// full list writes (i, j, S, d, v) and (j, i, -S, d, -v); a half list writes
+// whichever of the two the reference keeps (i < j, or its rule on S when
+// i == j; vesin/src/cpu_cell_list.cpp:101-133). -v is bit-identical to what
+// the reference computes for the reversed pair: IEEE subtraction, product and
+// sum are odd functions under round-to-nearest.
+//
+// When the claimed range does not fit the output arrays the block skips its
+// stores but the cursor keeps counting: the host then grows the arrays to the
+// exact total and runs the pass again.
+// ---------------------------------------------------------------------------
+
+constexpr int FUSED_BATCH = 512;
+constexpr int FUSED_WORDS = FUSED_BATCH / 32;
+constexpr int FUSED_LIST = 2048;
+constexpr int FUSED_TASKS = (TILE_POINTS * FUSED_WORDS + CTA_THREADS - 1) / CTA_THREADS;
+
+struct FusedShared {
+    SegmentTable table;
+    float4 near32[FUSED_BATCH];  // x, y, z relative to the unit centre, and their squared norm
+    double x[FUSED_BATCH];       // original positions of the candidates
+    double y[FUSED_BATCH];
+    double z[FUSED_BATCH];
+    int j[FUSED_BATCH];
+    int s[3][FUSED_BATCH];       // q - wrap shift of the candidate
+    double home_pos[3][TILE_POINTS];
+    int home_shift[3][TILE_POINTS];
+    int home_index[TILE_POINTS];
+    unsigned mask[FUSED_WORDS * TILE_POINTS]; // [word][lane]
+    unsigned list[FUSED_LIST];                // (home lane << 16) | slot in batch
+    int shift_out[CTA_WARPS][96];
+    double vector_out[CTA_WARPS][96];
+    unsigned long long claim;
+    int home_row_slots;
+};
+
+/// Segments of the half-shell stencil of a unit. Order: the unit's own row
+/// first (its own cells, then the n_search[0] cells after them), then the rows
+/// above. Returns the slots of the group; ends with a __syncthreads().
+__device__ __forceinline__ int setup_half_segments(const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int group, FusedShared& sh) {
+    SegmentTable& table = sh.table;
+    const int t = threadIdx.x;
+    const int own_row = unit.cells + plan.n_search[0];
+    const int row_width = unit.cells + 2 * plan.n_search[0];
+    const int rows_y = 2 * plan.n_search[1] + 1;
+    int length = 0;
+    if (t < SEG_MAX) {
+        const int global_t = group * SEG_MAX + t;
+        int start = 0;
+        int q0 = 0, q1 = 0, q2 = 0;
+        if (global_t < unit.n_stencil) {
+            int ox, oy, oz;
+            if (global_t < own_row) {
+                ox = global_t;
+                oy = 0;
+                oz = 0;
+            } else {
+                const int rest = global_t - own_row;
+                const int row = rest / row_width;
+                ox = rest % row_width - plan.n_search[0];
+                if (row < plan.n_search[1]) {
+                    oy = row + 1;
+                    oz = 0;
+                } else {
+                    const int upper = row - plan.n_search[1];
+                    oz = 1 + upper / rows_y;
+                    oy = upper % rows_y - plan.n_search[1];
+                }
+            }
+            int nb[3] = {unit.c0 + ox, unit.c1 + oy, unit.c2 + oz};
+            int q[3] = {0, 0, 0};
+            bool valid = true;
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+                if (plan.periodic[k]) {
+                    q[k] = floor_div(nb[k], plan.n_cells[k]);
+                    nb[k] -= q[k] * plan.n_cells[k];
+                } else if (nb[k] < 0 || nb[k] >= plan.n_cells[k]) {
+                    valid = false;
+                }
+            }
+            if (valid) {
+                const int linear = (nb[2] * plan.n_cells[1] + nb[1]) * plan.n_cells[0] + nb[0];
+                start = cell_start[linear];
+                length = cell_start[linear + 1] - start;
+                q0 = q[0];
+                q1 = q[1];
+                q2 = q[2];
+            }
+        }
+        table.start[t] = start;
+        table.q[0][t] = q0;
+        table.q[1][t] = q1;
+        table.q[2][t] = q2;
+    }
+    const int prefix = block_exclusive_scan(length, table.scan_tmp);
+    if (t < SEG_MAX) {
+        table.slot0[t] = prefix;
+    }
+    const int total = table.scan_tmp[CTA_WARPS];
+    if (t == 0) {
+        table.slot0[SEG_MAX] = total;
+    }
+    __syncthreads();
+    if (t == 0) {
+        // slots of this group that belong to the unit's own row
+        int own = 0;
+        if (group == 0) {
+            own = table.slot0[min(own_row, SEG_MAX)];
+        }
+        sh.home_row_slots = own;
+    }
+    __syncthreads();
+    return total;
+}
+
+/// Write `n_valid` consecutive pairs starting at output element `first`:
+/// lane l holds pair l. 12- and 24-byte elements are transposed through
+/// shared memory so that every store instruction covers one contiguous span.
+__device__ __forceinline__ void store_pairs(
+    FusedShared& sh, const PairOutput& out, int warp, int lane, unsigned long long first, int n_valid, unsigned long long a,
+    unsigned long long b, int s0, int s1, int s2, double d, double vx, double vy, double vz
+) {
+    if (lane < n_valid) {
+        reinterpret_cast<ulonglong2*>(out.pairs)[first + lane] = make_ulonglong2(a, b);
+        if (out.distances != nullptr) {
+            out.distances[first + lane] = d;
+        }
+    }
+    if (out.shifts != nullptr) {
+        int* buffer = sh.shift_out[warp];
+        buffer[3 * lane + 0] = s0;
+        buffer[3 * lane + 1] = s1;
+        buffer[3 * lane + 2] = s2;
+        __syncwarp();
+        int32_t* dst = out.shifts + 3 * first;
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            const int w = k * 32 + lane;
+            if (w < 3 * n_valid) {
+                dst[w] = buffer[w];
+            }
+        }
+    }
+    if (out.vectors != nullptr) {
+        double* buffer = sh.vector_out[warp];
+        buffer[3 * lane + 0] = vx;
+        buffer[3 * lane + 1] = vy;
+        buffer[3 * lane + 2] = vz;
+        __syncwarp();
+        double* dst = out.vectors + 3 * first;
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            const int w = k * 32 + lane;
+            if (w < 3 * n_valid) {
+                dst[w] = buffer[w];
+            }
+        }
+    }
+    __syncwarp();
+}
+
+template <bool FULL>
+__global__ void __launch_bounds__(CTA_THREADS) pairs_kernel(
+    const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
+    DeviceHeader* header
+) {
+    extern __shared__ __align__(16) unsigned char fused_smem[];
+    FusedShared& sh = *reinterpret_cast<FusedShared*>(fused_smem);
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const float cutoff2_lo = plan.cutoff2_lo;
+    const float cutoff2_hi = plan.cutoff2_hi;
+
+    for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
+        Unit unit = unit_of(plan, cell_start, u);
+        if (unit.n_home == 0) {
+            continue;
+        }
+        {
+            const int own_row = unit.cells + plan.n_search[0];
+            const int row_width = unit.cells + 2 * plan.n_search[0];
+            const int rows_above = plan.n_search[1] + plan.n_search[2] * (2 * plan.n_search[1] + 1);
+            unit.n_stencil = own_row + row_width * rows_above;
+        }
+        const int n_groups = (unit.n_stencil + SEG_MAX - 1) / SEG_MAX;
+        const int n_tiles = (unit.n_home + TILE_POINTS - 1) / TILE_POINTS;
+
+        double centre[3];
+#pragma unroll
+        for (int c = 0; c < 3; c++) {
+            centre[c] = plan.origin[c] + (unit.c0 + 0.5 * unit.cells) * plan.cell_vec[0][c] + (unit.c1 + 0.5) * plan.cell_vec[1][c] +
+                        (unit.c2 + 0.5) * plan.cell_vec[2][c];
+        }
+
+        for (int g = 0; g < n_groups; g++) {
+            const int group_total = setup_half_segments(plan, cell_start, unit, g, sh);
+            const int home_row_slots = sh.home_row_slots;
+            for (int batch0 = 0; batch0 < group_total; batch0 += FUSED_BATCH) {
+                const int batch_slots = min(FUSED_BATCH, group_total - batch0);
+                const int batch_words = (batch_slots + 31) >> 5;
+
+                // ---- stage the candidates: warps take segments, lanes take points ----
+                for (int t = warp; t < SEG_MAX; t += CTA_WARPS) {
+                    const int seg_slot0 = sh.table.slot0[t];
+                    const int seg_len = sh.table.slot0[t + 1] - seg_slot0;
+                    const int first = max(seg_slot0, batch0) - seg_slot0;
+                    const int last = min(seg_slot0 + seg_len, batch0 + batch_slots) - seg_slot0;
+                    if (first >= last) {
+                        continue;
+                    }
+                    const int q0 = sh.table.q[0][t], q1 = sh.table.q[1][t], q2 = sh.table.q[2][t];
+                    for (int o = first + lane; o < last; o += 32) {
+                        const size_t p = static_cast<size_t>(sh.table.start[t]) + o;
+                        const int s = seg_slot0 + o - batch0;
+                        const double px = sorted.pos[3 * p + 0];
+                        const double py = sorted.pos[3 * p + 1];
+                        const double pz = sorted.pos[3 * p + 2];
+                        const int r0 = q0 - sorted.shift[3 * p + 0];
+                        const int r1 = q1 - sorted.shift[3 * p + 1];
+                        const int r2 = q2 - sorted.shift[3 * p + 2];
+                        sh.x[s] = px;
+                        sh.y[s] = py;
+                        sh.z[s] = pz;
+                        sh.j[s] = sorted.index[p];
+                        sh.s[0][s] = r0;
+                        sh.s[1][s] = r1;
+                        sh.s[2][s] = r2;
+                        const float fx = static_cast<float>(px + (r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0]) - centre[0]);
+                        const float fy = static_cast<float>(py + (r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1]) - centre[1]);
+                        const float fz = static_cast<float>(pz + (r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2]) - centre[2]);
+                        sh.near32[s] = make_float4(fx, fy, fz, fx * fx + fy * fy + fz * fz);
+                    }
+                }
+                for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
+                    sh.near32[s] = make_float4(0.0f, 0.0f, 0.0f, __int_as_float(0x7f800000)); // never a hit
+                }
+
+                for (int tile = 0; tile < n_tiles; tile++) {
+                    __syncthreads(); // staging done; previous tile done with mask / list / home
+                    const int il = tile * TILE_POINTS + lane;
+                    const bool valid = il < unit.n_home;
+                    const size_t pi = static_cast<size_t>(unit.begin) + (valid ? il : 0);
+                    const double rix = sorted.pos[3 * pi + 0];
+                    const double riy = sorted.pos[3 * pi + 1];
+                    const double riz = sorted.pos[3 * pi + 2];
+                    const int si0 = sorted.shift[3 * pi + 0];
+                    const int si1 = sorted.shift[3 * pi + 1];
+                    const int si2 = sorted.shift[3 * pi + 2];
+                    if (warp == 0) {
+                        sh.home_index[lane] = sorted.index[pi];
+                        sh.home_pos[0][lane] = rix;
+                        sh.home_pos[1][lane] = riy;
+                        sh.home_pos[2][lane] = riz;
+                        sh.home_shift[0][lane] = si0;
+                        sh.home_shift[1][lane] = si1;
+                        sh.home_shift[2][lane] = si2;
+                    }
+                    // d2 = |c|^2 + (|i|^2 - 2 c.i): one add and three fused multiply-adds per candidate.
+                    // Lanes without a point carry NaN: every comparison fails.
+                    const float nan = __int_as_float(0x7fc00000);
+                    const float xi = valid ? static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - centre[0]) : nan;
+                    const float yi = valid ? static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - centre[1]) : nan;
+                    const float zi = valid ? static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - centre[2]) : nan;
+                    const float ax = -2.0f * xi;
+                    const float ay = -2.0f * yi;
+                    const float az = -2.0f * zi;
+                    const float an = xi * xi + yi * yi + zi * zi;
+
+                    for (int w = warp; w < batch_words; w += CTA_WARPS) {
+                        unsigned inside = 0; // surely inside the cutoff
+                        unsigned near = 0;   // inside, or too close to the cutoff for fp32
+                        const float4* candidates = sh.near32 + w * 32;
+#pragma unroll
+                        for (int b = 0; b < 32; b++) {
+                            const float4 cand = candidates[b]; // broadcast
+                            const float d2 = fmaf(cand.x, ax, fmaf(cand.y, ay, fmaf(cand.z, az, cand.w + an)));
+                            if (d2 < cutoff2_lo) {
+                                inside |= 1u << b;
+                            }
+                            if (d2 <= cutoff2_hi) {
+                                near |= 1u << b;
+                            }
+                        }
+                        // half shell inside the unit's own row: only slots after the point's own
+                        unsigned keep = 0xffffffffu;
+                        const int word_slot = batch0 + w * 32;
+                        if (word_slot < home_row_slots) {
+                            const int own = il - word_slot; // bit of the point itself in this word
+                            const unsigned after = (own < 0) ? 0xffffffffu : ((own >= 31) ? 0u : (0xffffffffu << (own + 1)));
+                            const int row_bits = home_row_slots - word_slot; // bits of this word inside the row
+                            const unsigned in_row = (row_bits >= 32) ? 0xffffffffu : ((1u << row_bits) - 1u);
+                            keep = after | ~in_row;
+                        }
+                        inside &= keep;
+                        unsigned band = near & keep & ~inside;
+                        while (band != 0) {
+                            // the exact fp64 predicate of the reference decides
+                            const int b = __ffs(band) - 1;
+                            band &= band - 1;
+                            const int s = w * 32 + b;
+                            double vx, vy, vz;
+                            const double d2_exact = exact_pair(
+                                plan, rix, riy, riz, sh.x[s], sh.y[s], sh.z[s], sh.s[0][s] + si0, sh.s[1][s] + si1, sh.s[2][s] + si2, vx, vy, vz
+                            );
+                            if (d2_exact < plan.cutoff2) {
+                                inside |= 1u << b;
+                            }
+                        }
+                        sh.mask[w * TILE_POINTS + lane] = inside;
+                    }
+                    __syncthreads();
+
+                    // ---- compact the hit bits: tasks = words in [word][lane] order ----
+                    const int n_tasks = TILE_POINTS * batch_words;
+                    const int task0 = threadIdx.x * FUSED_TASKS;
+                    unsigned task_word[FUSED_TASKS];
+                    int my_hits = 0;
+#pragma unroll
+                    for (int k = 0; k < FUSED_TASKS; k++) {
+                        const int task = task0 + k;
+                        task_word[k] = (task < n_tasks) ? sh.mask[task] : 0u;
+                        my_hits += __popc(task_word[k]);
+                    }
+                    const int my_first = block_exclusive_scan(my_hits, sh.table.scan_tmp);
+                    const int total_hits = sh.table.scan_tmp[CTA_WARPS];
+                    if (total_hits == 0) {
+                        continue;
+                    }
+                    if (threadIdx.x == 0) {
+                        // claim the output range of this block of pairs
+                        const unsigned long long wanted = static_cast<unsigned long long>(total_hits) * (FULL ? 2 : 1);
+                        const unsigned long long first = atomicAdd(&header->pair_cursor, wanted);
+                        sh.claim = (first + wanted <= capacity) ? first : ~0ull;
+                    }
+                    __syncthreads();
+                    const unsigned long long claim = sh.claim;
+                    if (claim == ~0ull) {
+                        continue; // counted, not written: the host will grow the arrays
+                    }
+
+                    for (int round0 = 0; round0 < total_hits; round0 += FUSED_LIST) {
+                        if (round0 != 0) {
+                            __syncthreads(); // previous round consumed
+                        }
+                        {
+                            int position = my_first - round0;
+#pragma unroll
+                            for (int k = 0; k < FUSED_TASKS; k++) {
+                                const int task = task0 + k;
+                                unsigned word = task_word[k];
+                                // task = word index * 32 + home lane
+                                const unsigned code = (static_cast<unsigned>(task & 31) << 16) | (static_cast<unsigned>(task >> 5) << 5);
+                                while (word != 0) {
+                                    const int b = __ffs(word) - 1;
+                                    word &= word - 1;
+                                    if (position >= 0 && position < FUSED_LIST) {
+                                        sh.list[position] = code | b;
+                                    }
+                                    position++;
+                                }
+                            }
+                        }
+                        __syncthreads();
+
+                        const int in_round = min(FUSED_LIST, total_hits - round0);
+                        for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
+                            const int n_valid = min(32, in_round - chunk0);
+                            double vx = 0, vy = 0, vz = 0, d = 0;
+                            int s0 = 0, s1 = 0, s2 = 0;
+                            unsigned long long index_i = 0, index_j = 0;
+                            if (lane < n_valid) {
+                                const unsigned entry = sh.list[chunk0 + lane];
+                                const int h = entry >> 16;
+                                const int s = entry & 0xffff;
+                                s0 = sh.s[0][s] + sh.home_shift[0][h];
+                                s1 = sh.s[1][s] + sh.home_shift[1][h];
+                                s2 = sh.s[2][s] + sh.home_shift[2][h];
+                                const double d2 = exact_pair(
+                                    plan, sh.home_pos[0][h], sh.home_pos[1][h], sh.home_pos[2][h], sh.x[s], sh.y[s], sh.z[s], s0, s1, s2, vx, vy, vz
+                                );
+                                d = __dsqrt_rn(d2);
+                                index_i = static_cast<unsigned long long>(sh.home_index[h]);
+                                index_j = static_cast<unsigned long long>(sh.j[s]);
+                            }
+                            const unsigned long long first = claim + round0 + chunk0;
+                            if (FULL) {
+                                store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
+                                store_pairs(sh, out, warp, lane, first + total_hits, n_valid, index_j, index_i, -s0, -s1, -s2, d, -vx, -vy, -vz);
+                            } else {
+                                // the orientation the reference's half list keeps
+                                const bool forward = (index_i < index_j) || (index_i == index_j && half_rule(s0, s1, s2));
+                                if (!forward) {
+                                    const unsigned long long swap = index_i;
+                                    index_i = index_j;
+                                    index_j = swap;
+                                    s0 = -s0;
+                                    s1 = -s1;
+                                    s2 = -s2;
+                                    vx = -vx;
+                                    vy = -vy;
+                                    vz = -vz;
+                                }
+                                store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
+                            }
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+        }
+    }
+}
+
 int pair_grid(int n_units, int per_sm) {
     int device = 0;
     int sms = 148;
@@ -1033,6 +1461,8 @@ int pair_grid(int n_units, int per_sm) {
 void configure_kernels() {
     cudaFuncSetAttribute(emit_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
     cudaFuncSetAttribute(emit_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
+    cudaFuncSetAttribute(pairs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
+    cudaFuncSetAttribute(pairs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
 }
 
 void launch_header_init(DeviceHeader* header, const double* box, const bool* periodic, cudaStream_t stream) {
@@ -1115,6 +1545,18 @@ void launch_emit(
         emit_kernel<false><<<grid, CTA_THREADS, sizeof(EmitShared), stream>>>(
             plan, cell_start, sorted, masks, unit_mask_base, unit_words, unit_start, row_start, row_fill, out
         );
+    }
+}
+
+void launch_pairs(
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
+    DeviceHeader* header, cudaStream_t stream
+) {
+    int grid = pair_grid(plan.n_units, 16);
+    if (plan.full) {
+        pairs_kernel<true><<<grid, CTA_THREADS, sizeof(FusedShared), stream>>>(plan, cell_start, sorted, out, capacity, header);
+    } else {
+        pairs_kernel<false><<<grid, CTA_THREADS, sizeof(FusedShared), stream>>>(plan, cell_start, sorted, out, capacity, header);
     }
 }
 

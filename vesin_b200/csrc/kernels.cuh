@@ -22,6 +22,7 @@ struct DeviceHeader {
     unsigned long long first_bad;    // smallest index of a point with a non-finite coordinate
     unsigned long long total_pairs;  // written by the scan over per-point pair counts
     unsigned long long mask_cursor;  // words of hit-mask storage claimed by the count pass
+    unsigned long long pair_cursor;  // output elements claimed by the fused pass (= its pair total)
     unsigned int status;             // sticky error bits, see STATUS_*
     unsigned int pad;
     double box[9];                   // copy of the caller's box
@@ -97,6 +98,15 @@ void launch_emit(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks, const unsigned long long* unit_mask_base,
     const uint32_t* unit_words, const unsigned long long* unit_start, const unsigned long long* row_start, uint32_t* row_fill,
     PairOutput out, cudaStream_t stream
+);
+
+/// Fused pass for unsorted lists: decides every candidate of the half-shell
+/// stencil once and writes the pairs into ranges claimed from
+/// header->pair_cursor. Blocks whose range would pass `capacity` (in pairs)
+/// only count.
+void launch_pairs(
+    const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
+    DeviceHeader* header, cudaStream_t stream
 );
 
 /// One-time per-device kernel attribute setup (shared-memory opt-in).

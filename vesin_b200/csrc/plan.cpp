@@ -244,10 +244,15 @@ GridPlan make_plan(
     const double eps = 5.9604644775390625e-08; // 2^-24
     double c = cutoff * 1.01;
     double band = 4.0 * eps * (2.0 * std::sqrt(3.0) * c * (2.0 * reach + c) + 3.0 * c * c);
+    // The fused pass evaluates d2 as |c|^2 + |i|^2 - 2 c.i: seven roundings on
+    // terms bounded by (2 M)^2.
+    band += 40.0 * eps * reach * reach;
     band += 4.0 * eps * plan.cutoff2; // rounding of the bounds themselves
     double lo = plan.cutoff2 - band;
     double hi = plan.cutoff2 + band;
-    plan.cutoff2_lo = (lo > 0.0) ? std::nextafter(static_cast<float>(lo), 0.0f) : 0.0f;
+    // "surely inside" only exists when the band is narrower than the cutoff;
+    // the expanded form of d2 can come out negative, so 0 is not a safe floor
+    plan.cutoff2_lo = (lo > 0.0) ? std::nextafter(static_cast<float>(lo), 0.0f) : -std::numeric_limits<float>::infinity();
     float hi_f = static_cast<float>(hi);
     plan.cutoff2_hi = std::isfinite(hi_f) ? std::nextafter(hi_f, std::numeric_limits<float>::infinity())
                                           : std::numeric_limits<float>::max();
