@@ -36,6 +36,52 @@ VESIN_API void vesin_b200_set_profiling(int enabled);
  * made with this list. */
 VESIN_API int vesin_b200_stage_times(const struct VesinNeighborList* neighbors, double* stage_ms);
 
+/* Largest system vesin_b200_neighbors_no_alloc accepts. */
+#define VESIN_B200_NO_ALLOC_MAX_POINTS 32768
+
+/*
+ * No counterpart in the reference: a list build that allocates nothing.
+ *
+ * For callers that must not call cudaMalloc when they need a list: a step
+ * function that runs while a CUDA graph is captured or replayed in the same
+ * process, an application that handed all device memory to its own pool, a
+ * loop with a hard latency bound. vesin_neighbors allocates whenever a system
+ * outgrows its workspace; this function never does. The caller passes the
+ * inputs AND the output arrays (device memory on `device_id`, `capacity` pairs
+ * each; shifts / distances / vectors may be NULL to skip them); the scratch of
+ * the kernels is a fixed array of about 2.3 MB that every GPU holds from
+ * library load to process exit. Hence:
+ *   - at most VESIN_B200_NO_ALLOC_MAX_POINTS points, larger systems get an error;
+ *   - the list is unsorted, same pair set as vesin_neighbors;
+ *   - when the list has more than `capacity` pairs the call fails, `*length`
+ *     holds the number needed and the arrays hold nothing usable;
+ *   - all calls share the scratch array (what must be zero is cleared at the
+ *     start of each call); calls are serialised per device by a host lock and
+ *     run on the legacy default stream; the function returns when the list is
+ *     complete. Work that overlapped on the GPU with another user of the same
+ *     array would race: there is none inside one process;
+ *   - the FIRST call on a device looks up the array's device address and sets
+ *     kernel attributes: make it before any stream capture starts.
+ * Returns 0, or 1 with *error_message set (valid until this thread's next
+ * failing call).
+ */
+VESIN_API int vesin_b200_neighbors_no_alloc(
+    const double (*points)[3],
+    size_t n_points,
+    const double box[3][3],
+    const bool periodic[3],
+    int device_id,
+    double cutoff,
+    bool full,
+    size_t capacity,
+    size_t (*pairs)[2],
+    int32_t (*shifts)[3],
+    double* distances,
+    double (*vectors)[3],
+    size_t* length,
+    const char** error_message
+);
+
 /* No counterpart in the reference. Version string of this library. */
 VESIN_API const char* vesin_b200_version(void);
 

@@ -1,0 +1,100 @@
+"""GPU test of the list build that allocates nothing
+(vesin_b200_neighbors_no_alloc, include/vesin_b200.h).
+
+That entry point exists for callers that may not call cudaMalloc when they
+need a neighbor list (a step running next to a CUDA-graph capture, an
+application that owns all device memory through its own pool, a loop with a
+hard latency bound): the caller brings the output arrays and the kernels work
+in a fixed scratch array inside the library. The test calls it through the C
+ABI and checks the result against vesin_neighbors on the same inputs: indices
+and shifts bit for bit after canonical sorting, distances and vectors within
+the 1e-12 relative tolerance of the other fp64 tests. Two calls are made in a
+row on different systems, the second smaller than the first, so that data left
+in the shared scratch by the first call would show up as wrong pairs.
+
+This file sorts last on purpose: a run that stops at the first failure has
+then already run every other test.
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from vesin_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+RTOL_FP64 = 1e-12
+
+
+def _existing_entry_point(torch, points, box, periodic, cutoff, full):
+    from gpu_utils import gpu_compute
+
+    return gpu_compute(points, box, periodic, cutoff, full, "ijSdD")
+
+
+def _no_alloc(torch, lib, points, box, periodic, cutoff, full, capacity):
+    from vesin_b200._c_api import get_library
+
+    lib = get_library()
+    device = torch.device("cuda", 0)
+    d_points = torch.tensor(np.asarray(points, dtype=np.float64).reshape(-1, 3), device=device)
+    d_box = torch.tensor(np.asarray(box, dtype=np.float64), device=device)
+    d_periodic = torch.tensor(np.asarray(periodic, dtype=bool), device=device)
+    # the caller owns the outputs
+    pairs = torch.full((capacity, 2), -1, dtype=torch.int64, device=device)
+    shifts = torch.full((capacity, 3), 99, dtype=torch.int32, device=device)
+    distances = torch.full((capacity,), -1.0, dtype=torch.float64, device=device)
+    vectors = torch.full((capacity, 3), -1.0, dtype=torch.float64, device=device)
+    torch.cuda.synchronize()
+    length = ctypes.c_size_t(0)
+    error = ctypes.c_char_p()
+    status = lib.vesin_b200_neighbors_no_alloc(
+        d_points.data_ptr(), d_points.shape[0], d_box.data_ptr(), d_periodic.data_ptr(), 0, float(cutoff), bool(full), capacity,
+        pairs.data_ptr(), shifts.data_ptr(), distances.data_ptr(), vectors.data_ptr(), ctypes.byref(length), ctypes.byref(error),
+    )
+    message = error.value.decode() if error.value else None
+    n = min(length.value, capacity)
+    result = {
+        "i": pairs[:n, 0].cpu().numpy(),
+        "j": pairs[:n, 1].cpu().numpy(),
+        "S": shifts[:n].cpu().numpy(),
+        "d": distances[:n].cpu().numpy(),
+        "D": vectors[:n].cpu().numpy(),
+    }
+    return status, message, length.value, result
+
+
+def test_two_calls_in_a_row_match_vesin_neighbors():
+    import torch
+
+    assert torch.cuda.is_available()
+    calls = [
+        (W.diamond(6, seed=17), 5.0, True),      # 1728 points, full list
+        (W.small_triclinic(48, seed=9), 7.5, False),  # smaller system, many images, half list
+    ]
+    for (points, box, periodic), cutoff, full in calls:
+        expected = _existing_entry_point(torch, points, box, periodic, cutoff, full)
+        capacity = len(expected["i"]) + 100
+        status, message, length, got = _no_alloc(torch, None, points, box, periodic, cutoff, full, capacity)
+        assert status == 0, message
+        assert length == len(expected["i"])
+        O.assert_same(got, expected, RTOL_FP64, "no-alloc build against vesin_neighbors")
+
+
+def test_limits_are_reported():
+    import torch
+
+    points, box, periodic = W.diamond(3, seed=1)
+    status, message, length, _ = _no_alloc(torch, None, points, box, periodic, 5.0, True, 10)
+    assert status == 1 and "output arrays hold 10" in message
+    expected = _existing_entry_point(torch, points, box, periodic, 5.0, True)
+    assert length == len(expected["i"])  # the number of pairs needed is still reported
+
+    from vesin_b200._c_api import NO_ALLOC_MAX_POINTS
+
+    too_many = np.zeros((NO_ALLOC_MAX_POINTS + 1, 3))
+    status, message, _, _ = _no_alloc(torch, None, too_many, np.eye(3) * 10, [True] * 3, 1.0, True, 10)
+    assert status == 1 and f"at most {NO_ALLOC_MAX_POINTS} points" in message

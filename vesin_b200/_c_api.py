@@ -58,7 +58,9 @@ EXPORTED_SYMBOLS = (
     "vesin_b200_set_profiling",
     "vesin_b200_stage_times",
     "vesin_b200_version",
+    "vesin_b200_neighbors_no_alloc",
 )
+NO_ALLOC_MAX_POINTS = 32768
 
 
 def build_library(verbose=False):
@@ -101,6 +103,23 @@ def get_library():
     lib.vesin_b200_set_profiling.argtypes = [ctypes.c_int]
     lib.vesin_b200_stage_times.restype = ctypes.c_int
     lib.vesin_b200_stage_times.argtypes = [ctypes.POINTER(VesinNeighborList), ctypes.POINTER(ctypes.c_double)]
+    lib.vesin_b200_neighbors_no_alloc.restype = ctypes.c_int
+    lib.vesin_b200_neighbors_no_alloc.argtypes = [
+        ctypes.c_void_p,  # points
+        ctypes.c_size_t,
+        ctypes.c_void_p,  # box
+        ctypes.c_void_p,  # periodic
+        ctypes.c_int,  # device_id
+        ctypes.c_double,  # cutoff
+        ctypes.c_bool,  # full
+        ctypes.c_size_t,  # capacity
+        ctypes.c_void_p,  # pairs
+        ctypes.c_void_p,  # shifts
+        ctypes.c_void_p,  # distances
+        ctypes.c_void_p,  # vectors
+        ctypes.POINTER(ctypes.c_size_t),
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
     lib.vesin_b200_version.restype = ctypes.c_char_p
     lib.vesin_b200_version.argtypes = []
     _LIBRARY = lib
