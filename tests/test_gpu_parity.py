@@ -146,3 +146,47 @@ def test_errors():
     # a zero box is fine when nothing is periodic
     res = vesin_b200.NeighborList(cutoff=1.0, full_list=True).compute(points, torch.zeros_like(box), False, "ij")
     assert len(res[0]) == 2
+
+
+def test_reused_list_follows_changing_inputs():
+    """A re-used list starts every build from the plan of the previous one; a
+    kernel checks box, periodicity and extent, and the build is redone when
+    they changed. Every step must give the oracle's list."""
+    import torch
+
+    import vesin_b200
+
+    rng = np.random.default_rng(77)
+    points, box, periodic = W.diamond(4, seed=31)
+    calculator = vesin_b200.NeighborList(cutoff=4.0, full_list=True)
+    steps = [
+        (points, box, periodic),                                    # first build: plans from a read-back
+        (points + rng.normal(0, 0.02, points.shape), box, periodic),  # same box: speculative plan accepted
+        (points, box * 1.07, periodic),                             # box changed
+        (points, box * 1.07, np.array([True, False, True])),        # periodicity changed
+        (points * 1.6, box * 1.07, np.array([True, False, True])),  # points left the non-periodic window
+        (points * 1.6, box * 1.07, np.array([True, False, True])),  # accepted again
+        (points @ W.random_rotation(5).T, box @ W.random_rotation(5).T, periodic),
+    ]
+    for step, (p, b, per) in enumerate(steps):
+        for _ in range(2):
+            got = gpu_compute(p, b, per, 4.0, True, "ijSdD", calculator=calculator)
+            expected = O.restated_neighbors(p, b, per, 4.0, True, "ijSdD")
+            O.assert_same(got, expected, RTOL_FP64, f"step {step}")
+
+    # errors are still raised when the plan is speculative
+    device = torch.device("cuda", 0)
+    bad = torch.tensor(points, device=device)
+    bad[7, 1] = float("nan")
+    with pytest.raises(RuntimeError, match="point 7 has non-finite coordinate along axis 1: nan"):
+        calculator.compute(bad, torch.tensor(box * 1.07, device=device), torch.tensor(periodic, device=device), "ij")
+    with pytest.raises(RuntimeError, match="the box matrix is not invertible"):
+        calculator.compute(torch.tensor(points, device=device), torch.zeros((3, 3), dtype=torch.float64, device=device), True, "ij")
+    got = gpu_compute(points, box, periodic, 4.0, True, "ijSdD", calculator=calculator)
+    O.assert_same(got, O.restated_neighbors(points, box, periodic, 4.0, True, "ijSdD"), RTOL_FP64, "after errors")
+
+    # the sorted path speculates too
+    calculator = vesin_b200.NeighborList(cutoff=4.0, full_list=False, sorted=True)
+    for p, b, per in steps[:4]:
+        got = gpu_compute(p, b, per, 4.0, False, "ijSdD", calculator=calculator)
+        O.assert_same(got, O.restated_neighbors(p, b, per, 4.0, False, "ijSdD"), RTOL_FP64, "sorted")

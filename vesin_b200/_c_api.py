@@ -7,7 +7,9 @@ import os
 import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIBRARY_PATH = os.path.join(HERE, "lib", "libvesin.so")
+# VESIN_B200_LIBRARY points at another build of the same library (e.g. one made
+# with extra compiler flags); the default is the in-tree build.
+LIBRARY_PATH = os.environ.get("VESIN_B200_LIBRARY", os.path.join(HERE, "lib", "libvesin.so"))
 
 VesinUnknownDevice = 0
 VesinCPU = 1

@@ -102,6 +102,19 @@ struct Workspace {
     // output arrays (capacity in pairs); kept allocated when not requested
     DeviceBuffer out_pairs, out_shifts, out_distances, out_vectors;
 
+    // What the last build on this list saw, and the plan made from it: the
+    // next build starts from this plan without waiting for a read-back.
+    struct PlanCache {
+        bool valid = false;
+        double box[9] = {};
+        bool periodic[3] = {};
+        size_t n_points = 0;
+        double cutoff = 0.0;
+        bool full = false;
+        bool sorted = false;
+        GridPlan plan{};
+    } cache;
+
     cudaEvent_t events[2 * N_STAGES] = {};
     bool events_created = false;
     bool timed = false;
@@ -342,143 +355,271 @@ void neighbors(
     cudaStream_t stream = ws.stream;
     const auto* flat_points = reinterpret_cast<const double*>(points);
 
-    // ---- box, periodicity, bounds and finite check: one read-back ----
-    timer.begin(VesinB200StageBounds);
-    launch_header_init(ws.d_header, reinterpret_cast<const double*>(box), periodic, stream);
-    launch_bounds(flat_points, n_points, ws.d_header, stream);
-    timer.end(VesinB200StageBounds);
-    VB200_CUDA(cudaGetLastError());
-    read_header(ws);
-    timer.collect(VesinB200StageBounds);
     const DeviceHeader& header = *ws.h_header;
+    const size_t max_cells = size_t(1) << 27;
 
-    if (header.first_bad != NO_BAD_POINT) {
+    const auto bad_point_error = [&]() {
         // same text as the CPU path (vesin/src/types.hpp:163-169)
         double bad[3];
         VB200_CUDA(cudaMemcpy(bad, flat_points + 3 * header.first_bad, sizeof(bad), cudaMemcpyDeviceToHost));
         for (int axis = 0; axis < 3; axis++) {
             if (!std::isfinite(bad[axis])) {
-                throw std::runtime_error(
-                    "point " + std::to_string(header.first_bad) + " has non-finite coordinate along axis " +
-                    std::to_string(axis) + ": " + std::to_string(bad[axis])
+                return std::runtime_error(
+                    "point " + std::to_string(header.first_bad) + " has non-finite coordinate along axis " + std::to_string(axis) +
+                    ": " + std::to_string(bad[axis])
                 );
             }
         }
-    }
+        return std::runtime_error("point " + std::to_string(header.first_bad) + " has a non-finite coordinate");
+    };
+    const auto pair_limit_error = [&]() {
+        return std::runtime_error(
+            "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_points * pair_limit_per_point) +
+            " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_points) + "). " +
+            "Consider reducing the cutoff distance, or explicitly setting " +
+            "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable."
+        );
+    };
+    // Plan from the header the host has just read. Errors in the reference's
+    // order: box first (vesin/src/types.hpp:75-78), then the points.
+    const auto plan_from_header = [&]() {
+        auto& cache = ws.cache;
+        cache.valid = false;
+        PointBounds bounds{};
+        for (int c = 0; c < 3; c++) {
+            bool have = n_points != 0 && header.min_key[c] != ~0ull;
+            bounds.min[c] = have ? key_to_double(header.min_key[c]) : 0.0;
+            bounds.max[c] = have ? key_to_double(header.max_key[c]) : 0.0;
+            cache.periodic[c] = header.periodic[c] != 0;
+        }
+        std::memcpy(cache.box, header.box, sizeof(cache.box));
+        cache.plan = make_plan(header.box, cache.periodic, bounds, n_points, options.cutoff, options.full, options.sorted, max_cells);
+        if (header.first_bad != NO_BAD_POINT) {
+            throw bad_point_error();
+        }
+        cache.n_points = n_points;
+        cache.cutoff = options.cutoff;
+        cache.full = options.full;
+        cache.sorted = options.sorted;
+        cache.valid = true;
+    };
 
-    bool host_periodic[3] = {header.periodic[0] != 0, header.periodic[1] != 0, header.periodic[2] != 0};
-    PointBounds bounds{};
-    for (int c = 0; c < 3; c++) {
-        bounds.min[c] = n_points ? key_to_double(header.min_key[c]) : 0.0;
-        bounds.max[c] = n_points ? key_to_double(header.max_key[c]) : 0.0;
-    }
-    const size_t max_cells = size_t(1) << 27;
-    GridPlan plan = make_plan(header.box, host_periodic, bounds, n_points, options.cutoff, options.full, options.sorted, max_cells);
+    // ---- speculation: reuse the plan of the previous build when the request
+    // is the same; a kernel checks that box, periodicity and extent still are ----
+    bool speculative = ws.cache.valid && ws.cache.n_points == n_points && ws.cache.cutoff == options.cutoff &&
+                       ws.cache.full == options.full && ws.cache.sorted == options.sorted &&
+                       options.algorithm != VesinBruteForce; // its legality check wants the box of THIS call
+    bool header_is_fresh = false;
 
-    if (options.algorithm == VesinBruteForce && 2.0 * options.cutoff > min_periodic_face_distance(plan)) {
-        // vesin/src/vesin_cuda.cpp:404-409
-        throw std::runtime_error("Invalid cutoff: too large for box dimensions");
-    }
+    for (int round = 0;; round++) {
+        timer.begin(VesinB200StageBounds);
+        launch_header_init(ws.d_header, reinterpret_cast<const double*>(box), periodic, stream);
+        launch_bounds(flat_points, n_points, ws.d_header, stream);
+        timer.end(VesinB200StageBounds);
+        if (!speculative) {
+            if (!header_is_fresh) {
+                VB200_CUDA(cudaGetLastError());
+                read_header(ws);
+            }
+            plan_from_header();
+        }
+        const GridPlan& plan = ws.cache.plan;
+        launch_validate(ws.d_header, ws.cache.box, ws.cache.periodic, plan, n_points, stream);
 
-    if (n_points == 0) {
-        set_outputs(list, ws, options, 256);
-        list.length = 0;
-        ws.timed = timer.enabled;
-        return;
-    }
+        if (options.algorithm == VesinBruteForce && 2.0 * options.cutoff > min_periodic_face_distance(plan)) {
+            // vesin/src/vesin_cuda.cpp:404-409
+            throw std::runtime_error("Invalid cutoff: too large for box dimensions");
+        }
 
-    // ---- scratch ----
-    const size_t n_cells = static_cast<size_t>(plan.n_cells_total);
-    ws.cell_of.reserve(n_points * sizeof(int32_t));
-    ws.rank.reserve(n_points * sizeof(int32_t));
-    ws.shift.reserve(n_points * 3 * sizeof(int32_t));
-    ws.cell_count.reserve(n_cells * sizeof(int32_t));
-    ws.cell_start.reserve((n_cells + 1) * sizeof(int32_t));
-    ws.sorted_pos.reserve(n_points * 3 * sizeof(double));
-    ws.sorted_index.reserve(n_points * sizeof(int32_t));
-    ws.sorted_shift.reserve(n_points * 3 * sizeof(int32_t));
-    const size_t n_units = static_cast<size_t>(plan.n_units);
-    ws.unit_mask_base.reserve(n_units * sizeof(unsigned long long));
-    ws.unit_words.reserve(n_units * sizeof(uint32_t));
-    ws.unit_count.reserve(n_units * sizeof(unsigned long long));
-    ws.unit_start.reserve((n_units + 1) * sizeof(unsigned long long));
-    if (plan.by_index) {
+        if (n_points == 0) {
+            VB200_CUDA(cudaGetLastError());
+            read_header(ws);
+            if (header.status & STATUS_PLAN_STALE) {
+                speculative = false;
+                header_is_fresh = true;
+                continue;
+            }
+            set_outputs(list, ws, options, 256);
+            list.length = 0;
+            ws.timed = timer.enabled;
+            return;
+        }
+
+        // ---- scratch ----
+        const size_t n_cells = static_cast<size_t>(plan.n_cells_total);
+        const size_t n_units = static_cast<size_t>(plan.n_units);
+        ws.cell_of.reserve(n_points * sizeof(int32_t));
+        ws.rank.reserve(n_points * sizeof(int32_t));
+        ws.shift.reserve(n_points * 3 * sizeof(int32_t));
+        ws.cell_count.reserve(n_cells * sizeof(int32_t));
+        ws.cell_start.reserve((n_cells + 1) * sizeof(int32_t));
+        ws.sorted_pos.reserve(n_points * 3 * sizeof(double));
+        ws.sorted_index.reserve(n_points * sizeof(int32_t));
+        ws.sorted_shift.reserve(n_points * 3 * sizeof(int32_t));
+        ws.scan_tmp.reserve(scan_tmp_bytes(std::max(n_points, n_cells)));
+        SortedPoints sorted{ws.sorted_pos.as<double>(), ws.sorted_index.as<int32_t>(), ws.sorted_shift.as<int32_t>()};
+
+        // ---- cell list ----
+        timer.begin(VesinB200StageBin);
+        VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
+        launch_bin(
+            flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
+            ws.cell_count.as<int32_t>(), ws.d_header, stream
+        );
+        timer.end(VesinB200StageBin);
+        timer.begin(VesinB200StageScanCells);
+        launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
+        timer.end(VesinB200StageScanCells);
+        timer.begin(VesinB200StageScatter);
+        launch_scatter(
+            flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(),
+            sorted, ws.d_header, stream
+        );
+        timer.end(VesinB200StageScatter);
+        const auto collect_front_stages = [&]() {
+            timer.collect(VesinB200StageBounds);
+            timer.collect(VesinB200StageBin);
+            timer.collect(VesinB200StageScanCells);
+            timer.collect(VesinB200StageScatter);
+        };
+        // after a read-back: did the validation kernel accept the plan?
+        const auto plan_was_refused = [&]() {
+            if ((header.status & STATUS_ABORT_MASK) == 0) {
+                return false;
+            }
+            if (!speculative) {
+                // a plan made from this very header can only be refused for a bad point
+                throw bad_point_error();
+            }
+            speculative = false;
+            header_is_fresh = true; // box, periodicity and bounds were just read
+            return true;
+        };
+
+        if (!plan.by_index) {
+            // ---- unsorted list: one fused pass, one read-back. The arrays of
+            // the previous call are tried first; when the pairs do not fit,
+            // the pass has still counted them: grow to the exact total and run
+            // it again (first build on a list, or a system that grew). ----
+            set_outputs(list, ws, options, std::max<size_t>(common_capacity(ws, options), 256));
+            size_t capacity = common_capacity(ws, options);
+            size_t total = 0;
+            bool refused = false;
+            for (int attempt = 0;; attempt++) {
+                PairOutput out{
+                    reinterpret_cast<unsigned long long*>(list.pairs),
+                    reinterpret_cast<int32_t*>(list.shifts),
+                    list.distances,
+                    reinterpret_cast<double*>(list.vectors),
+                };
+                timer.begin(VesinB200StageEmit);
+                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, stream);
+                timer.end(VesinB200StageEmit);
+                VB200_CUDA(cudaGetLastError());
+                read_header(ws);
+                if (attempt == 0) {
+                    collect_front_stages();
+                    if (plan_was_refused()) {
+                        refused = true;
+                        break;
+                    }
+                }
+                timer.collect(VesinB200StageEmit);
+                total = static_cast<size_t>(header.pair_cursor);
+                if (total > n_points * pair_limit_per_point) {
+                    throw pair_limit_error();
+                }
+                if (total <= capacity) {
+                    break;
+                }
+                if (attempt >= 2) {
+                    throw std::runtime_error("internal error: the pair total kept changing between passes");
+                }
+                set_outputs(list, ws, options, total + total / 16 + 256);
+                capacity = common_capacity(ws, options);
+                VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, sizeof(unsigned long long), stream));
+            }
+            if (refused) {
+                continue;
+            }
+            list.length = total;
+            ws.timed = timer.enabled;
+            return;
+        }
+
+        // ---- sorted list: rows in index order need a scan between two passes ----
+        ws.unit_mask_base.reserve(n_units * sizeof(unsigned long long));
+        ws.unit_words.reserve(n_units * sizeof(uint32_t));
+        ws.unit_count.reserve(n_units * sizeof(unsigned long long));
+        ws.unit_start.reserve((n_units + 1) * sizeof(unsigned long long));
         ws.row_count.reserve(n_points * sizeof(uint32_t));
         ws.row_start.reserve((n_points + 1) * sizeof(unsigned long long));
         ws.row_fill.reserve(n_points * sizeof(uint32_t));
-    }
-    ws.scan_tmp.reserve(scan_tmp_bytes(std::max(n_points, n_cells)));
-    {
-        // first guess for the hit-mask storage: uniform density. Every unit
-        // stores (tiles of 32 lanes) x (words per home point).
-        double per_cell = static_cast<double>(n_points) / static_cast<double>(n_cells);
-        double stencil_cells = (plan.pencil + 2.0 * plan.n_search[0]) * (2.0 * plan.n_search[1] + 1.0) * (2.0 * plan.n_search[2] + 1.0);
-        double words = per_cell * stencil_cells / 32.0 + 1.5;
-        double lanes = static_cast<double>(n_units) * 32.0 * std::ceil(per_cell * plan.pencil / 32.0 + 0.35);
-        double guess = 1.2 * words * lanes * sizeof(uint32_t);
-        guess = std::min(guess, 2.0e9);
         if (ws.masks.bytes == 0) {
+            // first guess for the hit-mask storage: uniform density. Every unit
+            // stores (tiles of 32 lanes) x (words per home point).
+            double per_cell = static_cast<double>(n_points) / static_cast<double>(n_cells);
+            double stencil_cells = (plan.pencil + 2.0 * plan.n_search[0]) * (2.0 * plan.n_search[1] + 1.0) * (2.0 * plan.n_search[2] + 1.0);
+            double words = per_cell * stencil_cells / 32.0 + 1.5;
+            double lanes = static_cast<double>(n_units) * 32.0 * std::ceil(per_cell * plan.pencil / 32.0 + 0.35);
+            double guess = std::min(1.2 * words * lanes * sizeof(uint32_t), 2.0e9);
             ws.masks.reserve(static_cast<size_t>(guess) + 1024);
         }
-    }
-    SortedPoints sorted{ws.sorted_pos.as<double>(), ws.sorted_index.as<int32_t>(), ws.sorted_shift.as<int32_t>()};
 
-    // ---- cell list ----
-    timer.begin(VesinB200StageBin);
-    VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
-    launch_bin(flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_count.as<int32_t>(), stream);
-    timer.end(VesinB200StageBin);
-
-    timer.begin(VesinB200StageScanCells);
-    launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
-    timer.end(VesinB200StageScanCells);
-
-    timer.begin(VesinB200StageScatter);
-    launch_scatter(flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), sorted, stream);
-    timer.end(VesinB200StageScatter);
-
-    const auto pair_limit_message = [&](size_t) {
-        return "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_points * pair_limit_per_point) +
-               " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_points) + "). " +
-               "Consider reducing the cutoff distance, or explicitly setting " +
-               "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable.";
-    };
-
-    if (!plan.by_index) {
-        // ---- unsorted list: one fused pass. The arrays of the previous call
-        // (or a density estimate on the first call) are tried first; when the
-        // pairs do not fit, the pass has still counted them: grow to the
-        // exact total and run it again. ----
-        size_t capacity = common_capacity(ws, options);
-        if (capacity == 0) {
-            double estimate = 0.0;
-            if (plan.periodic[0] && plan.periodic[1] && plan.periodic[2]) {
-                double volume = plan.face_dist[0] * plan.face_dist[1] * plan.face_dist[2];
-                // |det H| from the face distances and the row lengths is not
-                // available cheaply for skewed cells: use the inverse's determinant
-                double det_inv = plan.Hinv[0][0] * (plan.Hinv[1][1] * plan.Hinv[2][2] - plan.Hinv[2][1] * plan.Hinv[1][2]) -
-                                 plan.Hinv[0][1] * (plan.Hinv[1][0] * plan.Hinv[2][2] - plan.Hinv[1][2] * plan.Hinv[2][0]) +
-                                 plan.Hinv[0][2] * (plan.Hinv[1][0] * plan.Hinv[2][1] - plan.Hinv[1][1] * plan.Hinv[2][0]);
-                if (std::abs(det_inv) > 0.0) {
-                    volume = 1.0 / std::abs(det_inv);
-                }
-                double density = static_cast<double>(n_points) / volume;
-                estimate = static_cast<double>(n_points) * density * 4.18879 * options.cutoff * options.cutoff * options.cutoff;
-                if (!options.full) {
-                    estimate *= 0.5;
-                }
-                estimate = estimate * 1.1 + 1024.0;
-                if (estimate > static_cast<double>(n_points) * static_cast<double>(pair_limit_per_point) || estimate * 60.0 > 8.0e9) {
-                    estimate = 0.0; // not worth reserving blindly: count first
+        bool refused = false;
+        for (int attempt = 0;; attempt++) {
+            timer.begin(VesinB200StageCount);
+            VB200_CUDA(cudaMemsetAsync(ws.unit_count.ptr, 0, n_units * sizeof(unsigned long long), stream));
+            VB200_CUDA(cudaMemsetAsync(ws.row_count.ptr, 0, n_points * sizeof(uint32_t), stream));
+            launch_count(
+                plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.masks.bytes / sizeof(uint32_t),
+                ws.unit_mask_base.as<unsigned long long>(), ws.unit_words.as<uint32_t>(), ws.unit_count.as<unsigned long long>(),
+                ws.row_count.as<uint32_t>(), ws.d_header, stream
+            );
+            timer.end(VesinB200StageCount);
+            timer.begin(VesinB200StageScanRows);
+            launch_scan_rows(
+                ws.row_count.as<uint32_t>(), ws.row_start.as<unsigned long long>(), n_points, ws.scan_tmp.ptr,
+                &ws.d_header->total_pairs, stream
+            );
+            timer.end(VesinB200StageScanRows);
+            VB200_CUDA(cudaGetLastError());
+            read_header(ws);
+            if (attempt == 0) {
+                collect_front_stages();
+                if (plan_was_refused()) {
+                    refused = true;
+                    break;
                 }
             }
-            capacity = std::max<size_t>(256, static_cast<size_t>(estimate));
+            timer.collect(VesinB200StageCount);
+            timer.collect(VesinB200StageScanRows);
+            if ((header.status & STATUS_MASK_OVERFLOW) == 0) {
+                break;
+            }
+            if (attempt >= 2) {
+                throw std::runtime_error("internal error: hit-mask storage kept overflowing");
+            }
+            // the cursor holds the exact requirement: grow and decide again
+            size_t wanted = static_cast<size_t>(header.mask_cursor) * sizeof(uint32_t);
+            ws.masks.reserve(wanted + wanted / 16 + 1024);
+            size_t offset = offsetof(DeviceHeader, total_pairs);
+            VB200_CUDA(cudaMemsetAsync(reinterpret_cast<char*>(ws.d_header) + offset, 0, offsetof(DeviceHeader, box) - offset, stream));
+        }
+        if (refused) {
+            continue;
+        }
+
+        const size_t total = static_cast<size_t>(header.total_pairs);
+        if (total > n_points * pair_limit_per_point) {
+            throw pair_limit_error();
+        }
+        size_t capacity = std::max<size_t>(total, 256);
+        if (capacity > common_capacity(ws, options) && ws.out_pairs.bytes != 0) {
+            capacity += capacity / 16; // a list that keeps growing gets some headroom
         }
         set_outputs(list, ws, options, capacity);
-        capacity = common_capacity(ws, options);
-
-        size_t total = 0;
-        for (int attempt = 0;; attempt++) {
+        if (total > 0) {
             PairOutput out{
                 reinterpret_cast<unsigned long long*>(list.pairs),
                 reinterpret_cast<int32_t*>(list.shifts),
@@ -486,125 +627,21 @@ void neighbors(
                 reinterpret_cast<double*>(list.vectors),
             };
             timer.begin(VesinB200StageEmit);
-            launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, stream);
+            VB200_CUDA(cudaMemsetAsync(ws.row_fill.ptr, 0, n_points * sizeof(uint32_t), stream));
+            launch_emit(
+                plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.unit_mask_base.as<unsigned long long>(),
+                ws.unit_words.as<uint32_t>(), ws.unit_start.as<unsigned long long>(), ws.row_start.as<unsigned long long>(),
+                ws.row_fill.as<uint32_t>(), out, stream
+            );
             timer.end(VesinB200StageEmit);
             VB200_CUDA(cudaGetLastError());
-            read_header(ws);
-            if (attempt == 0) {
-                timer.collect(VesinB200StageBin);
-                timer.collect(VesinB200StageScanCells);
-                timer.collect(VesinB200StageScatter);
-            }
+            VB200_CUDA(cudaStreamSynchronize(stream));
             timer.collect(VesinB200StageEmit);
-            total = static_cast<size_t>(header.pair_cursor);
-            if (total > n_points * pair_limit_per_point) {
-                throw std::runtime_error(pair_limit_message(total));
-            }
-            if (total <= capacity) {
-                break;
-            }
-            if (attempt >= 2) {
-                throw std::runtime_error("internal error: the pair total kept changing between passes");
-            }
-            set_outputs(list, ws, options, total + total / 16 + 256);
-            capacity = common_capacity(ws, options);
-            VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, sizeof(unsigned long long), stream));
         }
         list.length = total;
         ws.timed = timer.enabled;
         return;
     }
-
-    // ---- pass 1: decide every candidate; pairs per point; totals ----
-    for (int attempt = 0;; attempt++) {
-        timer.begin(VesinB200StageCount);
-        VB200_CUDA(cudaMemsetAsync(ws.unit_count.ptr, 0, n_units * sizeof(unsigned long long), stream));
-        if (plan.by_index) {
-            VB200_CUDA(cudaMemsetAsync(ws.row_count.ptr, 0, n_points * sizeof(uint32_t), stream));
-        }
-        launch_count(
-            plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.masks.bytes / sizeof(uint32_t),
-            ws.unit_mask_base.as<unsigned long long>(), ws.unit_words.as<uint32_t>(), ws.unit_count.as<unsigned long long>(),
-            ws.row_count.as<uint32_t>(), ws.d_header, stream
-        );
-        timer.end(VesinB200StageCount);
-
-        timer.begin(VesinB200StageScanRows);
-        if (plan.by_index) {
-            launch_scan_rows(
-                ws.row_count.as<uint32_t>(), ws.row_start.as<unsigned long long>(), n_points, ws.scan_tmp.ptr,
-                &ws.d_header->total_pairs, stream
-            );
-        } else {
-            launch_scan_units(
-                ws.unit_count.as<unsigned long long>(), ws.unit_start.as<unsigned long long>(), n_units, ws.scan_tmp.ptr,
-                &ws.d_header->total_pairs, stream
-            );
-        }
-        timer.end(VesinB200StageScanRows);
-        VB200_CUDA(cudaGetLastError());
-        read_header(ws);
-        if (attempt == 0) {
-            timer.collect(VesinB200StageBin);
-            timer.collect(VesinB200StageScanCells);
-            timer.collect(VesinB200StageScatter);
-        }
-        timer.collect(VesinB200StageCount);
-        timer.collect(VesinB200StageScanRows);
-
-        if ((header.status & STATUS_MASK_OVERFLOW) == 0) {
-            break;
-        }
-        if (attempt >= 2) {
-            throw std::runtime_error("internal error: hit-mask storage kept overflowing");
-        }
-        // the cursor holds the exact requirement: grow and decide again
-        size_t wanted = static_cast<size_t>(header.mask_cursor) * sizeof(uint32_t);
-        ws.masks.reserve(wanted + wanted / 16 + 1024);
-        size_t offset = offsetof(DeviceHeader, total_pairs);
-        VB200_CUDA(cudaMemsetAsync(reinterpret_cast<char*>(ws.d_header) + offset, 0, offsetof(DeviceHeader, box) - offset, stream));
-    }
-
-    const size_t total = static_cast<size_t>(header.total_pairs);
-    if (total > n_points * pair_limit_per_point) {
-        throw std::runtime_error(
-            "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_points * pair_limit_per_point) +
-            " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_points) + "). " +
-            "Consider reducing the cutoff distance, or explicitly setting " +
-            "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable."
-        );
-    }
-
-    // ---- exactly sized output, then pass 2 ----
-    size_t capacity = std::max<size_t>(total, 256);
-    if (capacity * 2 * sizeof(size_t) > ws.out_pairs.bytes && ws.out_pairs.bytes != 0) {
-        capacity += capacity / 16; // a list that keeps growing gets some headroom
-    }
-    set_outputs(list, ws, options, capacity);
-
-    if (total > 0) {
-        PairOutput out{
-            reinterpret_cast<unsigned long long*>(list.pairs),
-            reinterpret_cast<int32_t*>(list.shifts),
-            list.distances,
-            reinterpret_cast<double*>(list.vectors),
-        };
-        timer.begin(VesinB200StageEmit);
-        if (plan.by_index) {
-            VB200_CUDA(cudaMemsetAsync(ws.row_fill.ptr, 0, n_points * sizeof(uint32_t), stream));
-        }
-        launch_emit(
-            plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.unit_mask_base.as<unsigned long long>(),
-            ws.unit_words.as<uint32_t>(), ws.unit_start.as<unsigned long long>(), ws.row_start.as<unsigned long long>(),
-            ws.row_fill.as<uint32_t>(), out, stream
-        );
-        timer.end(VesinB200StageEmit);
-        VB200_CUDA(cudaGetLastError());
-        VB200_CUDA(cudaStreamSynchronize(stream));
-        timer.collect(VesinB200StageEmit);
-    }
-    list.length = total;
-    ws.timed = timer.enabled;
 }
 
 void free_neighbors(VesinNeighborList& list) {

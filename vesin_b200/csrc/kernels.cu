@@ -172,6 +172,71 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const double* __res
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// validation of a speculative plan
+// The host builds the grid plan from the box, periodicity and bounds it saw at
+// the end of the PREVIOUS build on the same list, and launches the whole build
+// without waiting for a read-back. This kernel compares that assumption with
+// what is in device memory now; when it does not hold it sets
+// STATUS_PLAN_STALE, every later kernel of the build returns at once, and the
+// host plans again from the header it reads back. Replaces the two blocking
+// read-backs of check_box (vesin/src/vesin_cuda.cpp:393-399).
+// ---------------------------------------------------------------------------
+
+struct ExpectedInputs {
+    double box[9];
+    int periodic[3];
+};
+
+__global__ void validate_kernel(DeviceHeader* header, const ExpectedInputs expected, const GridPlan plan, size_t n_points) {
+    if (threadIdx.x != 0) {
+        return;
+    }
+    unsigned status = 0;
+    for (int k = 0; k < 9; k++) {
+        if (__double_as_longlong(header->box[k]) != __double_as_longlong(expected.box[k])) {
+            status |= STATUS_PLAN_STALE;
+        }
+    }
+    for (int k = 0; k < 3; k++) {
+        if ((header->periodic[k] != 0) != (expected.periodic[k] != 0)) {
+            status |= STATUS_PLAN_STALE;
+        }
+    }
+    if (header->first_bad != NO_BAD_POINT) {
+        status |= STATUS_BAD_POINT;
+    } else if (n_points != 0) {
+        // along non-periodic directions the cells only cover a window around
+        // the points the plan was made for: every point must still be inside
+        for (int k = 0; k < 3; k++) {
+            if (plan.periodic[k]) {
+                continue;
+            }
+            double lo = 0.0;
+            double hi = 0.0;
+            for (int c = 0; c < 3; c++) {
+                unsigned long long min_key = header->min_key[c];
+                unsigned long long max_key = header->max_key[c];
+                unsigned long long min_bits = (min_key >> 63) ? (min_key & 0x7fffffffffffffffull) : ~min_key;
+                unsigned long long max_bits = (max_key >> 63) ? (max_key & 0x7fffffffffffffffull) : ~max_key;
+                double u = plan.Hinv[c][k];
+                double a = u * __longlong_as_double(static_cast<long long>(min_bits));
+                double b = u * __longlong_as_double(static_cast<long long>(max_bits));
+                lo += fmin(a, b);
+                hi += fmax(a, b);
+            }
+            double window = plan.n_cells[k] / plan.scale[k];
+            if (!(lo >= plan.t0[k]) || !(hi <= plan.t0[k] + window)) {
+                status |= STATUS_PLAN_STALE;
+            }
+        }
+    }
+    if (status != 0) {
+        atomicOr(&header->status, status);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // bin: wrap + cell + histogram
 // Replaces assign_cell_indices + count_particles_per_cell
@@ -181,8 +246,11 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const double* __res
 
 __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
     const double* __restrict__ points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
-    int32_t* __restrict__ shift, int32_t* __restrict__ cell_count
+    int32_t* __restrict__ shift, int32_t* __restrict__ cell_count, const DeviceHeader* __restrict__ header
 ) {
+    if (header->status & STATUS_ABORT_MASK) {
+        return;
+    }
     size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     bool active = i < n;
     unsigned active_mask = __ballot_sync(FULL_MASK, active);
@@ -371,10 +439,11 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
 
 __global__ void __launch_bounds__(CTA_THREADS) scatter_kernel(
     const double* __restrict__ points, size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank,
-    const int32_t* __restrict__ shift, const int32_t* __restrict__ cell_start, SortedPoints sorted
+    const int32_t* __restrict__ shift, const int32_t* __restrict__ cell_start, SortedPoints sorted,
+    const DeviceHeader* __restrict__ header
 ) {
     size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n) {
+    if (i >= n || (header->status & STATUS_ABORT_MASK)) {
         return;
     }
     size_t p = static_cast<size_t>(cell_start[cell_of[i]]) + rank[i];
@@ -573,7 +642,7 @@ __device__ __forceinline__ int words_of_unit(const GridPlan& plan, const int32_t
 constexpr int COUNT_BATCH = 1024; // candidate slots staged at once
 #define FAR_AWAY __int_as_float(0x7f800000) // +inf: never inside any cutoff
 
-__global__ void __launch_bounds__(CTA_THREADS) count_kernel(
+__global__ void __launch_bounds__(CTA_THREADS, 4) count_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, uint32_t* __restrict__ masks,
     unsigned long long mask_capacity, unsigned long long* __restrict__ unit_mask_base, uint32_t* __restrict__ unit_words,
     unsigned long long* __restrict__ unit_count, uint32_t* __restrict__ row_count, DeviceHeader* header
@@ -585,6 +654,9 @@ __global__ void __launch_bounds__(CTA_THREADS) count_kernel(
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    if (header->status & STATUS_ABORT_MASK) {
+        return;
+    }
 
     for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
         const Unit unit = unit_of(plan, cell_start, u);
@@ -1040,6 +1112,7 @@ __global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
 // ---------------------------------------------------------------------------
 
 constexpr int FUSED_BATCH = 512;
+constexpr int DEFAULT_UNIT_RUN = 4; // neighbouring units handled back to back by one CTA
 constexpr int FUSED_WORDS = FUSED_BATCH / 32;
 constexpr int FUSED_LIST = 2048;
 constexpr int FUSED_TASKS = (TILE_POINTS * FUSED_WORDS + CTA_THREADS - 1) / CTA_THREADS;
@@ -1190,9 +1263,9 @@ __device__ __forceinline__ void store_pairs(
 }
 
 template <bool FULL>
-__global__ void __launch_bounds__(CTA_THREADS) pairs_kernel(
+__global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header
+    DeviceHeader* header, const int UNIT_RUN
 ) {
     extern __shared__ __align__(16) unsigned char fused_smem[];
     FusedShared& sh = *reinterpret_cast<FusedShared*>(fused_smem);
@@ -1202,7 +1275,15 @@ __global__ void __launch_bounds__(CTA_THREADS) pairs_kernel(
     const float cutoff2_lo = plan.cutoff2_lo;
     const float cutoff2_hi = plan.cutoff2_hi;
 
-    for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
+    if (header->status & STATUS_ABORT_MASK) {
+        return; // the validation kernel refused the plan: the host will redo the build
+    }
+
+    // Consecutive units share two thirds of their stencil: a CTA takes runs of
+    // UNIT_RUN neighbouring units so that most of its loads hit in L1.
+    const int n_runs = (plan.n_units + UNIT_RUN - 1) / UNIT_RUN;
+    for (int run = blockIdx.x; run < n_runs; run += gridDim.x)
+    for (int u = run * UNIT_RUN; u < min(plan.n_units, (run + 1) * UNIT_RUN); u++) {
         Unit unit = unit_of(plan, cell_start, u);
         if (unit.n_home == 0) {
             continue;
@@ -1231,7 +1312,8 @@ __global__ void __launch_bounds__(CTA_THREADS) pairs_kernel(
                 const int batch_words = (batch_slots + 31) >> 5;
 
                 // ---- stage the candidates: warps take segments, lanes take points ----
-                for (int t = warp; t < SEG_MAX; t += CTA_WARPS) {
+                const int group_segments = min(SEG_MAX, unit.n_stencil - g * SEG_MAX);
+                for (int t = warp; t < group_segments; t += CTA_WARPS) {
                     const int seg_slot0 = sh.table.slot0[t];
                     const int seg_len = sh.table.slot0[t + 1] - seg_slot0;
                     const int first = max(seg_slot0, batch0) - seg_slot0;
@@ -1480,12 +1562,25 @@ void launch_bounds(const double* points, size_t n, DeviceHeader* header, cudaStr
     bounds_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, header);
 }
 
+void launch_validate(
+    DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan, size_t n_points, cudaStream_t stream
+) {
+    ExpectedInputs expected;
+    for (int k = 0; k < 9; k++) {
+        expected.box[k] = box[k];
+    }
+    for (int k = 0; k < 3; k++) {
+        expected.periodic[k] = periodic[k] ? 1 : 0;
+    }
+    validate_kernel<<<1, 32, 0, stream>>>(header, expected, plan, n_points);
+}
+
 void launch_bin(
     const double* points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift, int32_t* cell_count,
-    cudaStream_t stream
+    const DeviceHeader* header, cudaStream_t stream
 ) {
     size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    bin_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, plan, cell_of, rank, shift, cell_count);
+    bin_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, plan, cell_of, rank, shift, cell_count, header);
 }
 
 size_t scan_tmp_bytes(size_t n) {
@@ -1514,10 +1609,10 @@ void launch_scan_rows(
 
 void launch_scatter(
     const double* points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
-    SortedPoints sorted, cudaStream_t stream
+    SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
 ) {
     size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    scatter_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, cell_of, rank, shift, cell_start, sorted);
+    scatter_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, cell_of, rank, shift, cell_start, sorted, header);
 }
 
 void launch_count(
@@ -1552,11 +1647,14 @@ void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
     DeviceHeader* header, cudaStream_t stream
 ) {
-    int grid = pair_grid(plan.n_units, 16);
+    // two waves of CTAs (4 are resident per SM by registers and shared memory)
+    const int unit_run = DEFAULT_UNIT_RUN;
+    const int per_sm = 8;
+    int grid = pair_grid((plan.n_units + unit_run - 1) / unit_run, per_sm);
     if (plan.full) {
-        pairs_kernel<true><<<grid, CTA_THREADS, sizeof(FusedShared), stream>>>(plan, cell_start, sorted, out, capacity, header);
+        pairs_kernel<true><<<grid, CTA_THREADS, sizeof(FusedShared), stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run);
     } else {
-        pairs_kernel<false><<<grid, CTA_THREADS, sizeof(FusedShared), stream>>>(plan, cell_start, sorted, out, capacity, header);
+        pairs_kernel<false><<<grid, CTA_THREADS, sizeof(FusedShared), stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run);
     }
 }
 

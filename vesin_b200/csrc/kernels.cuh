@@ -30,6 +30,9 @@ struct DeviceHeader {
 };
 
 constexpr unsigned int STATUS_MASK_OVERFLOW = 1u;
+constexpr unsigned int STATUS_BAD_POINT = 2u;  // a point has a non-finite coordinate
+constexpr unsigned int STATUS_PLAN_STALE = 4u; // box / periodicity / extent differ from what the plan was made for
+constexpr unsigned int STATUS_ABORT_MASK = STATUS_BAD_POINT | STATUS_PLAN_STALE;
 constexpr unsigned long long NO_BAD_POINT = ~0ull;
 
 /// Cell-sorted copy of the points ("records"): original position, original
@@ -55,10 +58,17 @@ void launch_header_init(DeviceHeader* header, const double* box, const bool* per
 /// Min / max of every coordinate and the first non-finite point.
 void launch_bounds(const double* points, size_t n, DeviceHeader* header, cudaStream_t stream);
 
+/// Checks the inputs in device memory against what `plan` was made for (box,
+/// periodicity, extent along non-periodic directions, finite coordinates).
+/// On a mismatch the header's status makes every later kernel return at once.
+void launch_validate(
+    DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan, size_t n_points, cudaStream_t stream
+);
+
 /// Wrap into the cell, pick the cell, histogram with warp-aggregated atomics.
 void launch_bin(
     const double* points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift,
-    int32_t* cell_count, cudaStream_t stream
+    int32_t* cell_count, const DeviceHeader* header, cudaStream_t stream
 );
 
 /// Exclusive scan of int32 counts into int32 starts (n + 1 entries).
@@ -74,7 +84,7 @@ size_t scan_tmp_bytes(size_t n);
 /// Counting-sort scatter into the cell-sorted records.
 void launch_scatter(
     const double* points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift,
-    const int32_t* cell_start, SortedPoints sorted, cudaStream_t stream
+    const int32_t* cell_start, SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
 );
 
 /// Exclusive scan of uint64 counts into uint64 starts (n + 1 entries); the
