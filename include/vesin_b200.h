@@ -36,6 +36,39 @@ VESIN_API void vesin_b200_set_profiling(int enabled);
  * made with this list. */
 VESIN_API int vesin_b200_stage_times(const struct VesinNeighborList* neighbors, double* stage_ms);
 
+/*
+ * No counterpart in the reference (its callers loop over systems, e.g.
+ * python/vesin/vesin/metatomic/_neighbors.py:197-199): the lists of a batch of
+ * independent small systems in ONE call.
+ *
+ * points          device, all systems back to back
+ * system_offsets  HOST array of n_systems + 1 offsets into `points`
+ * boxes, periodic device arrays with one box / one flag triple per system, or
+ *                 both NULL when no system is periodic
+ * global_indices  false: pair indices count from the start of each system (as
+ *                 n_systems separate calls of vesin_neighbors would give);
+ *                 true: from the start of the batch
+ * pair_offsets    out: device array of n_systems + 1 entries owned by the list;
+ *                 system k owns pairs [pair_offsets[k], pair_offsets[k + 1])
+ * The pair set of every system is what vesin_neighbors gives for it. Pairs
+ * are grouped by system; `options.sorted`, `algorithm` and `skin` are ignored.
+ * At most 2048 points per system. Same error and ownership rules as
+ * vesin_neighbors; `neighbors` is released with vesin_free.
+ */
+VESIN_API int vesin_b200_neighbors_batch(
+    const double (*points)[3],
+    const size_t* system_offsets,
+    size_t n_systems,
+    const double (*boxes)[3][3],
+    const bool (*periodic)[3],
+    struct VesinDevice device,
+    struct VesinOptions options,
+    bool global_indices,
+    struct VesinNeighborList* neighbors,
+    const size_t** pair_offsets,
+    const char** error_message
+);
+
 /* Largest system vesin_b200_neighbors_no_alloc accepts. */
 #define VESIN_B200_NO_ALLOC_MAX_POINTS 32768
 

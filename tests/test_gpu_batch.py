@@ -1,0 +1,93 @@
+"""GPU parity of the batch entry point (vesin_b200_neighbors_batch, through
+the C ABI): every system of a batch must get the list that the CPU oracle
+gives for that system alone."""
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from vesin_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+def _check_batch(points, offsets, boxes, periodic, cutoff, full, global_indices=False):
+    import torch
+
+    import vesin_b200
+
+    device = torch.device("cuda", 0)
+    calculator = vesin_b200.BatchNeighborList(cutoff=cutoff, full_list=full)
+    (i, j, S, d, D), pair_offsets = calculator.compute(
+        torch.tensor(points, device=device),
+        offsets,
+        None if boxes is None else torch.tensor(boxes, device=device),
+        None if periodic is None else torch.tensor(periodic, device=device),
+        "ijSdD",
+        global_indices=global_indices,
+    )
+    i, j, S, d, D = (t.cpu().numpy() for t in (i, j, S, d, D))
+    pair_offsets = pair_offsets.cpu().numpy()
+    assert pair_offsets[0] == 0 and pair_offsets[-1] == len(i)
+    for k in range(len(offsets) - 1):
+        lo, hi = pair_offsets[k], pair_offsets[k + 1]
+        shift = offsets[k] if global_indices else 0
+        got = {"i": i[lo:hi] - shift, "j": j[lo:hi] - shift, "S": S[lo:hi], "d": d[lo:hi], "D": D[lo:hi]}
+        system = points[offsets[k] : offsets[k + 1]]
+        box = np.zeros((3, 3)) if boxes is None else boxes[k]
+        pbc = [False] * 3 if periodic is None else periodic[k]
+        expected = O.restated_neighbors(system, box, pbc, cutoff, full, "ijSdD")
+        O.assert_same(got, expected, 1e-12, f"system {k}")
+        expected = O.canonical(expected)
+        got = O.canonical(got)
+        assert np.array_equal(got["d"], expected["d"]) and np.array_equal(got["D"], expected["D"])
+
+
+@pytest.mark.parametrize("full", [True, False])
+def test_molecules(full):
+    points, offsets = W.molecule_batch(n_systems=400, seed=4)
+    _check_batch(points, offsets, None, None, 4.0, full)
+    _check_batch(points, offsets, None, None, 4.0, full, global_indices=True)
+
+
+@pytest.mark.parametrize("full", [True, False])
+def test_periodic_systems_with_many_images(full, monkeypatch):
+    monkeypatch.setenv("VESIN_CUDA_MAX_PAIRS_PER_POINT", "100000")
+    rng = np.random.default_rng(12)
+    systems, boxes, periodic = [], [], []
+    for k in range(24):
+        n_atoms = int(rng.integers(1, 40))
+        p, b, _ = W.small_triclinic(n_atoms, seed=100 + k)
+        flags = [bool(x) for x in rng.integers(0, 2, 3)] if k % 3 else [True, True, True]
+        # some points far outside the box
+        p = p + rng.integers(-3, 4, (n_atoms, 3)) @ b * (k % 2)
+        systems.append(p)
+        boxes.append(b)
+        periodic.append(flags)
+    offsets = np.concatenate([[0], np.cumsum([len(s) for s in systems])])
+    _check_batch(np.concatenate(systems), offsets, np.array(boxes), np.array(periodic), 7.0, full)
+
+
+def test_empty_systems_and_errors():
+    import torch
+
+    import vesin_b200
+
+    device = torch.device("cuda", 0)
+    points, offsets = W.molecule_batch(n_systems=6, seed=9)
+    # an empty system in the middle
+    offsets = np.concatenate([offsets[:3], offsets[2:]])
+    _check_batch(points, offsets, None, None, 4.0, True)
+
+    calculator = vesin_b200.BatchNeighborList(cutoff=4.0, full_list=True)
+    big = torch.zeros((3000, 3), dtype=torch.float64, device=device)
+    with pytest.raises(RuntimeError, match="at most 2048 points per system"):
+        calculator.compute(big, [0, 3000])
+    boxes = torch.zeros((1, 3, 3), dtype=torch.float64, device=device)
+    periodic = torch.ones((1, 3), dtype=torch.bool, device=device)
+    with pytest.raises(RuntimeError, match="the box matrix is not invertible \\(system 0"):
+        calculator.compute(big[:10], [0, 10], boxes, periodic)
+    bad = torch.zeros((10, 3), dtype=torch.float64, device=device)
+    bad[4, 0] = float("inf")
+    with pytest.raises(RuntimeError, match="point 4 of the batch has a non-finite coordinate"):
+        calculator.compute(bad, [0, 10])

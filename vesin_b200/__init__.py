@@ -14,6 +14,10 @@ def __getattr__(name):
         from . import _neighbors
 
         return getattr(_neighbors, name)
+    if name in ("BatchNeighborList", "split_batch"):
+        from . import _batch
+
+        return getattr(_batch, name)
     raise AttributeError(name)
 
 

@@ -61,6 +61,7 @@ EXPORTED_SYMBOLS = (
     "vesin_b200_stage_times",
     "vesin_b200_version",
     "vesin_b200_neighbors_no_alloc",
+    "vesin_b200_neighbors_batch",
 )
 NO_ALLOC_MAX_POINTS = 32768
 
@@ -120,6 +121,20 @@ def get_library():
         ctypes.c_void_p,  # distances
         ctypes.c_void_p,  # vectors
         ctypes.POINTER(ctypes.c_size_t),
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
+    lib.vesin_b200_neighbors_batch.restype = ctypes.c_int
+    lib.vesin_b200_neighbors_batch.argtypes = [
+        ctypes.c_void_p,  # points (device)
+        ctypes.c_void_p,  # system_offsets (host, size_t)
+        ctypes.c_size_t,  # n_systems
+        ctypes.c_void_p,  # boxes (device or NULL)
+        ctypes.c_void_p,  # periodic (device or NULL)
+        VesinDevice,
+        VesinOptions,
+        ctypes.c_bool,  # global_indices
+        ctypes.POINTER(VesinNeighborList),
+        ctypes.POINTER(ctypes.c_void_p),  # pair_offsets (out, device)
         ctypes.POINTER(ctypes.c_char_p),
     ]
     lib.vesin_b200_version.restype = ctypes.c_char_p

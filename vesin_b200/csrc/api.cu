@@ -187,6 +187,66 @@ extern "C" int vesin_b200_stage_times(const VesinNeighborList* neighbors, double
     return vb200::stage_times(*neighbors, stage_ms) ? 0 : 1;
 }
 
+extern "C" int vesin_b200_neighbors_batch(
+    const double (*points)[3],
+    const size_t* system_offsets,
+    size_t n_systems,
+    const double (*boxes)[3][3],
+    const bool (*periodic)[3],
+    VesinDevice device,
+    VesinOptions options,
+    bool global_indices,
+    VesinNeighborList* neighbors,
+    const size_t** pair_offsets,
+    const char** error_message
+) {
+    if (error_message == nullptr) {
+        return EXIT_FAILURE;
+    }
+    if (system_offsets == nullptr) {
+        *error_message = "`system_offsets` can not be a NULL pointer";
+        return EXIT_FAILURE;
+    }
+    if (points == nullptr && n_systems > 0 && system_offsets[n_systems] != system_offsets[0]) {
+        *error_message = "`points` can not be a NULL pointer";
+        return EXIT_FAILURE;
+    }
+    if (neighbors == nullptr) {
+        *error_message = "`neighbors` can not be a NULL pointer";
+        return EXIT_FAILURE;
+    }
+    if (!std::isfinite(options.cutoff) || options.cutoff <= 0) {
+        *error_message = "cutoff must be a finite, positive number";
+        return EXIT_FAILURE;
+    }
+    if (options.cutoff <= 1e-6) {
+        *error_message = "cutoff is too small";
+        return EXIT_FAILURE;
+    }
+    if (device.type != VesinCUDA) {
+        *error_message = "vesin_b200_neighbors_batch only works on CUDA devices";
+        return EXIT_FAILURE;
+    }
+    if (neighbors->device.type != VesinUnknownDevice &&
+        (neighbors->device.type != device.type || neighbors->device.device_id != device.device_id)) {
+        *error_message = "`neighbors` device and data `device` do not match, free the neighbors first";
+        return EXIT_FAILURE;
+    }
+    neighbors->device = device;
+    try {
+        vb200::neighbors_batch(points, system_offsets, n_systems, boxes, periodic, options, global_indices, *neighbors, pair_offsets);
+    } catch (const std::bad_alloc&) {
+        LAST_ERROR = "failed to allocate memory";
+        *error_message = LAST_ERROR.c_str();
+        return EXIT_FAILURE;
+    } catch (const std::exception& e) {
+        LAST_ERROR = e.what();
+        *error_message = LAST_ERROR.c_str();
+        return EXIT_FAILURE;
+    }
+    return EXIT_SUCCESS;
+}
+
 extern "C" const char* vesin_b200_version(void) {
     return "vesin-b200 0.1.0 (C ABI of vesin 0.5.8)";
 }

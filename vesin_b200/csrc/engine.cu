@@ -98,6 +98,7 @@ struct Workspace {
     DeviceBuffer sorted_pos, sorted_index, sorted_shift;
     DeviceBuffer masks, unit_mask_base, unit_words, unit_count, unit_start;
     DeviceBuffer row_count, row_start, row_fill, scan_tmp;
+    DeviceBuffer batch_offsets; // batches: where each system starts in the points array
 
     // output arrays (capacity in pairs); kept allocated when not requested
     DeviceBuffer out_pairs, out_shifts, out_distances, out_vectors;
@@ -123,7 +124,7 @@ struct Workspace {
     ~Workspace() {
         for (DeviceBuffer* buffer :
              {&cell_of, &rank, &shift, &cell_count, &cell_start, &sorted_pos, &sorted_index, &sorted_shift, &masks, &unit_mask_base,
-              &unit_words, &unit_count, &unit_start, &row_count, &row_start, &row_fill, &scan_tmp, &out_pairs, &out_shifts, &out_distances, &out_vectors}) {
+              &unit_words, &unit_count, &unit_start, &row_count, &row_start, &row_fill, &scan_tmp, &batch_offsets, &out_pairs, &out_shifts, &out_distances, &out_vectors}) {
             buffer->release();
         }
         if (d_header != nullptr) {
@@ -154,6 +155,7 @@ Workspace& workspace_of(VesinNeighborList& list) {
         VB200_CUDA(cudaMalloc(reinterpret_cast<void**>(&ws->d_header), sizeof(DeviceHeader)));
         VB200_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&ws->h_header), sizeof(DeviceHeader), cudaHostAllocDefault));
         configure_kernels();
+        configure_small_systems();
     }
     return *static_cast<Workspace*>(list.opaque);
 }
@@ -641,6 +643,128 @@ void neighbors(
         list.length = total;
         ws.timed = timer.enabled;
         return;
+    }
+}
+
+void neighbors_batch(
+    const double (*points)[3],
+    const size_t* system_offsets,
+    size_t n_systems,
+    const double (*boxes)[3][3],
+    const bool (*periodic)[3],
+    VesinOptions options,
+    bool global_indices,
+    VesinNeighborList& list,
+    const size_t** pair_offsets
+) {
+    if (n_systems >= (1ull << 31)) {
+        throw std::runtime_error("too many systems in the batch");
+    }
+    for (size_t k = 0; k < n_systems; k++) {
+        if (system_offsets[k + 1] < system_offsets[k]) {
+            throw std::runtime_error("`system_offsets` must not decrease");
+        }
+    }
+    const size_t n_points = n_systems ? system_offsets[n_systems] - system_offsets[0] : 0;
+    size_t largest = 0;
+    for (size_t k = 0; k < n_systems; k++) {
+        largest = std::max(largest, system_offsets[k + 1] - system_offsets[k]);
+    }
+    if (largest > small_systems_max_points()) {
+        throw std::runtime_error(
+            "a system of the batch has " + std::to_string(largest) + " points; the batch entry point handles at most " +
+            std::to_string(small_systems_max_points()) + " points per system, use vesin_neighbors for larger systems"
+        );
+    }
+    const auto on_device = [&](const void* ptr) {
+        PointerInfo info = inspect(ptr);
+        return info.resolved && info.on_device && info.device == list.device.device_id;
+    };
+    if (n_points > 0 && !on_device(points)) {
+        throw std::runtime_error("`points` pointer is not allocated on the CUDA device of `neighbors`");
+    }
+    if ((boxes != nullptr && !on_device(boxes)) || (periodic != nullptr && !on_device(periodic))) {
+        throw std::runtime_error("`boxes` and `periodic` must be NULL or device memory on the CUDA device of `neighbors`");
+    }
+    if ((boxes == nullptr) != (periodic == nullptr)) {
+        throw std::runtime_error("`boxes` and `periodic` must be given together");
+    }
+
+    DeviceGuard guard(list.device.device_id);
+    Workspace& ws = workspace_of(list);
+    ws.cache.valid = false; // the list was used for something else than a single system
+    const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
+    cudaStream_t stream = ws.stream;
+    const DeviceHeader& header = *ws.h_header;
+
+    ws.batch_offsets.reserve((n_systems + 1) * sizeof(unsigned long long));
+    ws.unit_count.reserve(std::max<size_t>(n_systems, 1) * sizeof(unsigned long long));
+    ws.unit_start.reserve((n_systems + 1) * sizeof(unsigned long long));
+    ws.scan_tmp.reserve(scan_tmp_bytes(std::max<size_t>(n_systems, 1)));
+    static_assert(sizeof(size_t) == sizeof(unsigned long long), "offsets are copied as they are");
+    VB200_CUDA(cudaMemcpyAsync(ws.batch_offsets.ptr, system_offsets, (n_systems + 1) * sizeof(size_t), cudaMemcpyHostToDevice, stream));
+    VB200_CUDA(cudaMemsetAsync(ws.d_header, 0, sizeof(DeviceHeader), stream));
+    VB200_CUDA(cudaMemsetAsync(&ws.d_header->first_bad, 0xff, sizeof(unsigned long long), stream));
+    VB200_CUDA(cudaMemsetAsync(&ws.d_header->mask_cursor, 0xff, sizeof(unsigned long long), stream)); // first singular system
+
+    BatchInput in{};
+    in.points = reinterpret_cast<const double*>(points);
+    in.offsets = ws.batch_offsets.as<unsigned long long>();
+    in.boxes = reinterpret_cast<const double*>(boxes);
+    in.periodic = reinterpret_cast<const bool*>(periodic);
+    in.n_systems = static_cast<unsigned>(n_systems);
+    in.cutoff = options.cutoff;
+    in.cutoff2 = options.cutoff * options.cutoff;
+    in.full = options.full ? 1 : 0;
+    in.global_indices = global_indices ? 1 : 0;
+
+    size_t total = 0;
+    if (n_systems > 0) {
+        launch_small_count(in, largest, ws.unit_count.as<unsigned long long>(), ws.d_header, stream);
+        launch_scan_units(
+            ws.unit_count.as<unsigned long long>(), ws.unit_start.as<unsigned long long>(), n_systems, ws.scan_tmp.ptr,
+            &ws.d_header->total_pairs, stream
+        );
+        VB200_CUDA(cudaGetLastError());
+        read_header(ws);
+        if (header.status & STATUS_SINGULAR_BOX) {
+            throw std::runtime_error("the box matrix is not invertible (system " + std::to_string(header.mask_cursor) + " of the batch)");
+        }
+        if (header.status & STATUS_BAD_POINT) {
+            throw std::runtime_error("point " + std::to_string(header.first_bad) + " of the batch has a non-finite coordinate");
+        }
+        total = static_cast<size_t>(header.total_pairs);
+        if (total > n_points * pair_limit_per_point) {
+            throw std::runtime_error(
+                "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_points * pair_limit_per_point) +
+                " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_points) + "). " +
+                "Consider reducing the cutoff distance, or explicitly setting " +
+                "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable."
+            );
+        }
+    } else {
+        VB200_CUDA(cudaMemsetAsync(ws.unit_start.ptr, 0, sizeof(unsigned long long), stream));
+    }
+
+    size_t capacity = std::max<size_t>(total, 256);
+    if (capacity > common_capacity(ws, options) && ws.out_pairs.bytes != 0) {
+        capacity += capacity / 16;
+    }
+    set_outputs(list, ws, options, capacity);
+    if (total > 0) {
+        PairOutput out{
+            reinterpret_cast<unsigned long long*>(list.pairs),
+            reinterpret_cast<int32_t*>(list.shifts),
+            list.distances,
+            reinterpret_cast<double*>(list.vectors),
+        };
+        launch_small_emit(in, largest, ws.unit_start.as<unsigned long long>(), out, ws.d_header, stream);
+        VB200_CUDA(cudaGetLastError());
+    }
+    VB200_CUDA(cudaStreamSynchronize(stream));
+    list.length = total;
+    if (pair_offsets != nullptr) {
+        *pair_offsets = reinterpret_cast<const size_t*>(ws.unit_start.ptr);
     }
 }
 

@@ -21,6 +21,20 @@ void neighbors(
     VesinNeighborList& list
 );
 
+/// Lists of a batch of independent small systems in one call (no counterpart
+/// in the reference, whose callers loop over systems). Throws like neighbors().
+void neighbors_batch(
+    const double (*points)[3],
+    const size_t* system_offsets,
+    size_t n_systems,
+    const double (*boxes)[3][3],
+    const bool (*periodic)[3],
+    VesinOptions options,
+    bool global_indices,
+    VesinNeighborList& list,
+    const size_t** pair_offsets
+);
+
 /// Release everything a list holds on its device. Replaces
 /// vesin::cuda::free_neighbors (vesin/src/vesin_cuda.cpp:129-138).
 void free_neighbors(VesinNeighborList& list);

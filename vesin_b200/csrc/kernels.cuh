@@ -33,6 +33,7 @@ constexpr unsigned int STATUS_MASK_OVERFLOW = 1u;
 constexpr unsigned int STATUS_BAD_POINT = 2u;  // a point has a non-finite coordinate
 constexpr unsigned int STATUS_PLAN_STALE = 4u; // box / periodicity / extent differ from what the plan was made for
 constexpr unsigned int STATUS_ABORT_MASK = STATUS_BAD_POINT | STATUS_PLAN_STALE;
+constexpr unsigned int STATUS_SINGULAR_BOX = 8u; // batches: the box of a system is not invertible
 constexpr unsigned long long NO_BAD_POINT = ~0ull;
 
 /// Cell-sorted copy of the points ("records"): original position, original
@@ -117,6 +118,33 @@ void launch_emit(
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
     DeviceHeader* header, cudaStream_t stream
+);
+
+// ---- batches of small systems (small_systems.cu) ----
+
+/// A batch of independent systems stored back to back.
+struct BatchInput {
+    const double* points;              // [offsets[n_systems]][3]
+    const unsigned long long* offsets; // [n_systems + 1], device memory
+    const double* boxes;               // [n_systems][9] or null (then nothing is periodic)
+    const bool* periodic;              // [n_systems][3] or null (then nothing is periodic)
+    unsigned n_systems;
+    double cutoff;
+    double cutoff2;
+    int full;
+    int global_indices; // pair indices count from the start of the batch, not of the system
+};
+
+/// Largest system the batch kernels accept (its points live in shared memory).
+size_t small_systems_max_points();
+void configure_small_systems();
+/// Pass 1: pairs of every system -> system_count; the first non-finite point
+/// and the first singular box are reported through the header.
+void launch_small_count(const BatchInput& in, size_t max_points, unsigned long long* system_count, DeviceHeader* header, cudaStream_t stream);
+/// Pass 2: every system writes its pairs at system_start[system].
+void launch_small_emit(
+    const BatchInput& in, size_t max_points, const unsigned long long* system_start, PairOutput out, DeviceHeader* header,
+    cudaStream_t stream
 );
 
 /// One-time per-device kernel attribute setup (shared-memory opt-in).
