@@ -40,6 +40,12 @@ WORKLOADS = {
     "liquid2m": (lambda: workloads.liquid(1 << 21), 6.0, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, half list, fp64 ABI, ijSdD"),
 }
 
+BATCH_WORKLOADS = {
+    # name: (n_systems, cutoff, full list, description)
+    "molecules16k": (16384, 4.0, True, "16384 non-periodic molecules of 16-64 atoms in a 6 A sphere, cutoff 4.0, full list, ijSdD, one batched call"),
+    "molecules2k": (2048, 4.0, True, "2048 non-periodic molecules of 16-64 atoms in a 6 A sphere, cutoff 4.0, full list, ijSdD, one batched call"),
+}
+
 BYTES_PER_POINT = 24  # fp64 positions
 BYTES_PER_PAIR = 16 + 12 + 8 + 24  # i, j as size_t; S int32[3]; d; D
 
@@ -156,6 +162,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if args.workload in BATCH_WORKLOADS:
+        run_reference_batch(args)
+        return
     make, cutoff, full, description = WORKLOADS[args.workload]
     system = make()
     n_pairs, seconds, timed = time_reference_cpu(system, cutoff, full, args.steps, args.warmup, budget_s=240.0)
@@ -187,6 +196,59 @@ def run_reference(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def run_reference_batch(args):
+    """Reference CPU path on a batch: one call per system, as its callers do."""
+    from oracle import oracle
+
+    oracle.build()
+    n_systems, cutoff, full, description = BATCH_WORKLOADS[args.workload]
+    points, offsets = workloads.molecule_batch(n_systems=n_systems, seed=4)
+    cpu = oracle.ReferenceCPU()
+    box = np.zeros((3, 3))
+    sample = min(n_systems, 4096)
+
+    def one_pass():
+        pairs = 0
+        for k in range(sample):
+            pairs += cpu.run(points[offsets[k] : offsets[k + 1]], box, [False] * 3, cutoff, full, "ijSdD", n_threads=1)
+        return pairs
+
+    for _ in range(min(args.warmup, 1)):
+        one_pass()
+    times = []
+    started = time.perf_counter()
+    n_pairs = 0
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        n_pairs = one_pass()
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - started > 120.0:
+            break
+    seconds = float(np.mean(times))
+    value = n_pairs / seconds
+    print(json.dumps({
+        "impl": "reference",
+        "metric": "neighbor pairs/s",
+        "value": value,
+        "unit": "pairs/s",
+        "systems_per_s": sample / seconds,
+        "n_gpus": args.gpus,
+        "steps": len(times),
+        "warmup": min(args.warmup, 1),
+        "ms_per_step": seconds * 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": description, "sample": f"first {sample} systems per step"},
+        "cpu_baseline": {"value": value, "unit": "pairs/s", "cores": 1, "kind": "reference",
+                         "sample": f"first {sample} systems, one reference CPU call per system, n_threads=1"},
+        "e2e": {"value": value, "unit": "pairs/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
 
 
 def run_ours(args):
@@ -397,17 +459,163 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_batch(args):
+    """Batch of independent molecules: one call per rank on its share of the
+    systems (contiguous chunks balanced by atoms, no communication)."""
+    import torch
+    import torch.distributed as dist
+
+    import vesin_b200
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    n_systems, cutoff, full, description = BATCH_WORKLOADS[args.workload]
+    # weak scaling: every rank brings n_systems systems of its own
+    points, offsets = workloads.molecule_batch(n_systems=n_systems, seed=4 + rank)
+    h_points = torch.from_numpy(points).pin_memory()
+    d_points = h_points.to(device)
+    calculator = vesin_b200.BatchNeighborList(cutoff=cutoff, full_list=full)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        (pairs, S, d, D), pair_offsets = calculator.compute(d_points, offsets, quantities="PSdD", copy=False)
+    n_pairs = int(pairs.shape[0])
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        for k in range(args.steps):
+            flush.fill_(k & 0xFF)
+            starts[k].record()
+            calculator.compute(d_points, offsets, quantities="PSdD", copy=False)
+            stops[k].record()
+        barrier()
+    device_ms = sum(a.elapsed_time(b) for a, b in zip(starts, stops)) / args.steps
+
+    # end to end: points from pinned host memory, every output back to the host
+    out_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (pairs, S, d, D, pair_offsets)]
+    staging = torch.empty_like(d_points)
+
+    def e2e_step():
+        staging.copy_(h_points, non_blocking=True)
+        outputs, po = calculator.compute(staging, offsets, quantities="PSdD", copy=False)
+        for host, dev in zip(out_host, list(outputs) + [po]):
+            host.copy_(dev, non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(1, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    times = torch.tensor([device_ms, e2e_ms], dtype=torch.float64, device=device)
+    totals = torch.tensor([float(n_pairs), float(n_systems), float(len(points))], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+    device_ms, e2e_ms = times.tolist()
+    total_pairs, total_systems, total_points = totals.tolist()
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+        bytes_per_call = algorithmic_bytes(len(points), n_pairs)
+        line = {
+            "metric": "neighbor pairs/s",
+            "value": total_pairs / (device_ms * 1e-3),
+            "unit": "pairs/s",
+            "systems_per_s": total_systems / (device_ms * 1e-3),
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": device_ms,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f64",
+            "data": "synthetic",
+            "config": {
+                "workload": description,
+                "n_points": int(total_points),
+                "n_pairs": int(total_pairs),
+                "per_gpu": "every rank builds its own batch of systems, no communication",
+                "l2": "256 MiB buffer written between timed calls (untimed)",
+            },
+            "roofline": {
+                "bound": "hbm",
+                "kernel": "small_systems_kernel (count + emit passes; latency-bound workload)",
+                "achieved": bytes_per_call / (device_ms * 1e-3) / 1e9,
+                "peak": peak,
+                "unit": "GB/s",
+                "frac": bytes_per_call / (device_ms * 1e-3) / 1e9 / peak,
+                "traffic": None,
+                "note": "whole call (both passes, scan, read-back), not one kernel",
+            },
+            "e2e": {
+                "value": total_pairs / (e2e_ms * 1e-3),
+                "unit": "pairs/s",
+                "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": len(points) * 24,
+                "d2h_bytes_per_step": n_pairs * BYTES_PER_PAIR + (n_systems + 1) * 8,
+            },
+            "gpu_launches": 5 * args.steps,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            from oracle import oracle
+
+            oracle.build()
+            cpu = oracle.ReferenceCPU()
+            sample = min(n_systems, 4096)
+            box = np.zeros((3, 3))
+            t0 = time.perf_counter()
+            cpu_pairs = 0
+            for k in range(sample):
+                cpu_pairs += cpu.run(points[offsets[k] : offsets[k + 1]], box, [False] * 3, cutoff, full, "ijSdD", n_threads=1)
+            seconds = time.perf_counter() - t0
+            line["cpu_baseline"] = {
+                "value": cpu_pairs / seconds,
+                "unit": "pairs/s",
+                "cores": 1,
+                "kind": "reference",
+                "sample": f"first {sample} systems, one reference CPU call per system (n_threads=1), as the reference's callers do",
+                "systems_per_s": sample / seconds,
+            }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="diamond512k", choices=sorted(WORKLOADS))
+    parser.add_argument("--workload", default="diamond512k", choices=sorted(WORKLOADS) + sorted(BATCH_WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload in BATCH_WORKLOADS:
+        run_batch(args)
     else:
         run_ours(args)
 
