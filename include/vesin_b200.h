@@ -69,6 +69,51 @@ VESIN_API int vesin_b200_neighbors_batch(
     const char** error_message
 );
 
+/* The slab of one rank: the box is cut along direction `axis` (which must be
+ * periodic); the rank owns the points whose fractional coordinate along that
+ * direction, wrapped into [0, 1), lies in [lower, upper). */
+struct VesinB200Slab {
+    int axis;
+    double lower;
+    double upper;
+};
+
+/*
+ * No counterpart in the reference (which has no multi-GPU notion): one rank's
+ * share of the list of a periodic system that is slab-decomposed over several
+ * GPUs.
+ *
+ * points        device: the rank's OWNED points first (n_owned of them), then its
+ *               halo: copies of the other ranks' points that lie within the
+ *               cutoff of the slab (any periodic image; the engine brings them
+ *               next to the slab itself)
+ * global_index  device: index of every local point in the whole system; these
+ *               indices are written to `pairs`
+ * box, periodic device: the box of the WHOLE system
+ * Full lists: the rank gets every pair (i, j, S) whose i it owns. Half lists:
+ * every pair of the system's half list comes out on exactly one rank. The
+ * union over ranks is the list vesin_neighbors gives for the whole system;
+ * shifts refer to the whole box and the original coordinates.
+ * Needs: slab thickness >= cutoff, and box length along `axis` >= slab + 2 halo
+ * layers. Unsorted lists only. Same error and ownership rules as
+ * vesin_neighbors. The halo exchange itself (NCCL send/recv between
+ * neighbouring ranks) is done by the caller; vesin_b200.ShardedNeighborList
+ * does it with torch.distributed.
+ */
+VESIN_API int vesin_b200_neighbors_slab(
+    const double (*points)[3],
+    size_t n_points,
+    size_t n_owned,
+    const int64_t* global_index,
+    const double box[3][3],
+    const bool periodic[3],
+    struct VesinB200Slab slab,
+    struct VesinDevice device,
+    struct VesinOptions options,
+    struct VesinNeighborList* neighbors,
+    const char** error_message
+);
+
 /* Largest system vesin_b200_neighbors_no_alloc accepts. */
 #define VESIN_B200_NO_ALLOC_MAX_POINTS 32768
 

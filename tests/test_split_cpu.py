@@ -65,3 +65,45 @@ def test_two_ranks_over_gloo(tmp_path):
         capture_output=True, text=True, timeout=240,
     )
     assert result.returncode == 0, result.stdout + result.stderr
+
+
+def test_halo_exchange_over_gloo(tmp_path):
+    """The halo exchange on CPU tensors with 2 and 3 gloo ranks: every rank must
+    end up with exactly the halo the single-process reference selects."""
+    script = tmp_path / "halo.py"
+    script.write_text(
+        textwrap.dedent(
+            f"""
+            import sys
+            sys.path.insert(0, {ROOT!r})
+            import numpy as np
+            import torch
+            import torch.distributed as dist
+            from vesin_b200 import workloads
+            from vesin_b200._sharded import choose_axis, exchange_halo, local_set, owner_of
+
+            dist.init_process_group("gloo")
+            rank, world = dist.get_rank(), dist.get_world_size()
+            points, box, periodic = workloads.liquid(6000, seed=21)
+            cutoff = 6.0
+            axis = choose_axis(box, periodic)
+            owner = owner_of(points, box, axis, world)
+            mine = np.nonzero(owner == rank)[0]
+            halo_points, halo_index = exchange_halo(
+                torch.from_numpy(points[mine]), torch.from_numpy(mine), box, axis, cutoff
+            )
+            owned, halo = local_set(points, box, periodic, cutoff, rank, world)
+            assert np.array_equal(owned, mine)
+            assert np.array_equal(halo_index.numpy(), halo), (rank, len(halo_index), len(halo))
+            assert np.array_equal(halo_points.numpy(), points[halo])
+            dist.destroy_process_group()
+            """
+        )
+    )
+    for world, port in ((2, 29741), (3, 29742)):
+        result = subprocess.run(
+            [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+             "--master-port", str(port), str(script)],
+            capture_output=True, text=True, timeout=300,
+        )
+        assert result.returncode == 0, result.stdout[-2000:] + result.stderr[-2000:]

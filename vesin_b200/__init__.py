@@ -18,6 +18,10 @@ def __getattr__(name):
         from . import _batch
 
         return getattr(_batch, name)
+    if name in ("ShardedNeighborList", "exchange_halo", "owner_of", "choose_axis", "local_set"):
+        from . import _sharded
+
+        return getattr(_sharded, name)
     raise AttributeError(name)
 
 

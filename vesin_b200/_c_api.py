@@ -41,6 +41,10 @@ class VesinOptions(ctypes.Structure):
     ]
 
 
+class VesinB200Slab(ctypes.Structure):
+    _fields_ = [("axis", ctypes.c_int), ("lower", ctypes.c_double), ("upper", ctypes.c_double)]
+
+
 class VesinNeighborList(ctypes.Structure):
     _fields_ = [
         ("length", ctypes.c_size_t),
@@ -62,6 +66,7 @@ EXPORTED_SYMBOLS = (
     "vesin_b200_version",
     "vesin_b200_neighbors_no_alloc",
     "vesin_b200_neighbors_batch",
+    "vesin_b200_neighbors_slab",
 )
 NO_ALLOC_MAX_POINTS = 32768
 
@@ -135,6 +140,20 @@ def get_library():
         ctypes.c_bool,  # global_indices
         ctypes.POINTER(VesinNeighborList),
         ctypes.POINTER(ctypes.c_void_p),  # pair_offsets (out, device)
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
+    lib.vesin_b200_neighbors_slab.restype = ctypes.c_int
+    lib.vesin_b200_neighbors_slab.argtypes = [
+        ctypes.c_void_p,  # points (device): owned first, then halo
+        ctypes.c_size_t,  # n_points
+        ctypes.c_size_t,  # n_owned
+        ctypes.c_void_p,  # global_index (device, int64)
+        ctypes.c_void_p,  # box (device)
+        ctypes.c_void_p,  # periodic (device)
+        VesinB200Slab,
+        VesinDevice,
+        VesinOptions,
+        ctypes.POINTER(VesinNeighborList),
         ctypes.POINTER(ctypes.c_char_p),
     ]
     lib.vesin_b200_version.restype = ctypes.c_char_p

@@ -247,6 +247,64 @@ extern "C" int vesin_b200_neighbors_batch(
     return EXIT_SUCCESS;
 }
 
+extern "C" int vesin_b200_neighbors_slab(
+    const double (*points)[3],
+    size_t n_points,
+    size_t n_owned,
+    const int64_t* global_index,
+    const double box[3][3],
+    const bool periodic[3],
+    VesinB200Slab slab,
+    VesinDevice device,
+    VesinOptions options,
+    VesinNeighborList* neighbors,
+    const char** error_message
+) {
+    if (error_message == nullptr) {
+        return EXIT_FAILURE;
+    }
+    if (points == nullptr || box == nullptr || periodic == nullptr || global_index == nullptr) {
+        *error_message = "`points`, `global_index`, `box` and `periodic` can not be NULL pointers";
+        return EXIT_FAILURE;
+    }
+    if (neighbors == nullptr) {
+        *error_message = "`neighbors` can not be a NULL pointer";
+        return EXIT_FAILURE;
+    }
+    if (!std::isfinite(options.cutoff) || options.cutoff <= 0) {
+        *error_message = "cutoff must be a finite, positive number";
+        return EXIT_FAILURE;
+    }
+    if (options.cutoff <= 1e-6) {
+        *error_message = "cutoff is too small";
+        return EXIT_FAILURE;
+    }
+    if (device.type != VesinCUDA) {
+        *error_message = "vesin_b200_neighbors_slab only works on CUDA devices";
+        return EXIT_FAILURE;
+    }
+    if (neighbors->device.type != VesinUnknownDevice &&
+        (neighbors->device.type != device.type || neighbors->device.device_id != device.device_id)) {
+        *error_message = "`neighbors` device and data `device` do not match, free the neighbors first";
+        return EXIT_FAILURE;
+    }
+    neighbors->device = device;
+    try {
+        vb200::neighbors_slab(
+            points, n_points, n_owned, global_index, box, periodic, slab.axis, slab.lower, slab.upper, options, *neighbors
+        );
+    } catch (const std::bad_alloc&) {
+        LAST_ERROR = "failed to allocate memory";
+        *error_message = LAST_ERROR.c_str();
+        return EXIT_FAILURE;
+    } catch (const std::exception& e) {
+        LAST_ERROR = e.what();
+        *error_message = LAST_ERROR.c_str();
+        return EXIT_FAILURE;
+    }
+    return EXIT_SUCCESS;
+}
+
 extern "C" const char* vesin_b200_version(void) {
     return "vesin-b200 0.1.0 (C ABI of vesin 0.5.8)";
 }

@@ -515,7 +515,7 @@ void neighbors(
                     reinterpret_cast<double*>(list.vectors),
                 };
                 timer.begin(VesinB200StageEmit);
-                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, stream);
+                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, nullptr, stream);
                 timer.end(VesinB200StageEmit);
                 VB200_CUDA(cudaGetLastError());
                 read_header(ws);
@@ -766,6 +766,148 @@ void neighbors_batch(
     if (pair_offsets != nullptr) {
         *pair_offsets = reinterpret_cast<const size_t*>(ws.unit_start.ptr);
     }
+}
+
+void neighbors_slab(
+    const double (*points)[3],
+    size_t n_points,
+    size_t n_owned,
+    const int64_t* global_index,
+    const double box[3][3],
+    const bool periodic[3],
+    int axis,
+    double lower,
+    double upper,
+    VesinOptions options,
+    VesinNeighborList& list
+) {
+    validate_pointers(points, box, periodic, list);
+    if (n_owned > n_points) {
+        throw std::runtime_error("`n_owned` can not be larger than `n_points`");
+    }
+    if (n_points >= (1ull << 31) - 1) {
+        throw std::runtime_error("this engine indexes points with 31 bits: too many points");
+    }
+    if (options.sorted) {
+        throw std::runtime_error("sorted lists are not available for slab-decomposed systems");
+    }
+    {
+        PointerInfo info = inspect(global_index);
+        if (n_points > 0 && !(info.resolved && info.on_device && info.device == list.device.device_id)) {
+            throw std::runtime_error("`global_index` pointer is not allocated on the CUDA device of `neighbors`");
+        }
+    }
+
+    DeviceGuard guard(list.device.device_id);
+    Workspace& ws = workspace_of(list);
+    ws.cache.valid = false; // this list is not used for plain single-system builds
+    const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
+    StageTimer timer(ws, PROFILING.load());
+    cudaStream_t stream = ws.stream;
+    const auto* flat_points = reinterpret_cast<const double*>(points);
+    const DeviceHeader& header = *ws.h_header;
+
+    timer.begin(VesinB200StageBounds);
+    launch_header_init(ws.d_header, reinterpret_cast<const double*>(box), periodic, stream);
+    launch_bounds(flat_points, n_points, ws.d_header, stream);
+    timer.end(VesinB200StageBounds);
+    VB200_CUDA(cudaGetLastError());
+    read_header(ws);
+    timer.collect(VesinB200StageBounds);
+
+    bool host_periodic[3] = {header.periodic[0] != 0, header.periodic[1] != 0, header.periodic[2] != 0};
+    PointBounds bounds{};
+    for (int c = 0; c < 3; c++) {
+        bool have = n_points != 0 && header.min_key[c] != ~0ull;
+        bounds.min[c] = have ? key_to_double(header.min_key[c]) : 0.0;
+        bounds.max[c] = have ? key_to_double(header.max_key[c]) : 0.0;
+    }
+    GridPlan plan = make_plan(header.box, host_periodic, bounds, n_points, options.cutoff, options.full, false, size_t(1) << 27);
+    if (header.first_bad != NO_BAD_POINT) {
+        throw std::runtime_error("local point " + std::to_string(header.first_bad) + " has a non-finite coordinate");
+    }
+    make_slab_window(plan, axis, lower, upper, n_points, n_owned, options.cutoff);
+
+    if (n_points == 0) {
+        set_outputs(list, ws, options, 256);
+        list.length = 0;
+        ws.timed = timer.enabled;
+        return;
+    }
+
+    const size_t n_cells = static_cast<size_t>(plan.n_cells_total);
+    ws.cell_of.reserve(n_points * sizeof(int32_t));
+    ws.rank.reserve(n_points * sizeof(int32_t));
+    ws.shift.reserve(n_points * 3 * sizeof(int32_t));
+    ws.cell_count.reserve(n_cells * sizeof(int32_t));
+    ws.cell_start.reserve((n_cells + 1) * sizeof(int32_t));
+    ws.sorted_pos.reserve(n_points * 3 * sizeof(double));
+    ws.sorted_index.reserve(n_points * sizeof(int32_t));
+    ws.sorted_shift.reserve(n_points * 3 * sizeof(int32_t));
+    ws.scan_tmp.reserve(scan_tmp_bytes(std::max(n_points, n_cells)));
+    SortedPoints sorted{ws.sorted_pos.as<double>(), ws.sorted_index.as<int32_t>(), ws.sorted_shift.as<int32_t>()};
+
+    timer.begin(VesinB200StageBin);
+    VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
+    launch_bin(
+        flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_count.as<int32_t>(),
+        ws.d_header, stream
+    );
+    timer.end(VesinB200StageBin);
+    timer.begin(VesinB200StageScanCells);
+    launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
+    timer.end(VesinB200StageScanCells);
+    timer.begin(VesinB200StageScatter);
+    launch_scatter(
+        flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), sorted,
+        ws.d_header, stream
+    );
+    timer.end(VesinB200StageScatter);
+
+    set_outputs(list, ws, options, std::max<size_t>(common_capacity(ws, options), 256));
+    size_t capacity = common_capacity(ws, options);
+    size_t total = 0;
+    for (int attempt = 0;; attempt++) {
+        PairOutput out{
+            reinterpret_cast<unsigned long long*>(list.pairs),
+            reinterpret_cast<int32_t*>(list.shifts),
+            list.distances,
+            reinterpret_cast<double*>(list.vectors),
+        };
+        timer.begin(VesinB200StageEmit);
+        launch_pairs(
+            plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, reinterpret_cast<const long long*>(global_index), stream
+        );
+        timer.end(VesinB200StageEmit);
+        VB200_CUDA(cudaGetLastError());
+        read_header(ws);
+        if (attempt == 0) {
+            timer.collect(VesinB200StageBin);
+            timer.collect(VesinB200StageScanCells);
+            timer.collect(VesinB200StageScatter);
+        }
+        timer.collect(VesinB200StageEmit);
+        total = static_cast<size_t>(header.pair_cursor);
+        if (total > std::max<size_t>(n_owned, 1) * 2 * pair_limit_per_point) {
+            throw std::runtime_error(
+                "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_owned * pair_limit_per_point) +
+                " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_owned) + "). " +
+                "Consider reducing the cutoff distance, or explicitly setting " +
+                "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable."
+            );
+        }
+        if (total <= capacity) {
+            break;
+        }
+        if (attempt >= 2) {
+            throw std::runtime_error("internal error: the pair total kept changing between passes");
+        }
+        set_outputs(list, ws, options, total + total / 16 + 256);
+        capacity = common_capacity(ws, options);
+        VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, sizeof(unsigned long long), stream));
+    }
+    list.length = total;
+    ws.timed = timer.enabled;
 }
 
 void free_neighbors(VesinNeighborList& list) {

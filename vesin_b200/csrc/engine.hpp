@@ -3,6 +3,7 @@
 #define VESIN_B200_ENGINE_HPP
 
 #include <cstddef>
+#include <cstdint>
 
 #include "vesin.h"
 
@@ -33,6 +34,22 @@ void neighbors_batch(
     bool global_indices,
     VesinNeighborList& list,
     const size_t** pair_offsets
+);
+
+/// One rank's share of a slab-decomposed periodic system (no counterpart in
+/// the reference). Throws like neighbors().
+void neighbors_slab(
+    const double (*points)[3],
+    size_t n_points,
+    size_t n_owned,
+    const int64_t* global_index,
+    const double box[3][3],
+    const bool periodic[3],
+    int axis,
+    double lower,
+    double upper,
+    VesinOptions options,
+    VesinNeighborList& list
 );
 
 /// Release everything a list holds on its device. Replaces

@@ -270,7 +270,22 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
         double g = floor((t - plan.t0[k]) * plan.scale[k]);
         g = fmin(fmax(g, -1.0e9), 1.0e9);
         int gi = static_cast<int>(g);
-        if (plan.periodic[k]) {
+        if (k == plan.window_axis) {
+            // slab decomposition: the image shift is whatever brings the point
+            // into this rank's window; owned points live in the inner layers,
+            // halo points in the first or the last layer
+            double image = floor(t - plan.t0[k]);
+            image = fmin(fmax(image, -1.0e9), 1.0e9);
+            wrap[k] = static_cast<int>(image);
+            int layer = static_cast<int>(fmin(fmax(floor((t - image - plan.t0[k]) * plan.scale[k]), -1.0), 1.0e9));
+            const int last = plan.n_cells[k] - 1;
+            if (i < static_cast<size_t>(plan.n_owned)) {
+                layer = min(max(layer, 1), last - 1);
+            } else {
+                layer = (2 * layer < last) ? 0 : last;
+            }
+            cell[k] = layer;
+        } else if (plan.periodic[k]) {
             int q = floor_div(gi, plan.n_cells[k]);
             wrap[k] = q;
             cell[k] = gi - q * plan.n_cells[k];
@@ -540,7 +555,7 @@ __device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_
             bool valid = true;
 #pragma unroll
             for (int k = 0; k < 3; k++) {
-                if (plan.periodic[k]) {
+                if (plan.periodic[k] && k != plan.window_axis) {
                     q[k] = floor_div(nb[k], plan.n_cells[k]);
                     nb[k] -= q[k] * plan.n_cells[k];
                 } else if (nb[k] < 0 || nb[k] >= plan.n_cells[k]) {
@@ -1132,6 +1147,7 @@ struct FusedShared {
     unsigned list[FUSED_LIST];                // (home lane << 16) | slot in batch
     int shift_out[CTA_WARPS][96];
     double vector_out[CTA_WARPS][96];
+    unsigned owned_word[FUSED_WORDS]; // slab decomposition: which slots of a word hold owned points
     unsigned long long claim;
     int home_row_slots;
 };
@@ -1150,6 +1166,7 @@ __device__ __forceinline__ int setup_half_segments(const GridPlan& plan, const i
         const int global_t = group * SEG_MAX + t;
         int start = 0;
         int q0 = 0, q1 = 0, q2 = 0;
+        int owned = 1;
         if (global_t < unit.n_stencil) {
             int ox, oy, oz;
             if (global_t < own_row) {
@@ -1174,7 +1191,7 @@ __device__ __forceinline__ int setup_half_segments(const GridPlan& plan, const i
             bool valid = true;
 #pragma unroll
             for (int k = 0; k < 3; k++) {
-                if (plan.periodic[k]) {
+                if (plan.periodic[k] && k != plan.window_axis) {
                     q[k] = floor_div(nb[k], plan.n_cells[k]);
                     nb[k] -= q[k] * plan.n_cells[k];
                 } else if (nb[k] < 0 || nb[k] >= plan.n_cells[k]) {
@@ -1188,12 +1205,17 @@ __device__ __forceinline__ int setup_half_segments(const GridPlan& plan, const i
                 q0 = q[0];
                 q1 = q[1];
                 q2 = q[2];
+                if (plan.window_axis >= 0) {
+                    const int layer = nb[plan.window_axis];
+                    owned = (layer >= 1 && layer <= plan.n_cells[plan.window_axis] - 2) ? 1 : 0;
+                }
             }
         }
         table.start[t] = start;
         table.q[0][t] = q0;
         table.q[1][t] = q1;
         table.q[2][t] = q2;
+        table.self_ok[t] = owned; // slab decomposition: does the segment hold owned points?
     }
     const int prefix = block_exclusive_scan(length, table.scan_tmp);
     if (t < SEG_MAX) {
@@ -1262,10 +1284,10 @@ __device__ __forceinline__ void store_pairs(
     __syncwarp();
 }
 
-template <bool FULL>
+template <bool FULL, bool SLAB>
 __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, const int UNIT_RUN
+    DeviceHeader* header, const int UNIT_RUN, const long long* __restrict__ global_index
 ) {
     extern __shared__ __align__(16) unsigned char fused_smem[];
     FusedShared& sh = *reinterpret_cast<FusedShared*>(fused_smem);
@@ -1297,6 +1319,27 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
         const int n_groups = (unit.n_stencil + SEG_MAX - 1) / SEG_MAX;
         const int n_tiles = (unit.n_home + TILE_POINTS - 1) / TILE_POINTS;
 
+        // Slab decomposition: a unit lies in one layer along the cut direction.
+        // Full lists: this rank writes (i, j) for its own i. A unit of owned
+        // points writes the forward pair of every hit and the reversed pair of
+        // hits whose candidate is owned too; a unit of the lower halo layer
+        // only writes reversed pairs (towards owned candidates above it); the
+        // upper halo layer sees nothing above it. Half lists: every unordered
+        // pair is evaluated on exactly one rank with an owned home point, and
+        // that rank writes it.
+        bool home_owned = true;
+        if (SLAB) {
+            const int layer = (plan.window_axis == 0) ? unit.c0 : ((plan.window_axis == 1) ? unit.c1 : unit.c2);
+            const int last = plan.n_cells[plan.window_axis] - 1;
+            if (layer == last) {
+                continue;
+            }
+            home_owned = layer >= 1;
+            if (!FULL && !home_owned) {
+                continue;
+            }
+        }
+
         double centre[3];
 #pragma unroll
         for (int c = 0; c < 3; c++) {
@@ -1307,10 +1350,25 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
         for (int g = 0; g < n_groups; g++) {
             const int group_total = setup_half_segments(plan, cell_start, unit, g, sh);
             const int home_row_slots = sh.home_row_slots;
+            bool all_owned = true;
+            if (SLAB) {
+                int segment_ok = 1;
+                if (threadIdx.x < SEG_MAX) {
+                    const int length = sh.table.slot0[threadIdx.x + 1] - sh.table.slot0[threadIdx.x];
+                    segment_ok = (length == 0) || sh.table.self_ok[threadIdx.x];
+                }
+                all_owned = __syncthreads_and(segment_ok) && home_owned;
+            }
             for (int batch0 = 0; batch0 < group_total; batch0 += FUSED_BATCH) {
                 const int batch_slots = min(FUSED_BATCH, group_total - batch0);
                 const int batch_words = (batch_slots + 31) >> 5;
 
+                if (SLAB) {
+                    if (threadIdx.x < FUSED_WORDS) {
+                        sh.owned_word[threadIdx.x] = 0;
+                    }
+                    __syncthreads();
+                }
                 // ---- stage the candidates: warps take segments, lanes take points ----
                 const int group_segments = min(SEG_MAX, unit.n_stencil - g * SEG_MAX);
                 for (int t = warp; t < group_segments; t += CTA_WARPS) {
@@ -1334,7 +1392,14 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         sh.x[s] = px;
                         sh.y[s] = py;
                         sh.z[s] = pz;
-                        sh.j[s] = sorted.index[p];
+                        if (SLAB) {
+                            sh.j[s] = static_cast<int>(global_index[sorted.index[p]]);
+                            if (sh.table.self_ok[t]) {
+                                atomicOr(&sh.owned_word[s >> 5], 1u << (s & 31));
+                            }
+                        } else {
+                            sh.j[s] = sorted.index[p];
+                        }
                         sh.s[0][s] = r0;
                         sh.s[1][s] = r1;
                         sh.s[2][s] = r2;
@@ -1360,7 +1425,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     const int si1 = sorted.shift[3 * pi + 1];
                     const int si2 = sorted.shift[3 * pi + 2];
                     if (warp == 0) {
-                        sh.home_index[lane] = sorted.index[pi];
+                        sh.home_index[lane] = SLAB ? static_cast<int>(global_index[sorted.index[pi]]) : sorted.index[pi];
                         sh.home_pos[0][lane] = rix;
                         sh.home_pos[1][lane] = riy;
                         sh.home_pos[2][lane] = riz;
@@ -1423,97 +1488,130 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     }
                     __syncthreads();
 
-                    // ---- compact the hit bits: tasks = words in [word][lane] order ----
-                    const int n_tasks = TILE_POINTS * batch_words;
-                    const int task0 = threadIdx.x * FUSED_TASKS;
-                    unsigned task_word[FUSED_TASKS];
-                    int my_hits = 0;
-#pragma unroll
-                    for (int k = 0; k < FUSED_TASKS; k++) {
-                        const int task = task0 + k;
-                        task_word[k] = (task < n_tasks) ? sh.mask[task] : 0u;
-                        my_hits += __popc(task_word[k]);
-                    }
-                    const int my_first = block_exclusive_scan(my_hits, sh.table.scan_tmp);
-                    const int total_hits = sh.table.scan_tmp[CTA_WARPS];
-                    if (total_hits == 0) {
-                        continue;
-                    }
-                    if (threadIdx.x == 0) {
-                        // claim the output range of this block of pairs
-                        const unsigned long long wanted = static_cast<unsigned long long>(total_hits) * (FULL ? 2 : 1);
-                        const unsigned long long first = atomicAdd(&header->pair_cursor, wanted);
-                        sh.claim = (first + wanted <= capacity) ? first : ~0ull;
-                    }
-                    __syncthreads();
-                    const unsigned long long claim = sh.claim;
-                    if (claim == ~0ull) {
-                        continue; // counted, not written: the host will grow the arrays
-                    }
-
-                    for (int round0 = 0; round0 < total_hits; round0 += FUSED_LIST) {
-                        if (round0 != 0) {
-                            __syncthreads(); // previous round consumed
-                        }
-                        {
-                            int position = my_first - round0;
-#pragma unroll
-                            for (int k = 0; k < FUSED_TASKS; k++) {
-                                const int task = task0 + k;
-                                unsigned word = task_word[k];
-                                // task = word index * 32 + home lane
-                                const unsigned code = (static_cast<unsigned>(task & 31) << 16) | (static_cast<unsigned>(task >> 5) << 5);
-                                while (word != 0) {
-                                    const int b = __ffs(word) - 1;
-                                    word &= word - 1;
-                                    if (position >= 0 && position < FUSED_LIST) {
-                                        sh.list[position] = code | b;
-                                    }
-                                    position++;
-                                }
+                    // ---- compact the hit bits and write. Tasks = words in [word][lane]
+                    // order. One pass writes both orientations (full) or the kept one
+                    // (half); a unit of a slab-decomposed full list that touches halo
+                    // points takes two passes, forward pairs then reversed pairs ----
+                    const int n_passes = (SLAB && FULL && !all_owned) ? 2 : 1;
+                    for (int pass = 0; pass < n_passes; pass++) {
+                        bool write_forward = true;
+                        bool write_reverse = FULL;
+                        bool only_owned_candidates = false;
+                        if (SLAB && FULL && !all_owned) {
+                            write_forward = (pass == 0);
+                            write_reverse = (pass == 1);
+                            only_owned_candidates = (pass == 1);
+                            if (pass == 0 && !home_owned) {
+                                continue;
                             }
+                        }
+                        if (pass != 0) {
+                            __syncthreads(); // list, claim and scan scratch of the first pass are free again
+                        }
+                        const int n_tasks = TILE_POINTS * batch_words;
+                        const int task0 = threadIdx.x * FUSED_TASKS;
+                        unsigned task_word[FUSED_TASKS];
+                        int my_hits = 0;
+#pragma unroll
+                        for (int k = 0; k < FUSED_TASKS; k++) {
+                            const int task = task0 + k;
+                            unsigned word = (task < n_tasks) ? sh.mask[task] : 0u;
+                            if (SLAB && only_owned_candidates && task < n_tasks) {
+                                word &= sh.owned_word[task >> 5];
+                            }
+                            task_word[k] = word;
+                            my_hits += __popc(word);
+                        }
+                        const int my_first = block_exclusive_scan(my_hits, sh.table.scan_tmp);
+                        const int total_hits = sh.table.scan_tmp[CTA_WARPS];
+                        if (total_hits == 0) {
+                            continue;
+                        }
+                        const int per_hit = (write_forward ? 1 : 0) + (write_reverse ? 1 : 0);
+                        if (threadIdx.x == 0) {
+                            // claim the output range of this block of pairs
+                            const unsigned long long wanted = static_cast<unsigned long long>(total_hits) * per_hit;
+                            const unsigned long long first = atomicAdd(&header->pair_cursor, wanted);
+                            sh.claim = (first + wanted <= capacity) ? first : ~0ull;
                         }
                         __syncthreads();
+                        const unsigned long long claim = sh.claim;
+                        if (claim == ~0ull) {
+                            continue; // counted, not written: the host will grow the arrays
+                        }
 
-                        const int in_round = min(FUSED_LIST, total_hits - round0);
-                        for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
-                            const int n_valid = min(32, in_round - chunk0);
-                            double vx = 0, vy = 0, vz = 0, d = 0;
-                            int s0 = 0, s1 = 0, s2 = 0;
-                            unsigned long long index_i = 0, index_j = 0;
-                            if (lane < n_valid) {
-                                const unsigned entry = sh.list[chunk0 + lane];
-                                const int h = entry >> 16;
-                                const int s = entry & 0xffff;
-                                s0 = sh.s[0][s] + sh.home_shift[0][h];
-                                s1 = sh.s[1][s] + sh.home_shift[1][h];
-                                s2 = sh.s[2][s] + sh.home_shift[2][h];
-                                const double d2 = exact_pair(
-                                    plan, sh.home_pos[0][h], sh.home_pos[1][h], sh.home_pos[2][h], sh.x[s], sh.y[s], sh.z[s], s0, s1, s2, vx, vy, vz
-                                );
-                                d = __dsqrt_rn(d2);
-                                index_i = static_cast<unsigned long long>(sh.home_index[h]);
-                                index_j = static_cast<unsigned long long>(sh.j[s]);
+                        for (int round0 = 0; round0 < total_hits; round0 += FUSED_LIST) {
+                            if (round0 != 0) {
+                                __syncthreads(); // previous round consumed
                             }
-                            const unsigned long long first = claim + round0 + chunk0;
-                            if (FULL) {
-                                store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
-                                store_pairs(sh, out, warp, lane, first + total_hits, n_valid, index_j, index_i, -s0, -s1, -s2, d, -vx, -vy, -vz);
-                            } else {
-                                // the orientation the reference's half list keeps
-                                const bool forward = (index_i < index_j) || (index_i == index_j && half_rule(s0, s1, s2));
-                                if (!forward) {
-                                    const unsigned long long swap = index_i;
-                                    index_i = index_j;
-                                    index_j = swap;
-                                    s0 = -s0;
-                                    s1 = -s1;
-                                    s2 = -s2;
-                                    vx = -vx;
-                                    vy = -vy;
-                                    vz = -vz;
+                            {
+                                int position = my_first - round0;
+#pragma unroll
+                                for (int k = 0; k < FUSED_TASKS; k++) {
+                                    const int task = task0 + k;
+                                    unsigned word = task_word[k];
+                                    // task = word index * 32 + home lane
+                                    const unsigned code = (static_cast<unsigned>(task & 31) << 16) | (static_cast<unsigned>(task >> 5) << 5);
+                                    while (word != 0) {
+                                        const int b = __ffs(word) - 1;
+                                        word &= word - 1;
+                                        if (position >= 0 && position < FUSED_LIST) {
+                                            sh.list[position] = code | b;
+                                        }
+                                        position++;
+                                    }
                                 }
-                                store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
+                            }
+                            __syncthreads();
+
+                            const int in_round = min(FUSED_LIST, total_hits - round0);
+                            for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
+                                const int n_valid = min(32, in_round - chunk0);
+                                double vx = 0, vy = 0, vz = 0, d = 0;
+                                int s0 = 0, s1 = 0, s2 = 0;
+                                unsigned long long index_i = 0, index_j = 0;
+                                if (lane < n_valid) {
+                                    const unsigned entry = sh.list[chunk0 + lane];
+                                    const int h = entry >> 16;
+                                    const int s = entry & 0xffff;
+                                    s0 = sh.s[0][s] + sh.home_shift[0][h];
+                                    s1 = sh.s[1][s] + sh.home_shift[1][h];
+                                    s2 = sh.s[2][s] + sh.home_shift[2][h];
+                                    const double d2 = exact_pair(
+                                        plan, sh.home_pos[0][h], sh.home_pos[1][h], sh.home_pos[2][h], sh.x[s], sh.y[s], sh.z[s], s0, s1, s2,
+                                        vx, vy, vz
+                                    );
+                                    d = __dsqrt_rn(d2);
+                                    index_i = static_cast<unsigned long long>(sh.home_index[h]);
+                                    index_j = static_cast<unsigned long long>(sh.j[s]);
+                                }
+                                const unsigned long long first = claim + round0 + chunk0;
+                                if (FULL) {
+                                    if (write_forward) {
+                                        store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
+                                    }
+                                    if (write_reverse) {
+                                        store_pairs(
+                                            sh, out, warp, lane, first + (write_forward ? total_hits : 0), n_valid, index_j, index_i, -s0, -s1, -s2,
+                                            d, -vx, -vy, -vz
+                                        );
+                                    }
+                                } else {
+                                    // the orientation the reference's half list keeps
+                                    const bool forward = (index_i < index_j) || (index_i == index_j && half_rule(s0, s1, s2));
+                                    if (!forward) {
+                                        const unsigned long long swap = index_i;
+                                        index_i = index_j;
+                                        index_j = swap;
+                                        s0 = -s0;
+                                        s1 = -s1;
+                                        s2 = -s2;
+                                        vx = -vx;
+                                        vy = -vy;
+                                        vz = -vz;
+                                    }
+                                    store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
+                                }
                             }
                         }
                     }
@@ -1543,8 +1641,10 @@ int pair_grid(int n_units, int per_sm) {
 void configure_kernels() {
     cudaFuncSetAttribute(emit_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
     cudaFuncSetAttribute(emit_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
-    cudaFuncSetAttribute(pairs_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
-    cudaFuncSetAttribute(pairs_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
+    cudaFuncSetAttribute(pairs_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
+    cudaFuncSetAttribute(pairs_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
+    cudaFuncSetAttribute(pairs_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
+    cudaFuncSetAttribute(pairs_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
 }
 
 void launch_header_init(DeviceHeader* header, const double* box, const bool* periodic, cudaStream_t stream) {
@@ -1645,16 +1745,23 @@ void launch_emit(
 
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, cudaStream_t stream
+    DeviceHeader* header, const long long* global_index, cudaStream_t stream
 ) {
     // two waves of CTAs (4 are resident per SM by registers and shared memory)
     const int unit_run = DEFAULT_UNIT_RUN;
     const int per_sm = 8;
     int grid = pair_grid((plan.n_units + unit_run - 1) / unit_run, per_sm);
-    if (plan.full) {
-        pairs_kernel<true><<<grid, CTA_THREADS, sizeof(FusedShared), stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run);
+    const size_t smem = sizeof(FusedShared);
+    if (plan.window_axis >= 0) {
+        if (plan.full) {
+            pairs_kernel<true, true><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, global_index);
+        } else {
+            pairs_kernel<false, true><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, global_index);
+        }
+    } else if (plan.full) {
+        pairs_kernel<true, false><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, nullptr);
     } else {
-        pairs_kernel<false><<<grid, CTA_THREADS, sizeof(FusedShared), stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run);
+        pairs_kernel<false, false><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, nullptr);
     }
 }
 

@@ -115,9 +115,11 @@ void launch_emit(
 /// stencil once and writes the pairs into ranges claimed from
 /// header->pair_cursor. Blocks whose range would pass `capacity` (in pairs)
 /// only count.
+/// With plan.window_axis >= 0 (slab decomposition) `global_index` maps the
+/// local index of a point to the index written into the pairs.
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, cudaStream_t stream
+    DeviceHeader* header, const long long* global_index, cudaStream_t stream
 );
 
 // ---- batches of small systems (small_systems.cu) ----

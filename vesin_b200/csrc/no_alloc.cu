@@ -185,7 +185,7 @@ size_t build(
     launch_bin(points, n_points, plan, cell_of, rank, shift, cell_count, d_header, stream);
     launch_scan_cells(cell_count, cell_start, static_cast<size_t>(plan.n_cells_total), scan_tmp, stream);
     launch_scatter(points, n_points, cell_of, rank, shift, cell_start, sorted, d_header, stream);
-    launch_pairs(plan, cell_start, sorted, out, capacity, d_header, stream);
+    launch_pairs(plan, cell_start, sorted, out, capacity, d_header, nullptr, stream);
     check(cudaGetLastError(), "launch");
     check(cudaMemcpy(&header, d_header, sizeof(header), cudaMemcpyDeviceToHost), "cudaMemcpy(header)");
     return static_cast<size_t>(header.pair_cursor);

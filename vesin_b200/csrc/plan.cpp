@@ -57,6 +57,43 @@ void invert(const double m[3][3], double det, double inv[3][3]) {
 
 } // namespace
 
+/// fp32 screen of the pair passes. Local coordinates (relative to the centre
+/// of the unit) of a point and of its candidates are bounded by M; each carries
+/// a rounding error of at most eps * M, a difference eps * (2 M + d), and the
+/// squared distance of a candidate near the cutoff is then off by at most
+///   eps * (2 sqrt(3) c (2 M + c) + 3 c^2).
+/// Four times that, plus the rounding of the expanded form used by the fused
+/// pass, is the half-width of the band inside which the fp64 predicate decides.
+static void update_screen(GridPlan& plan, double cutoff) {
+    double reach = 0.0;
+    for (int k = 0; k < 3; k++) {
+        double len = std::sqrt(
+            plan.cell_vec[k][0] * plan.cell_vec[k][0] + plan.cell_vec[k][1] * plan.cell_vec[k][1] +
+            plan.cell_vec[k][2] * plan.cell_vec[k][2]
+        );
+        double cells = plan.n_search[k] + 1.0;
+        if (k == 0) {
+            cells += 0.5 * plan.pencil; // the frame is centred on the pencil
+        }
+        reach += cells * len;
+    }
+    const double eps = 5.9604644775390625e-08; // 2^-24
+    double c = cutoff * 1.01;
+    double band = 4.0 * eps * (2.0 * std::sqrt(3.0) * c * (2.0 * reach + c) + 3.0 * c * c);
+    // The fused pass evaluates d2 as |c|^2 + |i|^2 - 2 c.i: seven roundings on
+    // terms bounded by (2 M)^2.
+    band += 40.0 * eps * reach * reach;
+    band += 4.0 * eps * plan.cutoff2; // rounding of the bounds themselves
+    double lo = plan.cutoff2 - band;
+    double hi = plan.cutoff2 + band;
+    // "surely inside" only exists when the band is narrower than the cutoff;
+    // the expanded form of d2 can come out negative, so 0 is not a safe floor
+    plan.cutoff2_lo = (lo > 0.0) ? std::nextafter(static_cast<float>(lo), 0.0f) : -std::numeric_limits<float>::infinity();
+    float hi_f = static_cast<float>(hi);
+    plan.cutoff2_hi = std::isfinite(hi_f) ? std::nextafter(hi_f, std::numeric_limits<float>::infinity())
+                                          : std::numeric_limits<float>::max();
+}
+
 GridPlan make_plan(
     const double box[9],
     const bool periodic[3],
@@ -210,6 +247,8 @@ GridPlan make_plan(
     plan.cutoff2 = cutoff * cutoff;
     plan.full = full ? 1 : 0;
     plan.by_index = sorted ? 1 : 0;
+    plan.window_axis = -1;
+    plan.n_owned = 0;
 
     // Pencil length: the pair passes give one lane to every home point, so a
     // work unit should hold about one warp of points.
@@ -222,41 +261,54 @@ GridPlan make_plan(
     plan.pencil = pencil;
     plan.n_units = ((plan.n_cells[0] + pencil - 1) / pencil) * plan.n_cells[1] * plan.n_cells[2];
 
-    // fp32 screen. Local coordinates (relative to the centre of the home
-    // cell) of a point and of its candidates are bounded by M; each carries a
-    // rounding error of at most eps * M, a difference eps * (2 M + d), and the
-    // squared distance of a candidate near the cutoff is then off by at most
-    //   eps * (2 sqrt(3) c (2 M + c) + 3 c^2).
-    // Four times that is taken as the half-width of the band inside which the
-    // fp64 predicate decides.
-    double reach = 0.0;
-    for (int k = 0; k < 3; k++) {
-        double len = std::sqrt(
-            plan.cell_vec[k][0] * plan.cell_vec[k][0] + plan.cell_vec[k][1] * plan.cell_vec[k][1] +
-            plan.cell_vec[k][2] * plan.cell_vec[k][2]
-        );
-        double cells = plan.n_search[k] + 1.0;
-        if (k == 0) {
-            cells += 0.5 * plan.pencil; // the frame is centred on the pencil
-        }
-        reach += cells * len;
-    }
-    const double eps = 5.9604644775390625e-08; // 2^-24
-    double c = cutoff * 1.01;
-    double band = 4.0 * eps * (2.0 * std::sqrt(3.0) * c * (2.0 * reach + c) + 3.0 * c * c);
-    // The fused pass evaluates d2 as |c|^2 + |i|^2 - 2 c.i: seven roundings on
-    // terms bounded by (2 M)^2.
-    band += 40.0 * eps * reach * reach;
-    band += 4.0 * eps * plan.cutoff2; // rounding of the bounds themselves
-    double lo = plan.cutoff2 - band;
-    double hi = plan.cutoff2 + band;
-    // "surely inside" only exists when the band is narrower than the cutoff;
-    // the expanded form of d2 can come out negative, so 0 is not a safe floor
-    plan.cutoff2_lo = (lo > 0.0) ? std::nextafter(static_cast<float>(lo), 0.0f) : -std::numeric_limits<float>::infinity();
-    float hi_f = static_cast<float>(hi);
-    plan.cutoff2_hi = std::isfinite(hi_f) ? std::nextafter(hi_f, std::numeric_limits<float>::infinity())
-                                          : std::numeric_limits<float>::max();
+    update_screen(plan, cutoff);
     return plan;
+}
+
+void make_slab_window(GridPlan& plan, int axis, double lower, double upper, size_t n_points, size_t n_owned, double cutoff) {
+    if (axis < 0 || axis > 2 || !plan.periodic[axis]) {
+        throw std::runtime_error("the slab direction must be a periodic direction of the box");
+    }
+    if (!(upper > lower)) {
+        throw std::runtime_error("the slab must have a positive thickness");
+    }
+    const double safe_cutoff = cutoff * (1.0 + 9.5e-10);
+    const double thickness = (upper - lower) * plan.face_dist[axis];
+    const double layers = std::floor(thickness / safe_cutoff);
+    if (layers < 1.0) {
+        throw std::runtime_error("the slab of a rank is thinner than the cutoff: use fewer ranks for this system");
+    }
+    const double width = (upper - lower) / layers; // fractional width of one layer
+    if ((upper - lower) + 2.0 * width > 1.0) {
+        throw std::runtime_error("slab plus halo is longer than the box: the box must span at least two slabs plus two cutoffs");
+    }
+    // undo the contribution of the old grid along `axis` ...
+    const int old_cells = plan.n_cells[axis];
+    // ... and install the window: one halo layer, the owned layers, one halo layer
+    plan.n_cells[axis] = static_cast<int32_t>(layers) + 2;
+    plan.n_search[axis] = 1;
+    plan.t0[axis] = lower - width;
+    plan.scale[axis] = 1.0 / width;
+    for (int c = 0; c < 3; c++) {
+        plan.cell_vec[axis][c] = plan.H[axis][c] * width;
+        plan.origin[c] += plan.t0[axis] * plan.H[axis][c];
+    }
+    (void)old_cells;
+    plan.window_axis = axis;
+    plan.n_owned = static_cast<int32_t>(n_owned);
+    plan.n_cells_total = plan.n_cells[0] * plan.n_cells[1] * plan.n_cells[2];
+    plan.n_stencil = (2 * plan.n_search[0] + 1) * (2 * plan.n_search[1] + 1) * (2 * plan.n_search[2] + 1);
+
+    // pencils run along the first direction; they must not mix layers
+    double per_cell = static_cast<double>(n_points) / static_cast<double>(plan.n_cells_total);
+    int pencil = per_cell > 0.0 ? static_cast<int>(std::floor(30.0 / per_cell)) : 1;
+    pencil = std::max(1, std::min({pencil, 8, plan.n_cells[0]}));
+    if (axis == 0) {
+        pencil = 1;
+    }
+    plan.pencil = pencil;
+    plan.n_units = ((plan.n_cells[0] + pencil - 1) / pencil) * plan.n_cells[1] * plan.n_cells[2];
+    update_screen(plan, cutoff);
 }
 
 double min_periodic_face_distance(const GridPlan& plan) {

@@ -45,6 +45,13 @@ struct GridPlan {
     /// Output order: 0 = unit after unit (any order is allowed for unsorted
     /// lists), 1 = one row per point in index order (sorted lists).
     int32_t by_index;
+    /// Slab decomposition: direction cut into slabs (-1: none). Along it the
+    /// cells cover only the window of this rank: layer 0 and the last layer
+    /// hold halo points, the layers between hold the owned points; there is
+    /// no wrap of the cell index, the image shift of a point is whatever
+    /// brings it into the window. Points with local index < n_owned are owned.
+    int32_t window_axis;
+    int32_t n_owned;
 
     double cutoff2;   // cutoff * cutoff in fp64: the exact predicate's bound
     float cutoff2_lo; // fp32 screen: below this a candidate is surely inside
@@ -71,6 +78,12 @@ GridPlan make_plan(
     bool sorted,
     size_t max_cells
 );
+
+/// Turn a plan of the whole box into the plan of one slab: direction `axis`
+/// (periodic) is cut, this rank owns fractional coordinates [lower, upper).
+/// Throws when the slab is thinner than the cutoff or the window (slab plus
+/// one halo layer on each side) is longer than the box.
+void make_slab_window(GridPlan& plan, int axis, double lower, double upper, size_t n_points, size_t n_owned, double cutoff);
 
 /// Smallest distance between opposite faces among periodic directions, or
 /// +inf when no direction is periodic (used for the brute-force legality
