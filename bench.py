@@ -46,6 +46,12 @@ BATCH_WORKLOADS = {
     "molecules2k": (2048, 4.0, True, "2048 non-periodic molecules of 16-64 atoms in a 6 A sphere, cutoff 4.0, full list, ijSdD, one batched call"),
 }
 
+SHARDED_WORKLOADS = {
+    # name: (n_atoms, cutoff, full list, description)
+    "liquid16m": (1 << 24, 6.0, False, "LJ-density liquid, 16777216 atoms, cutoff 6.0, half list, fp64, ijSdD, slab-decomposed over the ranks"),
+    "liquid2m_sharded": (1 << 21, 6.0, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, half list, fp64, ijSdD, slab-decomposed over the ranks"),
+}
+
 BYTES_PER_POINT = 24  # fp64 positions
 BYTES_PER_PAIR = 16 + 12 + 8 + 24  # i, j as size_t; S int32[3]; d; D
 
@@ -603,19 +609,132 @@ def run_batch(args):
         dist.destroy_process_group()
 
 
+def run_sharded(args):
+    """One large periodic system, slab-decomposed over the ranks: every step is
+    one halo exchange (send/recv between neighbouring ranks) plus one local
+    build per rank. Strong scaling: the system is the same at every N. With one
+    rank the plain C ABI builds the whole system."""
+    import torch
+    import torch.distributed as dist
+
+    import vesin_b200
+    from vesin_b200._sharded import choose_axis, owner_of
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    n_atoms, cutoff, full, description = SHARDED_WORKLOADS[args.workload]
+    points, box, periodic = workloads.liquid(n_atoms)
+    if world > 1:
+        axis = choose_axis(box, periodic)
+        mine = np.nonzero(owner_of(points, box, axis, world) == rank)[0]
+        d_points = torch.from_numpy(points[mine]).to(device)
+        d_index = torch.from_numpy(mine).to(device)
+        calculator = vesin_b200.ShardedNeighborList(cutoff=cutoff, full_list=full)
+
+        def step():
+            return calculator.compute(d_points, d_index, box, periodic, "PSdD", copy=False)[0].shape[0]
+    else:
+        d_points = torch.from_numpy(points).to(device)
+        d_box = torch.from_numpy(box).to(device)
+        d_periodic = torch.from_numpy(periodic).to(device)
+        calculator = vesin_b200.NeighborList(cutoff=cutoff, full_list=full)
+
+        def step():
+            return calculator.compute(d_points, d_box, d_periodic, "PSdD", copy=False)[0].shape[0]
+    del points
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        n_pairs = step()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    wall0 = time.perf_counter()
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        for k in range(args.steps):
+            starts[k].record()
+            n_pairs = step()
+            stops[k].record()
+        barrier()
+    wall_ms = (time.perf_counter() - wall0) * 1e3 / args.steps
+    device_ms = sum(a.elapsed_time(b) for a, b in zip(starts, stops)) / args.steps
+
+    times = torch.tensor([device_ms, wall_ms], dtype=torch.float64, device=device)
+    totals = torch.tensor([float(n_pairs), float(d_points.shape[0])], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(totals, op=dist.ReduceOp.SUM)
+    device_ms, wall_ms = times.tolist()
+    total_pairs, total_points = totals.tolist()
+    if rank == 0:
+        peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        peak = float(json.load(open(peaks_path))["hbm_gbs"]) if os.path.exists(peaks_path) else 6650.0
+        total_bytes = algorithmic_bytes(int(total_points), int(total_pairs))
+        achieved = total_bytes / (device_ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "neighbor pairs/s",
+            "value": total_pairs / (device_ms * 1e-3),
+            "unit": "pairs/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": device_ms,
+            "wall_ms_per_step": wall_ms,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "f64",
+            "data": "synthetic",
+            "config": {
+                "workload": description,
+                "n_points": int(total_points),
+                "n_pairs": int(total_pairs),
+                "per_gpu": "one slab per rank; a step = halo exchange (NCCL send/recv) + local build" if world > 1 else "whole system on one GPU",
+                "l2": "outputs (15 GB in total) exceed L2",
+            },
+            "roofline": {
+                "bound": "hbm",
+                "kernel": "whole step (all ranks)",
+                "achieved": achieved,
+                "peak": peak * world,
+                "unit": "GB/s",
+                "frac": achieved / (peak * world),
+                "traffic": None,
+            },
+            "e2e": None,
+            "gpu_launches": 8 * args.steps,
+            "clocks": clocks.summary(),
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--workload", default="diamond512k", choices=sorted(WORKLOADS) + sorted(BATCH_WORKLOADS))
+    parser.add_argument("--workload", default="diamond512k", choices=sorted(WORKLOADS) + sorted(BATCH_WORKLOADS) + sorted(SHARDED_WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload in BATCH_WORKLOADS:
         run_batch(args)
+    elif args.workload in SHARDED_WORKLOADS:
+        run_sharded(args)
     else:
         run_ours(args)
 
