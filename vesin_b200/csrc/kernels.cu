@@ -1369,45 +1369,36 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     }
                     __syncthreads();
                 }
-                // ---- stage the candidates: warps take segments, lanes take points ----
-                const int group_segments = min(SEG_MAX, unit.n_stencil - g * SEG_MAX);
-                for (int t = warp; t < group_segments; t += CTA_WARPS) {
-                    const int seg_slot0 = sh.table.slot0[t];
-                    const int seg_len = sh.table.slot0[t + 1] - seg_slot0;
-                    const int first = max(seg_slot0, batch0) - seg_slot0;
-                    const int last = min(seg_slot0 + seg_len, batch0 + batch_slots) - seg_slot0;
-                    if (first >= last) {
-                        continue;
-                    }
-                    const int q0 = sh.table.q[0][t], q1 = sh.table.q[1][t], q2 = sh.table.q[2][t];
-                    for (int o = first + lane; o < last; o += 32) {
-                        const size_t p = static_cast<size_t>(sh.table.start[t]) + o;
-                        const int s = seg_slot0 + o - batch0;
-                        const double px = sorted.pos[3 * p + 0];
-                        const double py = sorted.pos[3 * p + 1];
-                        const double pz = sorted.pos[3 * p + 2];
-                        const int r0 = q0 - sorted.shift[3 * p + 0];
-                        const int r1 = q1 - sorted.shift[3 * p + 1];
-                        const int r2 = q2 - sorted.shift[3 * p + 2];
-                        sh.x[s] = px;
-                        sh.y[s] = py;
-                        sh.z[s] = pz;
-                        if (SLAB) {
-                            sh.j[s] = static_cast<int>(global_index[sorted.index[p]]);
-                            if (sh.table.self_ok[t]) {
-                                atomicOr(&sh.owned_word[s >> 5], 1u << (s & 31));
-                            }
-                        } else {
-                            sh.j[s] = sorted.index[p];
+                // ---- stage the candidates: one slot per thread (the segment of a slot is
+                //      found by bisection), so all loads of a batch are in flight at once ----
+                for (int s = threadIdx.x; s < batch_slots; s += CTA_THREADS) {
+                    const int slot = batch0 + s;
+                    const int t = find_segment(sh.table, slot);
+                    const size_t p = static_cast<size_t>(sh.table.start[t]) + (slot - sh.table.slot0[t]);
+                    const double px = sorted.pos[3 * p + 0];
+                    const double py = sorted.pos[3 * p + 1];
+                    const double pz = sorted.pos[3 * p + 2];
+                    const int r0 = sh.table.q[0][t] - sorted.shift[3 * p + 0];
+                    const int r1 = sh.table.q[1][t] - sorted.shift[3 * p + 1];
+                    const int r2 = sh.table.q[2][t] - sorted.shift[3 * p + 2];
+                    sh.x[s] = px;
+                    sh.y[s] = py;
+                    sh.z[s] = pz;
+                    if (SLAB) {
+                        sh.j[s] = static_cast<int>(global_index[sorted.index[p]]);
+                        if (sh.table.self_ok[t]) {
+                            atomicOr(&sh.owned_word[s >> 5], 1u << (s & 31));
                         }
-                        sh.s[0][s] = r0;
-                        sh.s[1][s] = r1;
-                        sh.s[2][s] = r2;
-                        const float fx = static_cast<float>(px + (r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0]) - centre[0]);
-                        const float fy = static_cast<float>(py + (r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1]) - centre[1]);
-                        const float fz = static_cast<float>(pz + (r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2]) - centre[2]);
-                        sh.near32[s] = make_float4(fx, fy, fz, fx * fx + fy * fy + fz * fz);
+                    } else {
+                        sh.j[s] = sorted.index[p];
                     }
+                    sh.s[0][s] = r0;
+                    sh.s[1][s] = r1;
+                    sh.s[2][s] = r2;
+                    const float fx = static_cast<float>(px + (r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0]) - centre[0]);
+                    const float fy = static_cast<float>(py + (r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1]) - centre[1]);
+                    const float fz = static_cast<float>(pz + (r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2]) - centre[2]);
+                    sh.near32[s] = make_float4(fx, fy, fz, fx * fx + fy * fy + fz * fz);
                 }
                 for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
                     sh.near32[s] = make_float4(0.0f, 0.0f, 0.0f, __int_as_float(0x7f800000)); // never a hit
