@@ -34,6 +34,7 @@ WORKLOADS = {
     # name: (generator, cutoff, full list, description)
     "diamond512k": (lambda: workloads.diamond(40), 5.0, True, "diamond 40x40x40 (512000 atoms), cutoff 5.0, full list, fp64, ijSdD"),
     "diamond512k_half": (lambda: workloads.diamond(40), 5.0, False, "diamond 40x40x40 (512000 atoms), cutoff 5.0, half list, fp64, ijSdD"),
+    "diamond512k_f32": (lambda: workloads.diamond(40), 5.0, True, "diamond 40x40x40 (512000 atoms), cutoff 5.0, full list, fp32 in / fp32 d and D out (decisions in fp64), ijSdD"),
     "diamond110k": (lambda: workloads.diamond(24), 5.0, True, "diamond 24x24x24 (110592 atoms), cutoff 5.0, full list, fp64, ijSdD"),
     "diamond1000": (lambda: workloads.diamond(5), 5.0, True, "diamond 5x5x5 (1000 atoms), cutoff 5.0, full list, fp64, ijSdD"),
     "triclinic64": (lambda: workloads.small_triclinic(), 9.0, True, "64 atoms in a small triclinic cell, cutoff 9.0, full list, fp64, ijSdD"),
@@ -277,6 +278,14 @@ def run_ours(args):
     make, cutoff, full, description = WORKLOADS[args.workload]
     points, box, periodic = make()
     n_points = len(points)
+    float_io = args.workload.endswith("_f32")
+    if float_io:
+        points = points.astype(np.float32)
+        box = box.astype(np.float32)
+    entry_point = lib.vesin_b200_neighbors_f32 if float_io else lib.vesin_neighbors
+    value_size = 4 if float_io else 8
+    bytes_per_point = 3 * value_size
+    bytes_per_pair = 16 + 12 + 4 * value_size
 
     h_points = torch.from_numpy(points).pin_memory()
     d_points = h_points.to(device)
@@ -298,7 +307,7 @@ def run_ours(args):
     error = ctypes.c_char_p()
 
     def build(points_tensor):
-        status = lib.vesin_neighbors(
+        status = entry_point(
             points_tensor.data_ptr(), n_points, d_box.data_ptr(), d_periodic.data_ptr(), c_device, options,
             ctypes.byref(neighbors), ctypes.byref(error),
         )
@@ -343,8 +352,8 @@ def run_ours(args):
     out_host = {
         "pairs": torch.empty((n_pairs, 2), dtype=torch.int64).pin_memory(),
         "shifts": torch.empty((n_pairs, 3), dtype=torch.int32).pin_memory(),
-        "distances": torch.empty((n_pairs,), dtype=torch.float64).pin_memory(),
-        "vectors": torch.empty((n_pairs, 3), dtype=torch.float64).pin_memory(),
+        "distances": torch.empty((n_pairs,), dtype=torch.float32 if float_io else torch.float64).pin_memory(),
+        "vectors": torch.empty((n_pairs, 3), dtype=torch.float32 if float_io else torch.float64).pin_memory(),
     }
     e2e_steps = max(1, min(args.steps, 5))
     staging = torch.empty_like(d_points)
@@ -365,8 +374,8 @@ def run_ours(args):
         assert count == n_pairs
         copy_out("pairs", neighbors.pairs, count, torch.int64, "<u8")
         copy_out("shifts", neighbors.shifts, count, torch.int32, "<i4")
-        copy_out("distances", neighbors.distances, count, torch.float64, "<f8")
-        copy_out("vectors", neighbors.vectors, count, torch.float64, "<f8")
+        copy_out("distances", neighbors.distances, count, None, "<f4" if float_io else "<f8")
+        copy_out("vectors", neighbors.vectors, count, None, "<f4" if float_io else "<f8")
         torch.cuda.current_stream(device).synchronize()
 
     e2e_step()
@@ -391,7 +400,7 @@ def run_ours(args):
     if rank == 0:
         ms_per_step = device_ms / args.steps
         value = total_pairs / (ms_per_step * 1e-3)
-        bytes_per_build = algorithmic_bytes(n_points, n_pairs)
+        bytes_per_build = n_points * bytes_per_point + int(n_pairs) * bytes_per_pair
         peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
         if os.path.exists(peaks_path):
             with open(peaks_path) as fd:
@@ -412,7 +421,7 @@ def run_ours(args):
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,
-            "dtype": "f64",
+            "dtype": "f64" if not float_io else "f64 decisions, f32 storage",
             "data": "synthetic",
             "config": {
                 "workload": description,
@@ -439,15 +448,17 @@ def run_ours(args):
                 "value": total_pairs / (e2e_ms * 1e-3),
                 "unit": "pairs/s",
                 "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": n_points * 24,
-                "d2h_bytes_per_step": int(n_pairs) * BYTES_PER_PAIR,
+                "h2d_bytes_per_step": n_points * bytes_per_point,
+                "d2h_bytes_per_step": int(n_pairs) * bytes_per_pair,
             },
-            "gpu_launches": 8 * args.steps,  # header, bounds, bin, 3 x scan, scatter, pairs
+            "gpu_launches": 9 * args.steps,  # header, bounds, validate, bin, 3 x scan, scatter, pairs
             "wall_ms_per_step": wall_ms / args.steps,
             "clocks": clocks.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
-            cpu_pairs, cpu_seconds, timed = time_reference_cpu((points, box, periodic), cutoff, full, 2, 1, budget_s=45.0)
+            cpu_pairs, cpu_seconds, timed = time_reference_cpu(
+                (points.astype(np.float64), box.astype(np.float64), periodic), cutoff, full, 2, 1, budget_s=45.0
+            )
             assert cpu_pairs == n_pairs, f"CPU reference found {cpu_pairs} pairs, GPU {n_pairs}"
             cores = host_cores()
             line["cpu_baseline"] = {

@@ -37,6 +37,30 @@ VESIN_API void vesin_b200_set_profiling(int enabled);
 VESIN_API int vesin_b200_stage_times(const struct VesinNeighborList* neighbors, double* stage_ms);
 
 /*
+ * No counterpart in the reference's C API, which is fp64 only: its bindings
+ * upcast float32 inputs and downcast the results in separate passes
+ * (python/vesin/vesin/_neighbors.py:251-252,330,339). This entry point reads
+ * float32 points and box and writes float32 distances and vectors in the same
+ * pass: `neighbors->distances` and `neighbors->vectors` then point at FLOAT
+ * arrays (float[length], float[length][3]) although the struct declares
+ * doubles. Every decision is taken in fp64 on the exactly converted inputs, so
+ * pairs and shifts are those of vesin_neighbors on the upcast data; d and D are
+ * the fp64 results rounded once. Everything else as vesin_neighbors. A list
+ * used with this function must not be handed to vesin_neighbors without the
+ * caller remembering which element type the value arrays hold.
+ */
+VESIN_API int vesin_b200_neighbors_f32(
+    const float (*points)[3],
+    size_t n_points,
+    const float box[3][3],
+    const bool periodic[3],
+    struct VesinDevice device,
+    struct VesinOptions options,
+    struct VesinNeighborList* neighbors,
+    const char** error_message
+);
+
+/*
  * No counterpart in the reference (its callers loop over systems, e.g.
  * python/vesin/vesin/metatomic/_neighbors.py:197-199): the lists of a batch of
  * independent small systems in ONE call.
@@ -111,6 +135,38 @@ VESIN_API int vesin_b200_neighbors_slab(
     struct VesinDevice device,
     struct VesinOptions options,
     struct VesinNeighborList* neighbors,
+    const char** error_message
+);
+
+/*
+ * No counterpart in the reference: builds the two halo messages of a rank of a
+ * slab-decomposed system (see vesin_b200_neighbors_slab). Asynchronous, on the
+ * legacy default stream of the current device.
+ *
+ * points, global_index  device: the points the rank owns
+ * inverse_column        HOST: column `axis` of the inverse box, so that
+ *                       f = x*c[0] + y*c[1] + z*c[2] is the fractional
+ *                       coordinate along the cut direction
+ * lower, upper          the rank's slab in wrapped fractional coordinates
+ * reach                 cutoff / face distance along the cut direction
+ * to_lower, to_upper    device: messages for the two neighbours, (capacity + 1)
+ *                       rows of 4 doubles each: row 0 = number of records (it can
+ *                       exceed `capacity`: then the message is incomplete), every
+ *                       other row = x, y, z, global index (raw 64 bits)
+ * counts                device: 2 counters, scratch of the call
+ */
+VESIN_API int vesin_b200_pack_halo(
+    const double (*points)[3],
+    const int64_t* global_index,
+    size_t n_points,
+    const double inverse_column[3],
+    double lower,
+    double upper,
+    double reach,
+    double* to_lower,
+    double* to_upper,
+    size_t capacity,
+    uint64_t* counts,
     const char** error_message
 );
 

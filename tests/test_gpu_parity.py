@@ -190,3 +190,34 @@ def test_reused_list_follows_changing_inputs():
     for p, b, per in steps[:4]:
         got = gpu_compute(p, b, per, 4.0, False, "ijSdD", calculator=calculator)
         O.assert_same(got, O.restated_neighbors(p, b, per, 4.0, False, "ijSdD"), RTOL_FP64, "sorted")
+
+
+@pytest.mark.parametrize("sorted", [False, True])
+@pytest.mark.parametrize("full", [True, False])
+def test_float32_entry_point(full, sorted):
+    """float32 in, float32 out through vesin_b200_neighbors_f32: pairs and shifts
+    are the oracle's on the exactly upcast inputs; d and D are its fp64 values
+    rounded once (well inside the 1e-5 relative tolerance for fp32)."""
+    import torch
+
+    import vesin_b200
+
+    device = torch.device("cuda", 0)
+    for (points, box, periodic), cutoff in ((W.diamond(6, seed=2), 5.0), (W.small_triclinic(40, seed=8), 6.5), (W.cluster(), 4.0)):
+        p32 = points.astype(np.float32)
+        b32 = box.astype(np.float32)
+        calculator = vesin_b200.NeighborList(cutoff=cutoff, full_list=full, sorted=sorted)
+        i, j, S, d, D = calculator.compute(
+            torch.tensor(p32, device=device), torch.tensor(b32, device=device), torch.tensor(periodic, device=device), "ijSdD"
+        )
+        assert d.dtype == torch.float32 and D.dtype == torch.float32
+        got = {"i": i.cpu().numpy().astype(np.int64), "j": j.cpu().numpy().astype(np.int64), "S": S.cpu().numpy(),
+               "d": d.cpu().numpy(), "D": D.cpu().numpy()}
+        expected = O.restated_neighbors(p32.astype(np.float64), b32.astype(np.float64), periodic, cutoff, full, "ijSdD")
+        O.assert_same(got, expected, 1e-5, "float32")
+        got, expected = O.canonical(got), O.canonical(expected)
+        assert np.array_equal(got["d"], expected["d"].astype(np.float32))
+        assert np.array_equal(got["D"], expected["D"].astype(np.float32))
+    # numpy float32 in -> numpy float32 out
+    i, j, d = vesin_b200.NeighborList(cutoff=5.0, full_list=True).compute(p32, b32, periodic, "ijd")
+    assert d.dtype == np.float32

@@ -83,3 +83,50 @@ def test_slab_limits():
         calculator.build_local(*args, 0, 2)
     with pytest.raises(RuntimeError, match="must be a periodic direction"):
         calculator.build_local(args[0], args[1], args[2], box, [True, True, False], 2, 0, 2)
+
+
+def test_pack_halo_kernel():
+    """vesin_b200_pack_halo against the numpy selection, for every rank of a
+    4-rank decomposition, and the capacity overflow report."""
+    import ctypes
+
+    import torch
+
+    import vesin_b200
+    from vesin_b200._sharded import choose_axis, halo_masks, halo_reach, owner_of, wrapped_fraction
+
+    lib = vesin_b200.get_library()
+    device = torch.device("cuda", 0)
+    points, box, periodic = W.liquid(30000, seed=4)
+    points = points + np.array([300.0, -170.0, 55.0])  # far outside the box
+    world, cutoff = 4, 6.0
+    axis = choose_axis(box, periodic)
+    reach = halo_reach(box, axis, cutoff)
+    column = (ctypes.c_double * 3)(*np.linalg.inv(box)[:, axis])
+    owner = owner_of(points, box, axis, world)
+    for rank in range(world):
+        mine = np.nonzero(owner == rank)[0]
+        g = wrapped_fraction(points[mine], box, axis)
+        down, up = halo_masks(g, rank, world, reach)
+        for capacity in (len(mine), 10):
+            d_points = torch.tensor(points[mine], device=device)
+            d_index = torch.tensor(mine, device=device)
+            to_lower = torch.zeros((capacity + 1, 4), dtype=torch.float64, device=device)
+            to_upper = torch.zeros((capacity + 1, 4), dtype=torch.float64, device=device)
+            counts = torch.zeros(2, dtype=torch.int64, device=device)
+            error = ctypes.c_char_p()
+            status = lib.vesin_b200_pack_halo(
+                d_points.data_ptr(), d_index.data_ptr(), len(mine), column, rank / world, (rank + 1) / world, reach,
+                to_lower.data_ptr(), to_upper.data_ptr(), capacity, counts.data_ptr(), ctypes.byref(error),
+            )
+            assert status == 0, error.value
+            torch.cuda.synchronize()
+            for message, mask in ((to_lower, down), (to_upper, up)):
+                message = message.cpu().numpy()
+                expected = mine[mask]
+                assert int(message[0, 0]) == len(expected)  # the count is reported even when it does not fit
+                if len(expected) <= capacity:
+                    got_index = message[1 : 1 + len(expected), 3].copy().view(np.int64)
+                    order = np.argsort(got_index)
+                    assert np.array_equal(got_index[order], np.sort(expected))
+                    assert np.array_equal(message[1 : 1 + len(expected), :3][order], points[np.sort(expected)])

@@ -67,6 +67,8 @@ EXPORTED_SYMBOLS = (
     "vesin_b200_neighbors_no_alloc",
     "vesin_b200_neighbors_batch",
     "vesin_b200_neighbors_slab",
+    "vesin_b200_pack_halo",
+    "vesin_b200_neighbors_f32",
 )
 NO_ALLOC_MAX_POINTS = 32768
 
@@ -154,6 +156,23 @@ def get_library():
         VesinDevice,
         VesinOptions,
         ctypes.POINTER(VesinNeighborList),
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
+    lib.vesin_b200_neighbors_f32.restype = ctypes.c_int
+    lib.vesin_b200_neighbors_f32.argtypes = lib.vesin_neighbors.argtypes
+    lib.vesin_b200_pack_halo.restype = ctypes.c_int
+    lib.vesin_b200_pack_halo.argtypes = [
+        ctypes.c_void_p,  # points (device)
+        ctypes.c_void_p,  # global_index (device)
+        ctypes.c_size_t,
+        ctypes.POINTER(ctypes.c_double),  # inverse_column (host, 3)
+        ctypes.c_double,  # lower
+        ctypes.c_double,  # upper
+        ctypes.c_double,  # reach
+        ctypes.c_void_p,  # to_lower (device)
+        ctypes.c_void_p,  # to_upper (device)
+        ctypes.c_size_t,  # capacity
+        ctypes.c_void_p,  # counts (device, 2 x uint64)
         ctypes.POINTER(ctypes.c_char_p),
     ]
     lib.vesin_b200_version.restype = ctypes.c_char_p

@@ -122,17 +122,23 @@ class NeighborList:
         if len(points.shape) != 2 or points.shape[1] != 3:
             raise ValueError("`points` must be a nx3 array")
 
+        # float32 data goes through the fp32 entry point: no upcast pass before
+        # the call, no downcast pass after it (the decisions are fp64 either way)
         if from_torch:
             floating = initial_dtype.is_floating_point
             out_dtype = initial_dtype if floating else torch.float64
-            d_points = points.to(torch.float64).contiguous()
-            d_box = box.to(torch.float64).contiguous()
+            float_io = initial_dtype == torch.float32
+            work_dtype = torch.float32 if float_io else torch.float64
+            d_points = points.to(work_dtype).contiguous()
+            d_box = box.to(work_dtype).contiguous()
             d_periodic = torch.as_tensor(periodic, device=device).to(torch.bool).contiguous()
         else:
             floating = np.issubdtype(initial_dtype, np.floating)
             out_dtype = initial_dtype if floating else np.float64
-            d_points = torch.from_numpy(np.ascontiguousarray(points, dtype=np.float64)).to(device, non_blocking=False)
-            d_box = torch.from_numpy(np.ascontiguousarray(box, dtype=np.float64)).to(device)
+            float_io = initial_dtype == np.float32
+            work_dtype = np.float32 if float_io else np.float64
+            d_points = torch.from_numpy(np.ascontiguousarray(points, dtype=work_dtype)).to(device, non_blocking=False)
+            d_box = torch.from_numpy(np.ascontiguousarray(box, dtype=work_dtype)).to(device)
             d_periodic = torch.from_numpy(np.ascontiguousarray(periodic, dtype=np.bool_)).to(device)
         if tuple(d_periodic.shape) != (3,):
             raise ValueError(
@@ -162,7 +168,8 @@ class NeighborList:
         # the engine works on its own stream
         torch.cuda.current_stream(device).synchronize()
         error_message = ctypes.c_char_p()
-        status = self._lib.vesin_neighbors(
+        entry_point = self._lib.vesin_b200_neighbors_f32 if float_io else self._lib.vesin_neighbors
+        status = entry_point(
             d_points.data_ptr(),
             d_points.shape[0],
             d_box.data_ptr(),
@@ -189,9 +196,9 @@ class NeighborList:
             if "S" in quantities:
                 shifts = _view(self._neighbors.shifts, (n_pairs, 3), "<i4", device, owner)
             if "d" in quantities:
-                distances = _view(self._neighbors.distances, (n_pairs,), "<f8", device, owner).to(torch_float)
+                distances = _view(self._neighbors.distances, (n_pairs,), "<f4" if float_io else "<f8", device, owner).to(torch_float)
             if "D" in quantities:
-                vectors = _view(self._neighbors.vectors, (n_pairs, 3), "<f8", device, owner).to(torch_float)
+                vectors = _view(self._neighbors.vectors, (n_pairs, 3), "<f4" if float_io else "<f8", device, owner).to(torch_float)
 
         def finish(tensor):
             if from_torch:

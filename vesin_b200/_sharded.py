@@ -151,6 +151,9 @@ class ShardedNeighborList:
         self.full_list = bool(full_list)
         self.group = group
         self._neighbors = VesinNeighborList()
+        self.halo_capacity = None  # records per halo message; None: twice the uniform-density estimate
+        self._box_key = None
+        self._messages = None
 
     def __del__(self):
         try:
@@ -165,8 +168,7 @@ class ShardedNeighborList:
         device = points.device
         points = points.to(torch.float64).contiguous()
         global_index = global_index.to(torch.int64).contiguous()
-        d_box = torch.as_tensor(np.asarray(box, dtype=np.float64), device=device).contiguous()
-        d_periodic = torch.as_tensor(np.asarray(periodic, dtype=bool), device=device).contiguous()
+        d_box, d_periodic = self._device_box(box, periodic, device)
         options = VesinOptions()
         options.cutoff = self.cutoff
         options.full = self.full_list
@@ -220,6 +222,69 @@ class ShardedNeighborList:
                 data.append(finish(vectors))
         return tuple(data)
 
+    def _device_box(self, box, periodic, device):
+        """Device copies of box and periodicity, re-used while they do not change."""
+        box = np.ascontiguousarray(box, dtype=np.float64)
+        periodic = np.ascontiguousarray(periodic, dtype=bool)
+        key = (box.tobytes(), periodic.tobytes(), str(device))
+        if self._box_key != key:
+            self._box_key = key
+            self._d_box = torch.as_tensor(box, device=device).contiguous()
+            self._d_periodic = torch.as_tensor(periodic, device=device).contiguous()
+            inverse = np.linalg.inv(box)
+            self._inverse_columns = [(ctypes.c_double * 3)(*inverse[:, axis]) for axis in range(3)]
+        return self._d_box, self._d_periodic
+
+    def _exchange_on_device(self, points, global_index, box, axis, rank, world):
+        """Halo exchange for CUDA tensors: one kernel selects and packs both
+        messages (vesin_b200_pack_halo), the messages have a fixed capacity so no
+        sizes are exchanged, and the host waits once, for the four record counts."""
+        import torch.distributed as dist
+
+        device = points.device
+        n = points.shape[0]
+        reach = halo_reach(box, axis, self.cutoff)
+        capacity = self.halo_capacity
+        if capacity is None:
+            capacity = max(4096, int(2.0 * n * reach * world) + 1024)
+        if self._messages is None or self._messages[0].shape[0] != capacity + 1 or self._messages[0].device != device:
+            self._messages = [torch.empty((capacity + 1, 4), dtype=torch.float64, device=device) for _ in range(4)]
+            self._counts = torch.zeros(2, dtype=torch.int64, device=device)
+        to_lower, to_upper, from_upper, from_lower = self._messages
+        if torch.cuda.current_stream(device) != torch.cuda.default_stream(device):
+            torch.cuda.current_stream(device).synchronize()  # the pack kernel runs on the default stream
+        error = ctypes.c_char_p()
+        status = self._lib.vesin_b200_pack_halo(
+            points.data_ptr(), global_index.data_ptr(), n, self._inverse_columns[axis], rank / world, (rank + 1) / world, reach,
+            to_lower.data_ptr(), to_upper.data_ptr(), capacity, self._counts.data_ptr(), ctypes.byref(error),
+        )
+        if status != 0:
+            raise RuntimeError(error.value.decode("utf8"))
+        left, right = (rank - 1) % world, (rank + 1) % world
+
+        def peer(r):
+            return r if self.group is None else dist.get_global_rank(self.group, r)
+
+        # two ranks: both neighbours are the same peer; sends (lower, upper)
+        # pair with the peer's receives (from upper, from lower)
+        operations = [
+            dist.P2POp(dist.isend, to_lower, peer(left), self.group),
+            dist.P2POp(dist.isend, to_upper, peer(right), self.group),
+            dist.P2POp(dist.irecv, from_upper, peer(right), self.group),
+            dist.P2POp(dist.irecv, from_lower, peer(left), self.group),
+        ]
+        for request in dist.batch_isend_irecv(operations):
+            request.wait()
+        counts = torch.stack([from_upper[0, 0], from_lower[0, 0], to_lower[0, 0], to_upper[0, 0]]).cpu()
+        if float(counts.max()) > capacity:
+            raise RuntimeError(
+                f"a halo message needs {int(counts.max())} records but holds {capacity}: set `halo_capacity` on the calculator"
+            )
+        n_upper, n_lower = int(counts[0]), int(counts[1])
+        halo_points = torch.cat([from_upper[1 : 1 + n_upper, :3], from_lower[1 : 1 + n_lower, :3]])
+        halo_index = torch.cat([from_upper[1 : 1 + n_upper, 3], from_lower[1 : 1 + n_lower, 3]]).view(torch.int64)
+        return halo_points, halo_index
+
     def compute(self, points, global_index, box, periodic, quantities="ij", copy=True):
         """`points` (n, 3) and `global_index` (n,): the points this rank owns
         (see ``owner_of``), CUDA tensors. `box` (3, 3) and `periodic` (3,):
@@ -233,7 +298,13 @@ class ShardedNeighborList:
         if world == 1:
             raise RuntimeError("a single rank has no slab to exchange with: use vesin_b200.NeighborList")
         axis = choose_axis(box, periodic)
-        halo_points, halo_index = exchange_halo(points, global_index, box, axis, self.cutoff, self.group)
+        if points.device.type == "cuda":
+            points = points.to(torch.float64).contiguous()
+            global_index = global_index.to(torch.int64).contiguous()
+            self._device_box(box, periodic, points.device)
+            halo_points, halo_index = self._exchange_on_device(points, global_index, box, axis, rank, world)
+        else:
+            halo_points, halo_index = exchange_halo(points, global_index, box, axis, self.cutoff, self.group)
         local_points = torch.cat([points, halo_points])
         local_index = torch.cat([global_index, halo_index])
         return self.build_local(local_points, local_index, points.shape[0], box, periodic, axis, rank, world, quantities, copy)

@@ -50,15 +50,16 @@ static_assert(offsetof(VesinNeighborList, opaque) == 48, "VesinNeighborList layo
 // dynamically built messages live here until the next failure on this thread
 static thread_local std::string LAST_ERROR;
 
-extern "C" int vesin_neighbors(
-    const double (*points)[3],
+static int neighbors_entry(
+    const void* points,
     size_t n_points,
-    const double box[3][3],
+    const void* box,
     const bool periodic[3],
     VesinDevice device,
     VesinOptions options,
     VesinNeighborList* neighbors,
-    const char** error_message
+    const char** error_message,
+    bool float_io
 ) {
     // Order and wording of the checks: vesin/src/vesin.cpp:51-105
     if (error_message == nullptr) {
@@ -106,7 +107,7 @@ extern "C" int vesin_neighbors(
 
     try {
         if (device.type == VesinCUDA) {
-            vb200::neighbors(points, n_points, box, periodic, options, *neighbors);
+            vb200::neighbors(points, n_points, box, periodic, options, *neighbors, float_io);
         } else if (device.type == VesinCPU) {
             throw std::runtime_error(
                 "this build of vesin is the CUDA (sm_100a) engine only: data on VesinCPU is not supported, "
@@ -128,6 +129,32 @@ extern "C" int vesin_neighbors(
         return EXIT_FAILURE;
     }
     return EXIT_SUCCESS;
+}
+
+extern "C" int vesin_neighbors(
+    const double (*points)[3],
+    size_t n_points,
+    const double box[3][3],
+    const bool periodic[3],
+    VesinDevice device,
+    VesinOptions options,
+    VesinNeighborList* neighbors,
+    const char** error_message
+) {
+    return neighbors_entry(points, n_points, box, periodic, device, options, neighbors, error_message, /*float_io=*/false);
+}
+
+extern "C" int vesin_b200_neighbors_f32(
+    const float (*points)[3],
+    size_t n_points,
+    const float box[3][3],
+    const bool periodic[3],
+    VesinDevice device,
+    VesinOptions options,
+    VesinNeighborList* neighbors,
+    const char** error_message
+) {
+    return neighbors_entry(points, n_points, box, periodic, device, options, neighbors, error_message, /*float_io=*/true);
 }
 
 extern "C" void vesin_free(VesinNeighborList* neighbors) {

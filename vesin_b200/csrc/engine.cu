@@ -333,12 +333,13 @@ bool stage_times(const VesinNeighborList& list, double* stage_ms) {
 }
 
 void neighbors(
-    const double (*points)[3],
+    const void* points,
     size_t n_points,
-    const double box[3][3],
+    const void* box,
     const bool periodic[3],
     VesinOptions options,
-    VesinNeighborList& list
+    VesinNeighborList& list,
+    bool float_io
 ) {
     int device_count = 0;
     if (cudaGetDeviceCount(&device_count) != cudaSuccess || device_count == 0) {
@@ -355,7 +356,8 @@ void neighbors(
     const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
     StageTimer timer(ws, PROFILING.load());
     cudaStream_t stream = ws.stream;
-    const auto* flat_points = reinterpret_cast<const double*>(points);
+    const RealView flat_points{points, float_io ? 1 : 0};
+    const RealView flat_box{box, float_io ? 1 : 0};
 
     const DeviceHeader& header = *ws.h_header;
     const size_t max_cells = size_t(1) << 27;
@@ -363,7 +365,15 @@ void neighbors(
     const auto bad_point_error = [&]() {
         // same text as the CPU path (vesin/src/types.hpp:163-169)
         double bad[3];
-        VB200_CUDA(cudaMemcpy(bad, flat_points + 3 * header.first_bad, sizeof(bad), cudaMemcpyDeviceToHost));
+        if (float_io) {
+            float bad32[3];
+            VB200_CUDA(cudaMemcpy(bad32, static_cast<const float*>(points) + 3 * header.first_bad, sizeof(bad32), cudaMemcpyDeviceToHost));
+            bad[0] = bad32[0];
+            bad[1] = bad32[1];
+            bad[2] = bad32[2];
+        } else {
+            VB200_CUDA(cudaMemcpy(bad, static_cast<const double*>(points) + 3 * header.first_bad, sizeof(bad), cudaMemcpyDeviceToHost));
+        }
         for (int axis = 0; axis < 3; axis++) {
             if (!std::isfinite(bad[axis])) {
                 return std::runtime_error(
@@ -415,7 +425,7 @@ void neighbors(
 
     for (int round = 0;; round++) {
         timer.begin(VesinB200StageBounds);
-        launch_header_init(ws.d_header, reinterpret_cast<const double*>(box), periodic, stream);
+        launch_header_init(ws.d_header, flat_box, periodic, stream);
         launch_bounds(flat_points, n_points, ws.d_header, stream);
         timer.end(VesinB200StageBounds);
         if (!speculative) {
@@ -513,6 +523,7 @@ void neighbors(
                     reinterpret_cast<int32_t*>(list.shifts),
                     list.distances,
                     reinterpret_cast<double*>(list.vectors),
+                    float_io ? 1 : 0,
                 };
                 timer.begin(VesinB200StageEmit);
                 launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, nullptr, stream);
@@ -627,6 +638,7 @@ void neighbors(
                 reinterpret_cast<int32_t*>(list.shifts),
                 list.distances,
                 reinterpret_cast<double*>(list.vectors),
+                float_io ? 1 : 0,
             };
             timer.begin(VesinB200StageEmit);
             VB200_CUDA(cudaMemsetAsync(ws.row_fill.ptr, 0, n_points * sizeof(uint32_t), stream));
@@ -804,11 +816,11 @@ void neighbors_slab(
     const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
     StageTimer timer(ws, PROFILING.load());
     cudaStream_t stream = ws.stream;
-    const auto* flat_points = reinterpret_cast<const double*>(points);
+    const RealView flat_points{points, 0};
     const DeviceHeader& header = *ws.h_header;
 
     timer.begin(VesinB200StageBounds);
-    launch_header_init(ws.d_header, reinterpret_cast<const double*>(box), periodic, stream);
+    launch_header_init(ws.d_header, RealView{box, 0}, periodic, stream);
     launch_bounds(flat_points, n_points, ws.d_header, stream);
     timer.end(VesinB200StageBounds);
     VB200_CUDA(cudaGetLastError());

@@ -13,13 +13,16 @@ namespace vb200 {
 /// vesin::cuda::neighbors (vesin/src/vesin_cuda.cpp:819-923). Throws
 /// std::runtime_error / std::bad_alloc; the C entry point turns those into
 /// error strings.
+/// With `float_io`, `points` and `box` are float arrays and the distances /
+/// vectors of the list are float arrays too (the decisions stay fp64).
 void neighbors(
-    const double (*points)[3],
+    const void* points,
     size_t n_points,
-    const double box[3][3],
+    const void* box,
     const bool periodic[3],
     VesinOptions options,
-    VesinNeighborList& list
+    VesinNeighborList& list,
+    bool float_io
 );
 
 /// Lists of a batch of independent small systems in one call (no counterpart

@@ -38,6 +38,11 @@ __device__ __forceinline__ int floor_div(int a, int b) {
     return (r < 0) ? q - 1 : q;
 }
 
+__device__ __forceinline__ double load_real(const RealView& view, size_t k) {
+    // float -> double is exact: fp32 inputs are decided with the same fp64 arithmetic
+    return view.is_float ? static_cast<double>(static_cast<const float*>(view.data)[k]) : static_cast<const double*>(view.data)[k];
+}
+
 __device__ __forceinline__ unsigned lanemask_lt() {
     unsigned mask;
     asm("mov.u32 %0, %%lanemask_lt;" : "=r"(mask));
@@ -90,7 +95,7 @@ __device__ __forceinline__ int block_exclusive_scan(int value, int* warp_sums) {
 // (vesin/src/types.hpp:159-178).
 // ---------------------------------------------------------------------------
 
-__global__ void header_init_kernel(DeviceHeader* header, const double* box, const bool* periodic) {
+__global__ void header_init_kernel(DeviceHeader* header, const RealView box, const bool* periodic) {
     int t = threadIdx.x;
     if (t < 3) {
         header->min_key[t] = ~0ull;
@@ -98,7 +103,7 @@ __global__ void header_init_kernel(DeviceHeader* header, const double* box, cons
         header->periodic[t] = periodic[t] ? 1 : 0;
     }
     if (t < 9) {
-        header->box[t] = box[t];
+        header->box[t] = load_real(box, t);
     }
     if (t == 0) {
         header->first_bad = NO_BAD_POINT;
@@ -109,7 +114,7 @@ __global__ void header_init_kernel(DeviceHeader* header, const double* box, cons
     }
 }
 
-__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const double* __restrict__ points, size_t n, DeviceHeader* header) {
+__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const RealView points, size_t n, DeviceHeader* header) {
     double lo[3] = {DBL_MAX, DBL_MAX, DBL_MAX};
     double hi[3] = {-DBL_MAX, -DBL_MAX, -DBL_MAX};
     unsigned long long bad = NO_BAD_POINT;
@@ -118,7 +123,7 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const double* __res
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
 #pragma unroll
         for (int c = 0; c < 3; c++) {
-            double x = points[3 * i + c];
+            double x = load_real(points, 3 * i + c);
             if (isfinite(x)) {
                 lo[c] = fmin(lo[c], x);
                 hi[c] = fmax(hi[c], x);
@@ -245,7 +250,7 @@ __global__ void validate_kernel(DeviceHeader* header, const ExpectedInputs expec
 // ---------------------------------------------------------------------------
 
 __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
-    const double* __restrict__ points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
+    const RealView points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
     int32_t* __restrict__ shift, int32_t* __restrict__ cell_count, const DeviceHeader* __restrict__ header
 ) {
     if (header->status & STATUS_ABORT_MASK) {
@@ -258,9 +263,9 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
         return;
     }
 
-    double rx = points[3 * i + 0];
-    double ry = points[3 * i + 1];
-    double rz = points[3 * i + 2];
+    double rx = load_real(points, 3 * i + 0);
+    double ry = load_real(points, 3 * i + 1);
+    double rz = load_real(points, 3 * i + 2);
 
     int cell[3];
     int wrap[3];
@@ -453,7 +458,7 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
 // ---------------------------------------------------------------------------
 
 __global__ void __launch_bounds__(CTA_THREADS) scatter_kernel(
-    const double* __restrict__ points, size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank,
+    const RealView points, size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank,
     const int32_t* __restrict__ shift, const int32_t* __restrict__ cell_start, SortedPoints sorted,
     const DeviceHeader* __restrict__ header
 ) {
@@ -462,9 +467,9 @@ __global__ void __launch_bounds__(CTA_THREADS) scatter_kernel(
         return;
     }
     size_t p = static_cast<size_t>(cell_start[cell_of[i]]) + rank[i];
-    sorted.pos[3 * p + 0] = points[3 * i + 0];
-    sorted.pos[3 * p + 1] = points[3 * i + 1];
-    sorted.pos[3 * p + 2] = points[3 * i + 2];
+    sorted.pos[3 * p + 0] = load_real(points, 3 * i + 0);
+    sorted.pos[3 * p + 1] = load_real(points, 3 * i + 1);
+    sorted.pos[3 * p + 2] = load_real(points, 3 * i + 2);
     sorted.index[p] = static_cast<int32_t>(i);
     sorted.shift[3 * p + 0] = shift[3 * i + 0];
     sorted.shift[3 * p + 1] = shift[3 * i + 1];
@@ -1035,7 +1040,11 @@ __global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
                                     static_cast<unsigned long long>(sh.home_index[h]), static_cast<unsigned long long>(sh.j[slot])
                                 );
                                 if (out.distances != nullptr) {
-                                    out.distances[dest] = __dsqrt_rn(d2);
+                                    if (out.values_float) {
+                                        reinterpret_cast<float*>(out.distances)[dest] = static_cast<float>(__dsqrt_rn(d2));
+                                    } else {
+                                        out.distances[dest] = __dsqrt_rn(d2);
+                                    }
                                 }
                             }
                             if (BY_INDEX) {
@@ -1045,9 +1054,16 @@ __global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
                                     out.shifts[3 * dest + 2] = s2;
                                 }
                                 if (valid && out.vectors != nullptr) {
-                                    out.vectors[3 * dest + 0] = vx;
-                                    out.vectors[3 * dest + 1] = vy;
-                                    out.vectors[3 * dest + 2] = vz;
+                                    if (out.values_float) {
+                                        float* vectors = reinterpret_cast<float*>(out.vectors);
+                                        vectors[3 * dest + 0] = static_cast<float>(vx);
+                                        vectors[3 * dest + 1] = static_cast<float>(vy);
+                                        vectors[3 * dest + 2] = static_cast<float>(vz);
+                                    } else {
+                                        out.vectors[3 * dest + 0] = vx;
+                                        out.vectors[3 * dest + 1] = vy;
+                                        out.vectors[3 * dest + 2] = vz;
+                                    }
                                 }
                             } else {
                                 const unsigned long long first = cursor + round0 + chunk0;
@@ -1248,7 +1264,11 @@ __device__ __forceinline__ void store_pairs(
     if (lane < n_valid) {
         reinterpret_cast<ulonglong2*>(out.pairs)[first + lane] = make_ulonglong2(a, b);
         if (out.distances != nullptr) {
-            out.distances[first + lane] = d;
+            if (out.values_float) {
+                reinterpret_cast<float*>(out.distances)[first + lane] = static_cast<float>(d);
+            } else {
+                out.distances[first + lane] = d;
+            }
         }
     }
     if (out.shifts != nullptr) {
@@ -1266,7 +1286,22 @@ __device__ __forceinline__ void store_pairs(
             }
         }
     }
-    if (out.vectors != nullptr) {
+    if (out.vectors != nullptr && out.values_float) {
+        // fp32 output: rounded once from the fp64 result
+        float* buffer = reinterpret_cast<float*>(sh.vector_out[warp]);
+        buffer[3 * lane + 0] = static_cast<float>(vx);
+        buffer[3 * lane + 1] = static_cast<float>(vy);
+        buffer[3 * lane + 2] = static_cast<float>(vz);
+        __syncwarp();
+        float* dst = reinterpret_cast<float*>(out.vectors) + 3 * first;
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            const int w = k * 32 + lane;
+            if (w < 3 * n_valid) {
+                dst[w] = buffer[w];
+            }
+        }
+    } else if (out.vectors != nullptr) {
         double* buffer = sh.vector_out[warp];
         buffer[3 * lane + 0] = vx;
         buffer[3 * lane + 1] = vy;
@@ -1638,11 +1673,11 @@ void configure_kernels() {
     cudaFuncSetAttribute(pairs_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
 }
 
-void launch_header_init(DeviceHeader* header, const double* box, const bool* periodic, cudaStream_t stream) {
+void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, cudaStream_t stream) {
     header_init_kernel<<<1, 32, 0, stream>>>(header, box, periodic);
 }
 
-void launch_bounds(const double* points, size_t n, DeviceHeader* header, cudaStream_t stream) {
+void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream) {
     if (n == 0) {
         return;
     }
@@ -1667,7 +1702,7 @@ void launch_validate(
 }
 
 void launch_bin(
-    const double* points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift, int32_t* cell_count,
+    RealView points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift, int32_t* cell_count,
     const DeviceHeader* header, cudaStream_t stream
 ) {
     size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
@@ -1699,7 +1734,7 @@ void launch_scan_rows(
 }
 
 void launch_scatter(
-    const double* points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
+    RealView points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
     SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
 ) {
     size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;

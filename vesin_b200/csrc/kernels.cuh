@@ -50,14 +50,22 @@ struct PairOutput {
     int32_t* shifts;           // [total][3]
     double* distances;         // [total]
     double* vectors;           // [total][3]
+    int values_float;          // distances / vectors are float arrays (fp32 entry point); decisions stay fp64
+};
+
+/// Input coordinates: double (the reference's C API) or float (fp32 entry
+/// point; converted exactly to double when read).
+struct RealView {
+    const void* data;
+    int is_float;
 };
 
 // ---- launch wrappers (all asynchronous on `stream`) ----
 
-void launch_header_init(DeviceHeader* header, const double* box, const bool* periodic, cudaStream_t stream);
+void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, cudaStream_t stream);
 
 /// Min / max of every coordinate and the first non-finite point.
-void launch_bounds(const double* points, size_t n, DeviceHeader* header, cudaStream_t stream);
+void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream);
 
 /// Checks the inputs in device memory against what `plan` was made for (box,
 /// periodicity, extent along non-periodic directions, finite coordinates).
@@ -68,7 +76,7 @@ void launch_validate(
 
 /// Wrap into the cell, pick the cell, histogram with warp-aggregated atomics.
 void launch_bin(
-    const double* points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift,
+    RealView points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift,
     int32_t* cell_count, const DeviceHeader* header, cudaStream_t stream
 );
 
@@ -84,7 +92,7 @@ size_t scan_tmp_bytes(size_t n);
 
 /// Counting-sort scatter into the cell-sorted records.
 void launch_scatter(
-    const double* points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift,
+    RealView points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift,
     const int32_t* cell_start, SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
 );
 
