@@ -151,7 +151,9 @@ class ShardedNeighborList:
         self.full_list = bool(full_list)
         self.group = group
         self._neighbors = VesinNeighborList()
-        self.halo_capacity = None  # records per halo message; None: twice the uniform-density estimate
+        # records per halo message, the same on every rank; None: agreed on at the
+        # first build (twice the uniform-density estimate of the fullest rank)
+        self.halo_capacity = None
         self._box_key = None
         self._messages = None
 
@@ -244,9 +246,13 @@ class ShardedNeighborList:
         device = points.device
         n = points.shape[0]
         reach = halo_reach(box, axis, self.cutoff)
+        # every rank must use the same message size: agree on it once (the
+        # largest of the ranks' estimates, twice the uniform-density halo)
+        if self.halo_capacity is None:
+            wanted = torch.tensor([max(4096, int(2.0 * n * reach * world) + 1024)], dtype=torch.int64, device=device)
+            dist.all_reduce(wanted, op=dist.ReduceOp.MAX, group=self.group)
+            self.halo_capacity = int(wanted.item())
         capacity = self.halo_capacity
-        if capacity is None:
-            capacity = max(4096, int(2.0 * n * reach * world) + 1024)
         if self._messages is None or self._messages[0].shape[0] != capacity + 1 or self._messages[0].device != device:
             self._messages = [torch.empty((capacity + 1, 4), dtype=torch.float64, device=device) for _ in range(4)]
             self._counts = torch.zeros(2, dtype=torch.int64, device=device)
@@ -278,7 +284,8 @@ class ShardedNeighborList:
         counts = torch.stack([from_upper[0, 0], from_lower[0, 0], to_lower[0, 0], to_upper[0, 0]]).cpu()
         if float(counts.max()) > capacity:
             raise RuntimeError(
-                f"a halo message needs {int(counts.max())} records but holds {capacity}: set `halo_capacity` on the calculator"
+                f"a halo message needs {int(counts.max())} records but holds {capacity}: "
+                "set `halo_capacity` (same value on every rank) on the calculator"
             )
         n_upper, n_lower = int(counts[0]), int(counts[1])
         halo_points = torch.cat([from_upper[1 : 1 + n_upper, :3], from_lower[1 : 1 + n_lower, :3]])
