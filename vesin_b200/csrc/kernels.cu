@@ -1160,13 +1160,13 @@ struct FusedShared {
     int home_shift[3][TILE_POINTS];
     int home_index[TILE_POINTS];
     unsigned mask[FUSED_WORDS * TILE_POINTS]; // [word][lane]
-    unsigned list[FUSED_LIST];                // (home lane << 16) | slot in batch
-    int shift_out[CTA_WARPS][96];
-    double vector_out[CTA_WARPS][96];
+    unsigned short list[FUSED_LIST];          // (home lane << 9) | slot in batch
+    double transpose[CTA_WARPS][192];         // per warp: 64 shifts, then 64 vectors, on their way to coalesced stores
     unsigned owned_word[FUSED_WORDS]; // slab decomposition: which slots of a word hold owned points
     unsigned long long claim;
     int home_row_slots;
 };
+static_assert(FUSED_BATCH <= 512 && TILE_POINTS <= 32, "a list entry packs (lane, slot) into 14 bits");
 
 /// Segments of the half-shell stencil of a unit. Order: the unit's own row
 /// first (its own cells, then the n_search[0] cells after them), then the rows
@@ -1272,7 +1272,7 @@ __device__ __forceinline__ void store_pairs(
         }
     }
     if (out.shifts != nullptr) {
-        int* buffer = sh.shift_out[warp];
+        int* buffer = reinterpret_cast<int*>(sh.transpose[warp]);
         buffer[3 * lane + 0] = s0;
         buffer[3 * lane + 1] = s1;
         buffer[3 * lane + 2] = s2;
@@ -1285,10 +1285,11 @@ __device__ __forceinline__ void store_pairs(
                 dst[w] = buffer[w];
             }
         }
+        __syncwarp();
     }
     if (out.vectors != nullptr && out.values_float) {
         // fp32 output: rounded once from the fp64 result
-        float* buffer = reinterpret_cast<float*>(sh.vector_out[warp]);
+        float* buffer = reinterpret_cast<float*>(sh.transpose[warp]);
         buffer[3 * lane + 0] = static_cast<float>(vx);
         buffer[3 * lane + 1] = static_cast<float>(vy);
         buffer[3 * lane + 2] = static_cast<float>(vz);
@@ -1302,7 +1303,7 @@ __device__ __forceinline__ void store_pairs(
             }
         }
     } else if (out.vectors != nullptr) {
-        double* buffer = sh.vector_out[warp];
+        double* buffer = sh.transpose[warp];
         buffer[3 * lane + 0] = vx;
         buffer[3 * lane + 1] = vy;
         buffer[3 * lane + 2] = vz;
@@ -1317,6 +1318,82 @@ __device__ __forceinline__ void store_pairs(
         }
     }
     __syncwarp();
+}
+
+/// Full lists: lane l holds hit l and writes both orientations as the two
+/// consecutive elements first + 2 l (i, j, S, d, v) and first + 2 l + 1
+/// (j, i, -S, d, -v). `first` is even and the arrays are aligned (checked by
+/// the launch wrapper), so a lane stores its 32 bytes of indices and 16 bytes
+/// of distances at once, and the 24 + 48 bytes of shifts and vectors leave as
+/// 8- and 16-byte pieces of one contiguous span after a pass through shared
+/// memory.
+__device__ __forceinline__ void store_both(
+    FusedShared& sh, const PairOutput& out, int warp, int lane, unsigned long long first, int n_valid, unsigned long long a,
+    unsigned long long b, int s0, int s1, int s2, double d, double vx, double vy, double vz
+) {
+    const unsigned long long mine = first + 2 * lane;
+    if (lane < n_valid) {
+        unsigned long long* dst = out.pairs + 2 * mine;
+        asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(dst), "l"(a), "l"(b), "l"(b), "l"(a) : "memory");
+        if (out.distances != nullptr) {
+            if (out.values_float) {
+                const float df = static_cast<float>(d);
+                *reinterpret_cast<float2*>(reinterpret_cast<float*>(out.distances) + mine) = make_float2(df, df);
+            } else {
+                *reinterpret_cast<double2*>(out.distances + mine) = make_double2(d, d);
+            }
+        }
+    }
+    if (out.shifts != nullptr) {
+        int2* buffer = reinterpret_cast<int2*>(sh.transpose[warp]);
+        buffer[3 * lane + 0] = make_int2(s0, s1);
+        buffer[3 * lane + 1] = make_int2(s2, -s0);
+        buffer[3 * lane + 2] = make_int2(-s1, -s2);
+        __syncwarp();
+        int2* dst = reinterpret_cast<int2*>(out.shifts + 3 * first);
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            const int w = k * 32 + lane;
+            if (w < 3 * n_valid) {
+                dst[w] = buffer[w];
+            }
+        }
+        __syncwarp();
+    }
+    if (out.vectors != nullptr && out.values_float) {
+        const float fx = static_cast<float>(vx);
+        const float fy = static_cast<float>(vy);
+        const float fz = static_cast<float>(vz);
+        float2* buffer = reinterpret_cast<float2*>(sh.transpose[warp]);
+        buffer[3 * lane + 0] = make_float2(fx, fy);
+        buffer[3 * lane + 1] = make_float2(fz, -fx);
+        buffer[3 * lane + 2] = make_float2(-fy, -fz);
+        __syncwarp();
+        float2* dst = reinterpret_cast<float2*>(reinterpret_cast<float*>(out.vectors) + 3 * first);
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            const int w = k * 32 + lane;
+            if (w < 3 * n_valid) {
+                dst[w] = buffer[w];
+            }
+        }
+        __syncwarp();
+    } else if (out.vectors != nullptr) {
+        double2* buffer = reinterpret_cast<double2*>(sh.transpose[warp]);
+        buffer[3 * lane + 0] = make_double2(vx, vy);
+        buffer[3 * lane + 1] = make_double2(vz, -vx);
+        buffer[3 * lane + 2] = make_double2(-vy, -vz);
+        __syncwarp();
+        double2* dst = reinterpret_cast<double2*>(out.vectors + 3 * first);
+#pragma unroll
+        for (int k = 0; k < 3; k++) {
+            const int w = k * 32 + lane;
+            if (w < 3 * n_valid) {
+                dst[w] = buffer[w];
+            }
+        }
+        __syncwarp();
+    }
 }
 
 template <bool FULL, bool SLAB>
@@ -1577,12 +1654,12 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                     const int task = task0 + k;
                                     unsigned word = task_word[k];
                                     // task = word index * 32 + home lane
-                                    const unsigned code = (static_cast<unsigned>(task & 31) << 16) | (static_cast<unsigned>(task >> 5) << 5);
+                                    const unsigned code = (static_cast<unsigned>(task & 31) << 9) | (static_cast<unsigned>(task >> 5) << 5);
                                     while (word != 0) {
                                         const int b = __ffs(word) - 1;
                                         word &= word - 1;
                                         if (position >= 0 && position < FUSED_LIST) {
-                                            sh.list[position] = code | b;
+                                            sh.list[position] = static_cast<unsigned short>(code | b);
                                         }
                                         position++;
                                     }
@@ -1591,25 +1668,43 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                             __syncthreads();
 
                             const int in_round = min(FUSED_LIST, total_hits - round0);
+                            // both orientations side by side when the claim and the arrays allow it
+                            const bool interleave = FULL && write_forward && write_reverse && out.interleave_ok && (claim & 1ull) == 0;
                             for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
                                 const int n_valid = min(32, in_round - chunk0);
                                 double vx = 0, vy = 0, vz = 0, d = 0;
                                 int s0 = 0, s1 = 0, s2 = 0;
-                                unsigned long long index_i = 0, index_j = 0;
+                                int h = 0, s = 0;
                                 if (lane < n_valid) {
                                     const unsigned entry = sh.list[chunk0 + lane];
-                                    const int h = entry >> 16;
-                                    const int s = entry & 0xffff;
+                                    h = entry >> 9;
+                                    s = entry & 511;
                                     s0 = sh.s[0][s] + sh.home_shift[0][h];
                                     s1 = sh.s[1][s] + sh.home_shift[1][h];
                                     s2 = sh.s[2][s] + sh.home_shift[2][h];
-                                    const double d2 = exact_pair(
+                                }
+                                double d2;
+                                if (__any_sync(0xffffffffu, (s0 | s1 | s2) != 0)) {
+                                    d2 = exact_pair(
                                         plan, sh.home_pos[0][h], sh.home_pos[1][h], sh.home_pos[2][h], sh.x[s], sh.y[s], sh.z[s], s0, s1, s2,
                                         vx, vy, vz
                                     );
-                                    d = __dsqrt_rn(d2);
-                                    index_i = static_cast<unsigned long long>(sh.home_index[h]);
-                                    index_j = static_cast<unsigned long long>(sh.j[s]);
+                                } else {
+                                    // no image shift in this chunk: the shift term is the signed zero the
+                                    // reference's arithmetic gives for S = 0
+                                    vx = __dadd_rn(__dsub_rn(sh.x[s], sh.home_pos[0][h]), plan.zero_shift[0]);
+                                    vy = __dadd_rn(__dsub_rn(sh.y[s], sh.home_pos[1][h]), plan.zero_shift[1]);
+                                    vz = __dadd_rn(__dsub_rn(sh.z[s], sh.home_pos[2][h]), plan.zero_shift[2]);
+                                    d2 = __dadd_rn(__dadd_rn(__dmul_rn(vx, vx), __dmul_rn(vy, vy)), __dmul_rn(vz, vz));
+                                }
+                                d = __dsqrt_rn(d2);
+                                unsigned long long index_i = static_cast<unsigned long long>(sh.home_index[h]);
+                                unsigned long long index_j = static_cast<unsigned long long>(sh.j[s]);
+                                if (interleave) {
+                                    store_both(
+                                        sh, out, warp, lane, claim + 2ull * (round0 + chunk0), n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz
+                                    );
+                                    continue;
                                 }
                                 const unsigned long long first = claim + round0 + chunk0;
                                 if (FULL) {
@@ -1778,6 +1873,11 @@ void launch_pairs(
     const int per_sm = 8;
     int grid = pair_grid((plan.n_units + unit_run - 1) / unit_run, per_sm);
     const size_t smem = sizeof(FusedShared);
+    // paired stores of full lists: 32 bytes of indices, 16 of distances / vectors, 8 of shifts
+    // (half of that for float values); null arrays are not written
+    const auto aligned = [](const void* pointer, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(pointer) % bytes == 0; };
+    const uintptr_t value_bytes = out.values_float ? 8 : 16;
+    out.interleave_ok = aligned(out.pairs, 32) && aligned(out.shifts, 8) && aligned(out.distances, value_bytes) && aligned(out.vectors, value_bytes);
     if (plan.window_axis >= 0) {
         if (plan.full) {
             pairs_kernel<true, true><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, global_index);

@@ -51,6 +51,7 @@ struct PairOutput {
     double* distances;         // [total]
     double* vectors;           // [total][3]
     int values_float;          // distances / vectors are float arrays (fp32 entry point); decisions stay fp64
+    int interleave_ok;         // set by launch_pairs: the arrays are aligned for the paired stores of full lists
 };
 
 /// Input coordinates: double (the reference's C API) or float (fp32 entry

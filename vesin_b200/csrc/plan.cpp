@@ -77,6 +77,10 @@ static void update_screen(GridPlan& plan, double cutoff) {
         }
         reach += cells * len;
     }
+    for (int c = 0; c < 3; c++) {
+        volatile double zero = 0.0; // keeps the three products and two sums as written
+        plan.zero_shift[c] = (zero * plan.H[0][c] + zero * plan.H[1][c]) + zero * plan.H[2][c];
+    }
     const double eps = 5.9604644775390625e-08; // 2^-24
     double c = cutoff * 1.01;
     double band = 4.0 * eps * (2.0 * std::sqrt(3.0) * c * (2.0 * reach + c) + 3.0 * c * c);

@@ -53,6 +53,9 @@ struct GridPlan {
     int32_t window_axis;
     int32_t n_owned;
 
+    /// (0 * H[0][c] + 0 * H[1][c]) + 0 * H[2][c]: the signed zero the reference's
+    /// shift arithmetic adds to r_j - r_i when S = 0
+    double zero_shift[3];
     double cutoff2;   // cutoff * cutoff in fp64: the exact predicate's bound
     float cutoff2_lo; // fp32 screen: below this a candidate is surely inside
     float cutoff2_hi; // fp32 screen: above this a candidate is surely outside
