@@ -51,7 +51,9 @@ __device__ __forceinline__ unsigned lanemask_lt() {
 
 /// Exclusive scan of one value per thread over the whole CTA (256 threads).
 /// `warp_sums` is CTA_WARPS + 1 ints of shared memory; returns the exclusive
-/// prefix and stores the CTA total in warp_sums[CTA_WARPS].
+/// prefix and stores the CTA total in warp_sums[CTA_WARPS] (every thread
+/// stores the same value, so the total is visible to the caller at once).
+/// One barrier inside; two calls must be separated by another barrier.
 __device__ __forceinline__ int block_exclusive_scan(int value, int* warp_sums) {
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -67,25 +69,56 @@ __device__ __forceinline__ int block_exclusive_scan(int value, int* warp_sums) {
         warp_sums[warp] = inclusive;
     }
     __syncthreads();
-    if (warp == 0) {
-        int total = (lane < CTA_WARPS) ? warp_sums[lane] : 0;
-        int scan = total;
+    int before = 0;
+    int total = 0;
 #pragma unroll
-        for (int offset = 1; offset < CTA_WARPS; offset <<= 1) {
-            int up = __shfl_up_sync(FULL_MASK, scan, offset);
-            if (lane >= offset) {
-                scan += up;
-            }
-        }
-        if (lane < CTA_WARPS) {
-            warp_sums[lane] = scan - total; // exclusive prefix of the warp
-        }
-        if (lane == CTA_WARPS - 1) {
-            warp_sums[CTA_WARPS] = scan;
+    for (int w = 0; w < CTA_WARPS; w++) {
+        const int sum = warp_sums[w];
+        total += sum;
+        if (w < warp) {
+            before += sum;
         }
     }
-    __syncthreads();
-    return warp_sums[warp] + inclusive - value;
+    if (lane == 0) {
+        warp_sums[CTA_WARPS] = total;
+    }
+    __syncwarp();
+    return before + inclusive - value;
+}
+
+/// Position of the n-th (counting from 0) set bit of w. For a word with n or
+/// fewer set bits the result is some position below 32.
+__device__ __forceinline__ int select_bit(unsigned w, int n) {
+    int pos = 0;
+    int c = __popc(w & 0xffffu);
+    if (n >= c) {
+        n -= c;
+        pos = 16;
+        w >>= 16;
+    }
+    c = __popc(w & 0xffu);
+    if (n >= c) {
+        n -= c;
+        pos += 8;
+        w >>= 8;
+    }
+    c = __popc(w & 0xfu);
+    if (n >= c) {
+        n -= c;
+        pos += 4;
+        w >>= 4;
+    }
+    c = __popc(w & 0x3u);
+    if (n >= c) {
+        n -= c;
+        pos += 2;
+        w >>= 2;
+    }
+    c = static_cast<int>(w & 1u);
+    if (n >= c) {
+        pos += 1;
+    }
+    return pos;
 }
 
 // ---------------------------------------------------------------------------
@@ -1142,6 +1175,25 @@ __global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
 // exact total and runs the pass again.
 // ---------------------------------------------------------------------------
 
+// Optional instrumentation (-DVESIN_B200_PHASE_CLOCKS): thread 0 of every CTA of
+// the fused pass adds the clock cycles it spends in each phase to a global
+// table, read with vesin_b200_debug_phase_clocks(). Off in normal builds.
+#ifdef VESIN_B200_PHASE_CLOCKS
+__device__ unsigned long long g_phase_clocks[16];
+#define PHASE_CLOCK_START() long long phase_last_ = clock64()
+#define PHASE_MARK(k)                                                                          \
+    do {                                                                                       \
+        if (threadIdx.x == 0) {                                                                \
+            const long long phase_now_ = clock64();                                            \
+            atomicAdd(&g_phase_clocks[k], static_cast<unsigned long long>(phase_now_ - phase_last_)); \
+            phase_last_ = phase_now_;                                                          \
+        }                                                                                      \
+    } while (0)
+#else
+#define PHASE_CLOCK_START()
+#define PHASE_MARK(k)
+#endif
+
 constexpr int FUSED_BATCH = 512;
 constexpr int DEFAULT_UNIT_RUN = 4; // neighbouring units handled back to back by one CTA
 constexpr int FUSED_WORDS = FUSED_BATCH / 32;
@@ -1161,17 +1213,21 @@ struct FusedShared {
     int home_index[TILE_POINTS];
     unsigned mask[FUSED_WORDS * TILE_POINTS]; // [word][lane]
     unsigned short list[FUSED_LIST];          // (home lane << 9) | slot in batch
+    unsigned short prefix[CTA_THREADS];       // hits of the tasks of the threads before this one
     double transpose[CTA_WARPS][192];         // per warp: 64 shifts, then 64 vectors, on their way to coalesced stores
     unsigned owned_word[FUSED_WORDS]; // slab decomposition: which slots of a word hold owned points
     unsigned long long claim;
-    int home_row_slots;
 };
+static_assert(TILE_POINTS * FUSED_BATCH < 65536, "hit counts of a tile are kept in 16 bits");
 static_assert(FUSED_BATCH <= 512 && TILE_POINTS <= 32, "a list entry packs (lane, slot) into 14 bits");
 
 /// Segments of the half-shell stencil of a unit. Order: the unit's own row
 /// first (its own cells, then the n_search[0] cells after them), then the rows
-/// above. Returns the slots of the group; ends with a __syncthreads().
-__device__ __forceinline__ int setup_half_segments(const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int group, FusedShared& sh) {
+/// above. Returns the slots of the group and how many of them belong to the
+/// unit's own row; ends with a __syncthreads().
+__device__ __forceinline__ int setup_half_segments(
+    const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int group, FusedShared& sh, int& home_row_slots
+) {
     SegmentTable& table = sh.table;
     const int t = threadIdx.x;
     const int own_row = unit.cells + plan.n_search[0];
@@ -1207,10 +1263,13 @@ __device__ __forceinline__ int setup_half_segments(const GridPlan& plan, const i
             bool valid = true;
 #pragma unroll
             for (int k = 0; k < 3; k++) {
+                const bool outside = nb[k] < 0 || nb[k] >= plan.n_cells[k];
                 if (plan.periodic[k] && k != plan.window_axis) {
-                    q[k] = floor_div(nb[k], plan.n_cells[k]);
-                    nb[k] -= q[k] * plan.n_cells[k];
-                } else if (nb[k] < 0 || nb[k] >= plan.n_cells[k]) {
+                    if (outside) {
+                        q[k] = floor_div(nb[k], plan.n_cells[k]);
+                        nb[k] -= q[k] * plan.n_cells[k];
+                    }
+                } else if (outside) {
                     valid = false;
                 }
             }
@@ -1242,15 +1301,8 @@ __device__ __forceinline__ int setup_half_segments(const GridPlan& plan, const i
         table.slot0[SEG_MAX] = total;
     }
     __syncthreads();
-    if (t == 0) {
-        // slots of this group that belong to the unit's own row
-        int own = 0;
-        if (group == 0) {
-            own = table.slot0[min(own_row, SEG_MAX)];
-        }
-        sh.home_row_slots = own;
-    }
-    __syncthreads();
+    // slots of this group that belong to the unit's own row
+    home_row_slots = (group == 0) ? table.slot0[min(own_row, SEG_MAX)] : 0;
     return total;
 }
 
@@ -1412,6 +1464,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     if (header->status & STATUS_ABORT_MASK) {
         return; // the validation kernel refused the plan: the host will redo the build
     }
+    PHASE_CLOCK_START();
 
     // Consecutive units share two thirds of their stencil: a CTA takes runs of
     // UNIT_RUN neighbouring units so that most of its loads hit in L1.
@@ -1459,9 +1512,11 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         (unit.c2 + 0.5) * plan.cell_vec[2][c];
         }
 
+        PHASE_MARK(0); // unit setup
         for (int g = 0; g < n_groups; g++) {
-            const int group_total = setup_half_segments(plan, cell_start, unit, g, sh);
-            const int home_row_slots = sh.home_row_slots;
+            int home_row_slots;
+            const int group_total = setup_half_segments(plan, cell_start, unit, g, sh, home_row_slots);
+            PHASE_MARK(1); // segments
             bool all_owned = true;
             if (SLAB) {
                 int segment_ok = 1;
@@ -1517,7 +1572,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                 }
 
                 for (int tile = 0; tile < n_tiles; tile++) {
+                    PHASE_MARK(2); // staging (first tile) or the end of the previous tile
                     __syncthreads(); // staging done; previous tile done with mask / list / home
+                    PHASE_MARK(3); // wait
                     const int il = tile * TILE_POINTS + lane;
                     const bool valid = il < unit.n_home;
                     const size_t pi = static_cast<size_t>(unit.begin) + (valid ? il : 0);
@@ -1589,7 +1646,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         }
                         sh.mask[w * TILE_POINTS + lane] = inside;
                     }
+                    PHASE_MARK(4); // home points + decisions
                     __syncthreads();
+                    PHASE_MARK(5); // wait
 
                     // ---- compact the hit bits and write. Tasks = words in [word][lane]
                     // order. One pass writes both orientations (full) or the kept one
@@ -1612,24 +1671,25 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                             __syncthreads(); // list, claim and scan scratch of the first pass are free again
                         }
                         const int n_tasks = TILE_POINTS * batch_words;
-                        const int task0 = threadIdx.x * FUSED_TASKS;
-                        unsigned task_word[FUSED_TASKS];
+                        // word of hit bits of a task (= word index * 32 + home lane)
+                        const auto task_word = [&](int task) -> unsigned {
+                            unsigned word = (task < n_tasks) ? sh.mask[task] : 0u;
+                            if (SLAB && only_owned_candidates) {
+                                word &= sh.owned_word[(task >> 5) & (FUSED_WORDS - 1)];
+                            }
+                            return word;
+                        };
                         int my_hits = 0;
 #pragma unroll
                         for (int k = 0; k < FUSED_TASKS; k++) {
-                            const int task = task0 + k;
-                            unsigned word = (task < n_tasks) ? sh.mask[task] : 0u;
-                            if (SLAB && only_owned_candidates && task < n_tasks) {
-                                word &= sh.owned_word[task >> 5];
-                            }
-                            task_word[k] = word;
-                            my_hits += __popc(word);
+                            my_hits += __popc(task_word(threadIdx.x * FUSED_TASKS + k));
                         }
                         const int my_first = block_exclusive_scan(my_hits, sh.table.scan_tmp);
                         const int total_hits = sh.table.scan_tmp[CTA_WARPS];
                         if (total_hits == 0) {
                             continue;
                         }
+                        sh.prefix[threadIdx.x] = static_cast<unsigned short>(my_first);
                         const int per_hit = (write_forward ? 1 : 0) + (write_reverse ? 1 : 0);
                         if (threadIdx.x == 0) {
                             // claim the output range of this block of pairs
@@ -1638,6 +1698,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                             sh.claim = (first + wanted <= capacity) ? first : ~0ull;
                         }
                         __syncthreads();
+                        PHASE_MARK(6); // count, scan, claim
                         const unsigned long long claim = sh.claim;
                         if (claim == ~0ull) {
                             continue; // counted, not written: the host will grow the arrays
@@ -1647,27 +1708,55 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                             if (round0 != 0) {
                                 __syncthreads(); // previous round consumed
                             }
+                            const int in_round = min(FUSED_LIST, total_hits - round0);
                             {
-                                int position = my_first - round0;
+                                // List of the hits of this round, in task order. Every thread writes the
+                                // same number of consecutive entries whatever the hits of its own tasks:
+                                // it finds the task that holds its first entry in the scanned counts,
+                                // skips the bits before it and walks on from there.
+                                const int quota = (in_round + CTA_THREADS - 1) / CTA_THREADS;
+                                int position = round0 + threadIdx.x * quota;
+                                const int stop = min(position + quota, round0 + in_round);
+                                if (position < stop) {
+                                    int lo = 0;
+                                    int hi = CTA_THREADS;
 #pragma unroll
-                                for (int k = 0; k < FUSED_TASKS; k++) {
-                                    const int task = task0 + k;
-                                    unsigned word = task_word[k];
-                                    // task = word index * 32 + home lane
-                                    const unsigned code = (static_cast<unsigned>(task & 31) << 9) | (static_cast<unsigned>(task >> 5) << 5);
-                                    while (word != 0) {
-                                        const int b = __ffs(word) - 1;
-                                        word &= word - 1;
-                                        if (position >= 0 && position < FUSED_LIST) {
-                                            sh.list[position] = static_cast<unsigned short>(code | b);
+                                    for (int step = 0; step < 8; step++) {
+                                        const int mid = (lo + hi) >> 1;
+                                        if (static_cast<int>(sh.prefix[mid]) <= position) {
+                                            lo = mid;
+                                        } else {
+                                            hi = mid;
                                         }
-                                        position++;
+                                    }
+                                    int skip = position - static_cast<int>(sh.prefix[lo]);
+                                    int task = lo * FUSED_TASKS;
+                                    unsigned word = task_word(task);
+#pragma unroll
+                                    for (int k = 1; k < FUSED_TASKS; k++) {
+                                        const int count = __popc(word);
+                                        if (skip >= count) {
+                                            skip -= count;
+                                            task++;
+                                            word = task_word(task);
+                                        }
+                                    }
+                                    word &= 0xffffffffu << select_bit(word, skip);
+                                    for (; position < stop; position++) {
+                                        while (word == 0 && task + 1 < n_tasks) {
+                                            task++;
+                                            word = task_word(task);
+                                        }
+                                        const int bit = __ffs(word) - 1;
+                                        word &= word - 1;
+                                        sh.list[position - round0] =
+                                            static_cast<unsigned short>(((task & 31) << 9) | ((task >> 5) << 5) | (bit & 31));
                                     }
                                 }
                             }
                             __syncthreads();
+                            PHASE_MARK(7); // list of hits
 
-                            const int in_round = min(FUSED_LIST, total_hits - round0);
                             // both orientations side by side when the claim and the arrays allow it
                             const bool interleave = FULL && write_forward && write_reverse && out.interleave_ok && (claim & 1ull) == 0;
                             for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
@@ -1734,15 +1823,28 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                     store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
                                 }
                             }
+                            PHASE_MARK(8); // emission
                         }
                     }
                 }
                 __syncthreads();
+                PHASE_MARK(9); // wait
             }
         }
     }
 }
 
+} // namespace
+#ifdef VESIN_B200_PHASE_CLOCKS
+extern "C" __attribute__((visibility("default"))) void vesin_b200_debug_phase_clocks(unsigned long long* out, int reset) {
+    cudaMemcpyFromSymbol(out, g_phase_clocks, sizeof(g_phase_clocks));
+    if (reset) {
+        const unsigned long long zeros[16] = {0};
+        cudaMemcpyToSymbol(g_phase_clocks, zeros, sizeof(zeros));
+    }
+}
+#endif
+namespace {
 int pair_grid(int n_units, int per_sm) {
     int device = 0;
     int sms = 148;
