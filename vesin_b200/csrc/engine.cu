@@ -517,6 +517,9 @@ void neighbors(
             size_t capacity = common_capacity(ws, options);
             size_t total = 0;
             bool refused = false;
+            // arrays of the minimum size (a list that was never filled) cannot hold the pairs
+            // of a large system: the first pass then only counts (capacity 0)
+            bool count_only = capacity <= 256 && n_points >= 4096;
             for (int attempt = 0;; attempt++) {
                 PairOutput out{
                     reinterpret_cast<unsigned long long*>(list.pairs),
@@ -525,8 +528,9 @@ void neighbors(
                     reinterpret_cast<double*>(list.vectors),
                     float_io ? 1 : 0,
                 };
+                const size_t pass_capacity = count_only ? 0 : capacity;
                 timer.begin(VesinB200StageEmit);
-                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, nullptr, stream);
+                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, pass_capacity, ws.d_header, nullptr, stream);
                 timer.end(VesinB200StageEmit);
                 VB200_CUDA(cudaGetLastError());
                 read_header(ws);
@@ -542,14 +546,17 @@ void neighbors(
                 if (total > n_points * pair_limit_per_point) {
                     throw pair_limit_error();
                 }
-                if (total <= capacity) {
+                if (total <= pass_capacity) {
                     break;
                 }
                 if (attempt >= 2) {
                     throw std::runtime_error("internal error: the pair total kept changing between passes");
                 }
-                set_outputs(list, ws, options, total + total / 16 + 256);
-                capacity = common_capacity(ws, options);
+                count_only = false;
+                if (total > capacity) {
+                    set_outputs(list, ws, options, total + total / 16 + 256);
+                    capacity = common_capacity(ws, options);
+                }
                 VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, sizeof(unsigned long long), stream));
             }
             if (refused) {

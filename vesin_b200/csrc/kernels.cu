@@ -1206,14 +1206,12 @@ struct FusedShared {
     double x[FUSED_BATCH];       // original positions of the candidates
     double y[FUSED_BATCH];
     double z[FUSED_BATCH];
-    int j[FUSED_BATCH];
-    int s[3][FUSED_BATCH];       // q - wrap shift of the candidate
+    int4 sj[FUSED_BATCH];        // x, y, z: q - wrap shift of the candidate; w: its index
     double home_pos[3][TILE_POINTS];
-    int home_shift[3][TILE_POINTS];
-    int home_index[TILE_POINTS];
+    int4 home_sj[TILE_POINTS];   // x, y, z: wrap shift of the home point; w: its index
     unsigned mask[FUSED_WORDS * TILE_POINTS]; // [word][lane]
     unsigned short list[FUSED_LIST];          // (home lane << 9) | slot in batch
-    unsigned short prefix[CTA_THREADS];       // hits of the tasks of the threads before this one
+    unsigned short prefix[CTA_THREADS];       // hits of the tasks of the threads before this one in its warp
     double transpose[CTA_WARPS][192];         // per warp: 64 shifts, then 64 vectors, on their way to coalesced stores
     unsigned owned_word[FUSED_WORDS]; // slab decomposition: which slots of a word hold owned points
     unsigned long long claim;
@@ -1551,17 +1549,16 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     sh.x[s] = px;
                     sh.y[s] = py;
                     sh.z[s] = pz;
+                    int index_j;
                     if (SLAB) {
-                        sh.j[s] = static_cast<int>(global_index[sorted.index[p]]);
+                        index_j = static_cast<int>(global_index[sorted.index[p]]);
                         if (sh.table.self_ok[t]) {
                             atomicOr(&sh.owned_word[s >> 5], 1u << (s & 31));
                         }
                     } else {
-                        sh.j[s] = sorted.index[p];
+                        index_j = sorted.index[p];
                     }
-                    sh.s[0][s] = r0;
-                    sh.s[1][s] = r1;
-                    sh.s[2][s] = r2;
+                    sh.sj[s] = make_int4(r0, r1, r2, index_j);
                     const float fx = static_cast<float>(px + (r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0]) - centre[0]);
                     const float fy = static_cast<float>(py + (r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1]) - centre[1]);
                     const float fz = static_cast<float>(pz + (r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2]) - centre[2]);
@@ -1577,32 +1574,53 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     PHASE_MARK(3); // wait
                     const int il = tile * TILE_POINTS + lane;
                     const bool valid = il < unit.n_home;
-                    const size_t pi = static_cast<size_t>(unit.begin) + (valid ? il : 0);
-                    const double rix = sorted.pos[3 * pi + 0];
-                    const double riy = sorted.pos[3 * pi + 1];
-                    const double riz = sorted.pos[3 * pi + 2];
-                    const int si0 = sorted.shift[3 * pi + 0];
-                    const int si1 = sorted.shift[3 * pi + 1];
-                    const int si2 = sorted.shift[3 * pi + 2];
+                    // The home points are the first candidates of a unit (its own cells open the
+                    // stencil): while they sit in the staged batch they are read from there.
+                    const bool home_staged = (g == 0) && (batch0 == 0) && (tile * TILE_POINTS + TILE_POINTS <= FUSED_BATCH);
+                    // Lanes without a point carry NaN: every comparison fails.
+                    const float nan = __int_as_float(0x7fc00000);
+                    double rix, riy, riz;
+                    int si0, si1, si2, index_i;
+                    float xi, yi, zi, an;
+                    if (home_staged) {
+                        const int slot = valid ? il : 0;
+                        rix = sh.x[slot];
+                        riy = sh.y[slot];
+                        riz = sh.z[slot];
+                        const int4 packed = sh.sj[slot]; // own cells have no image shift: q = 0
+                        si0 = -packed.x;
+                        si1 = -packed.y;
+                        si2 = -packed.z;
+                        index_i = packed.w;
+                        const float4 local = sh.near32[slot];
+                        xi = valid ? local.x : nan;
+                        yi = valid ? local.y : nan;
+                        zi = valid ? local.z : nan;
+                        an = local.w;
+                    } else {
+                        const size_t pi = static_cast<size_t>(unit.begin) + (valid ? il : 0);
+                        rix = sorted.pos[3 * pi + 0];
+                        riy = sorted.pos[3 * pi + 1];
+                        riz = sorted.pos[3 * pi + 2];
+                        si0 = sorted.shift[3 * pi + 0];
+                        si1 = sorted.shift[3 * pi + 1];
+                        si2 = sorted.shift[3 * pi + 2];
+                        index_i = SLAB ? static_cast<int>(global_index[sorted.index[pi]]) : sorted.index[pi];
+                        xi = valid ? static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - centre[0]) : nan;
+                        yi = valid ? static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - centre[1]) : nan;
+                        zi = valid ? static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - centre[2]) : nan;
+                        an = xi * xi + yi * yi + zi * zi;
+                    }
                     if (warp == 0) {
-                        sh.home_index[lane] = SLAB ? static_cast<int>(global_index[sorted.index[pi]]) : sorted.index[pi];
                         sh.home_pos[0][lane] = rix;
                         sh.home_pos[1][lane] = riy;
                         sh.home_pos[2][lane] = riz;
-                        sh.home_shift[0][lane] = si0;
-                        sh.home_shift[1][lane] = si1;
-                        sh.home_shift[2][lane] = si2;
+                        sh.home_sj[lane] = make_int4(si0, si1, si2, index_i);
                     }
                     // d2 = |c|^2 + (|i|^2 - 2 c.i): one add and three fused multiply-adds per candidate.
-                    // Lanes without a point carry NaN: every comparison fails.
-                    const float nan = __int_as_float(0x7fc00000);
-                    const float xi = valid ? static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - centre[0]) : nan;
-                    const float yi = valid ? static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - centre[1]) : nan;
-                    const float zi = valid ? static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - centre[2]) : nan;
                     const float ax = -2.0f * xi;
                     const float ay = -2.0f * yi;
                     const float az = -2.0f * zi;
-                    const float an = xi * xi + yi * yi + zi * zi;
 
                     for (int w = warp; w < batch_words; w += CTA_WARPS) {
                         unsigned inside = 0; // surely inside the cutoff
@@ -1637,8 +1655,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                             band &= band - 1;
                             const int s = w * 32 + b;
                             double vx, vy, vz;
+                            const int4 cand = sh.sj[s];
                             const double d2_exact = exact_pair(
-                                plan, rix, riy, riz, sh.x[s], sh.y[s], sh.z[s], sh.s[0][s] + si0, sh.s[1][s] + si1, sh.s[2][s] + si2, vx, vy, vz
+                                plan, rix, riy, riz, sh.x[s], sh.y[s], sh.z[s], cand.x + si0, cand.y + si1, cand.z + si2, vx, vy, vz
                             );
                             if (d2_exact < plan.cutoff2) {
                                 inside |= 1u << b;
@@ -1684,25 +1703,41 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         for (int k = 0; k < FUSED_TASKS; k++) {
                             my_hits += __popc(task_word(threadIdx.x * FUSED_TASKS + k));
                         }
-                        const int my_first = block_exclusive_scan(my_hits, sh.table.scan_tmp);
-                        const int total_hits = sh.table.scan_tmp[CTA_WARPS];
+                        // scan of the hit counts: inside the warp with shuffles, across warps by
+                        // reading the eight warp totals after one barrier
+                        int inclusive = my_hits;
+#pragma unroll
+                        for (int offset = 1; offset < 32; offset <<= 1) {
+                            const int up = __shfl_up_sync(FULL_MASK, inclusive, offset);
+                            if (lane >= offset) {
+                                inclusive += up;
+                            }
+                        }
+                        sh.prefix[threadIdx.x] = static_cast<unsigned short>(inclusive - my_hits);
+                        if (lane == 31) {
+                            sh.table.scan_tmp[warp] = inclusive;
+                        }
+                        __syncthreads();
+                        int total_hits = 0;
+#pragma unroll
+                        for (int w = 0; w < CTA_WARPS; w++) {
+                            total_hits += sh.table.scan_tmp[w];
+                        }
                         if (total_hits == 0) {
                             continue;
                         }
-                        sh.prefix[threadIdx.x] = static_cast<unsigned short>(my_first);
                         const int per_hit = (write_forward ? 1 : 0) + (write_reverse ? 1 : 0);
+                        // claim the output range of this block of pairs; the answer is only
+                        // needed after the list below has been built
+                        const unsigned long long wanted = static_cast<unsigned long long>(total_hits) * per_hit;
+                        unsigned long long claimed = 0;
                         if (threadIdx.x == 0) {
-                            // claim the output range of this block of pairs
-                            const unsigned long long wanted = static_cast<unsigned long long>(total_hits) * per_hit;
-                            const unsigned long long first = atomicAdd(&header->pair_cursor, wanted);
-                            sh.claim = (first + wanted <= capacity) ? first : ~0ull;
+                            claimed = atomicAdd(&header->pair_cursor, wanted);
                         }
-                        __syncthreads();
-                        PHASE_MARK(6); // count, scan, claim
-                        const unsigned long long claim = sh.claim;
-                        if (claim == ~0ull) {
-                            continue; // counted, not written: the host will grow the arrays
+                        if (capacity == 0) {
+                            continue; // counting pass: the host sizes the arrays from the cursor
                         }
+                        unsigned long long claim = 0;
 
                         for (int round0 = 0; round0 < total_hits; round0 += FUSED_LIST) {
                             if (round0 != 0) {
@@ -1712,24 +1747,41 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                             {
                                 // List of the hits of this round, in task order. Every thread writes the
                                 // same number of consecutive entries whatever the hits of its own tasks:
-                                // it finds the task that holds its first entry in the scanned counts,
-                                // skips the bits before it and walks on from there.
+                                // it finds the task that holds its first entry in the scanned counts
+                                // (first the warp, then the thread), skips the bits before it and walks
+                                // on from there.
                                 const int quota = (in_round + CTA_THREADS - 1) / CTA_THREADS;
                                 int position = round0 + threadIdx.x * quota;
                                 const int stop = min(position + quota, round0 + in_round);
                                 if (position < stop) {
-                                    int lo = 0;
-                                    int hi = CTA_THREADS;
+                                    int owner_warp = 0;
+                                    int before = 0; // hits of the warps before the owner
+                                    {
+                                        int running = 0;
 #pragma unroll
-                                    for (int step = 0; step < 8; step++) {
+                                        for (int w = 0; w < CTA_WARPS - 1; w++) {
+                                            running += sh.table.scan_tmp[w];
+                                            if (running <= position) {
+                                                owner_warp = w + 1;
+                                                before = running;
+                                            }
+                                        }
+                                    }
+                                    const int target = position - before;
+                                    const unsigned short* local = sh.prefix + owner_warp * 32;
+                                    int lo = 0;
+                                    int hi = 32;
+#pragma unroll
+                                    for (int step = 0; step < 5; step++) {
                                         const int mid = (lo + hi) >> 1;
-                                        if (static_cast<int>(sh.prefix[mid]) <= position) {
+                                        if (static_cast<int>(local[mid]) <= target) {
                                             lo = mid;
                                         } else {
                                             hi = mid;
                                         }
                                     }
-                                    int skip = position - static_cast<int>(sh.prefix[lo]);
+                                    int skip = target - static_cast<int>(local[lo]);
+                                    lo += owner_warp * 32;
                                     int task = lo * FUSED_TASKS;
                                     unsigned word = task_word(task);
 #pragma unroll
@@ -1754,24 +1806,34 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                     }
                                 }
                             }
+                            if (round0 == 0 && threadIdx.x == 0) {
+                                sh.claim = (claimed + wanted <= capacity) ? claimed : ~0ull;
+                            }
                             __syncthreads();
                             PHASE_MARK(7); // list of hits
+                            if (round0 == 0) {
+                                claim = sh.claim;
+                            }
+                            if (claim == ~0ull) {
+                                break; // counted, not written: the host will grow the arrays
+                            }
 
                             // both orientations side by side when the claim and the arrays allow it
                             const bool interleave = FULL && write_forward && write_reverse && out.interleave_ok && (claim & 1ull) == 0;
                             for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
                                 const int n_valid = min(32, in_round - chunk0);
                                 double vx = 0, vy = 0, vz = 0, d = 0;
-                                int s0 = 0, s1 = 0, s2 = 0;
                                 int h = 0, s = 0;
                                 if (lane < n_valid) {
                                     const unsigned entry = sh.list[chunk0 + lane];
                                     h = entry >> 9;
                                     s = entry & 511;
-                                    s0 = sh.s[0][s] + sh.home_shift[0][h];
-                                    s1 = sh.s[1][s] + sh.home_shift[1][h];
-                                    s2 = sh.s[2][s] + sh.home_shift[2][h];
                                 }
+                                const int4 cand = sh.sj[s];
+                                const int4 home = sh.home_sj[h];
+                                int s0 = cand.x + home.x;
+                                int s1 = cand.y + home.y;
+                                int s2 = cand.z + home.z;
                                 double d2;
                                 if (__any_sync(0xffffffffu, (s0 | s1 | s2) != 0)) {
                                     d2 = exact_pair(
@@ -1787,8 +1849,8 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                     d2 = __dadd_rn(__dadd_rn(__dmul_rn(vx, vx), __dmul_rn(vy, vy)), __dmul_rn(vz, vz));
                                 }
                                 d = __dsqrt_rn(d2);
-                                unsigned long long index_i = static_cast<unsigned long long>(sh.home_index[h]);
-                                unsigned long long index_j = static_cast<unsigned long long>(sh.j[s]);
+                                unsigned long long index_i = static_cast<unsigned long long>(home.w);
+                                unsigned long long index_j = static_cast<unsigned long long>(cand.w);
                                 if (interleave) {
                                     store_both(
                                         sh, out, warp, lane, claim + 2ull * (round0 + chunk0), n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz
