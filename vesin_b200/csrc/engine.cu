@@ -425,8 +425,19 @@ void neighbors(
 
     for (int round = 0;; round++) {
         timer.begin(VesinB200StageBounds);
-        launch_header_init(ws.d_header, flat_box, periodic, stream);
-        launch_bounds(flat_points, n_points, ws.d_header, stream);
+        bool histogram_zeroed = false;
+        if (speculative) {
+            // the plan is known already: the first kernel also zeroes the cell histogram and
+            // the last block of the bounds kernel checks the plan
+            const size_t cached_cells = static_cast<size_t>(ws.cache.plan.n_cells_total);
+            ws.cell_count.reserve(cached_cells * sizeof(int32_t));
+            launch_header_init(ws.d_header, flat_box, periodic, ws.cell_count.as<int32_t>(), cached_cells, stream);
+            launch_bounds_validate(flat_points, n_points, ws.d_header, ws.cache.box, ws.cache.periodic, ws.cache.plan, stream);
+            histogram_zeroed = true;
+        } else {
+            launch_header_init(ws.d_header, flat_box, periodic, nullptr, 0, stream);
+            launch_bounds(flat_points, n_points, ws.d_header, stream);
+        }
         timer.end(VesinB200StageBounds);
         if (!speculative) {
             if (!header_is_fresh) {
@@ -434,9 +445,9 @@ void neighbors(
                 read_header(ws);
             }
             plan_from_header();
+            launch_validate(ws.d_header, ws.cache.box, ws.cache.periodic, ws.cache.plan, n_points, stream);
         }
         const GridPlan& plan = ws.cache.plan;
-        launch_validate(ws.d_header, ws.cache.box, ws.cache.periodic, plan, n_points, stream);
 
         if (options.algorithm == VesinBruteForce && 2.0 * options.cutoff > min_periodic_face_distance(plan)) {
             // vesin/src/vesin_cuda.cpp:404-409
@@ -473,7 +484,9 @@ void neighbors(
 
         // ---- cell list ----
         timer.begin(VesinB200StageBin);
-        VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
+        if (!histogram_zeroed) {
+            VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
+        }
         launch_bin(
             flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
             ws.cell_count.as<int32_t>(), ws.d_header, stream
@@ -827,7 +840,7 @@ void neighbors_slab(
     const DeviceHeader& header = *ws.h_header;
 
     timer.begin(VesinB200StageBounds);
-    launch_header_init(ws.d_header, RealView{box, 0}, periodic, stream);
+    launch_header_init(ws.d_header, RealView{box, 0}, periodic, nullptr, 0, stream);
     launch_bounds(flat_points, n_points, ws.d_header, stream);
     timer.end(VesinB200StageBounds);
     VB200_CUDA(cudaGetLastError());

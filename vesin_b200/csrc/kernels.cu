@@ -128,7 +128,17 @@ __device__ __forceinline__ int select_bit(unsigned w, int n) {
 // (vesin/src/types.hpp:159-178).
 // ---------------------------------------------------------------------------
 
-__global__ void header_init_kernel(DeviceHeader* header, const RealView box, const bool* periodic) {
+/// Resets the header (block 0) and zeroes `n_zero` counters (all blocks).
+__global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
+    DeviceHeader* header, const RealView box, const bool* periodic, int32_t* __restrict__ zero, size_t n_zero
+) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t k = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; k < n_zero; k += stride) {
+        zero[k] = 0;
+    }
+    if (blockIdx.x != 0) {
+        return;
+    }
     int t = threadIdx.x;
     if (t < 3) {
         header->min_key[t] = ~0ull;
@@ -144,10 +154,85 @@ __global__ void header_init_kernel(DeviceHeader* header, const RealView box, con
         header->mask_cursor = 0;
         header->pair_cursor = 0;
         header->status = 0;
+        header->ticket = 0;
     }
 }
 
-__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const RealView points, size_t n, DeviceHeader* header) {
+// ---------------------------------------------------------------------------
+// validation of a speculative plan
+// The host builds the grid plan from the box, periodicity and bounds it saw at
+// the end of the PREVIOUS build on the same list, and launches the whole build
+// without waiting for a read-back. The check (the last block of the bounds kernel, or a kernel of its own) compares that assumption with
+// what is in device memory now; when it does not hold it sets
+// STATUS_PLAN_STALE, every later kernel of the build returns at once, and the
+// host plans again from the header it reads back. Replaces the two blocking
+// read-backs of check_box (vesin/src/vesin_cuda.cpp:393-399).
+// ---------------------------------------------------------------------------
+
+struct ExpectedInputs {
+    double box[9];
+    int periodic[3];
+};
+
+/// Run by one thread once the bounds are final.
+__device__ void validate_inputs(DeviceHeader* header_in, const ExpectedInputs& expected, const GridPlan& plan, size_t n_points) {
+    // the bounds were written by other blocks with atomics: read them past L1
+    volatile DeviceHeader* header = header_in;
+    unsigned status = 0;
+    for (int k = 0; k < 9; k++) {
+        if (__double_as_longlong(header->box[k]) != __double_as_longlong(expected.box[k])) {
+            status |= STATUS_PLAN_STALE;
+        }
+    }
+    for (int k = 0; k < 3; k++) {
+        if ((header->periodic[k] != 0) != (expected.periodic[k] != 0)) {
+            status |= STATUS_PLAN_STALE;
+        }
+    }
+    if (header->first_bad != NO_BAD_POINT) {
+        status |= STATUS_BAD_POINT;
+    } else if (n_points != 0) {
+        // along non-periodic directions the cells only cover a window around
+        // the points the plan was made for: every point must still be inside
+        for (int k = 0; k < 3; k++) {
+            if (plan.periodic[k]) {
+                continue;
+            }
+            double lo = 0.0;
+            double hi = 0.0;
+            for (int c = 0; c < 3; c++) {
+                unsigned long long min_key = header->min_key[c];
+                unsigned long long max_key = header->max_key[c];
+                unsigned long long min_bits = (min_key >> 63) ? (min_key & 0x7fffffffffffffffull) : ~min_key;
+                unsigned long long max_bits = (max_key >> 63) ? (max_key & 0x7fffffffffffffffull) : ~max_key;
+                double u = plan.Hinv[c][k];
+                double a = u * __longlong_as_double(static_cast<long long>(min_bits));
+                double b = u * __longlong_as_double(static_cast<long long>(max_bits));
+                lo += fmin(a, b);
+                hi += fmax(a, b);
+            }
+            double window = plan.n_cells[k] / plan.scale[k];
+            if (!(lo >= plan.t0[k]) || !(hi <= plan.t0[k] + window)) {
+                status |= STATUS_PLAN_STALE;
+            }
+        }
+    }
+    if (status != 0) {
+        atomicOr(&header_in->status, status);
+    }
+}
+
+__global__ void validate_kernel(DeviceHeader* header, const ExpectedInputs expected, const GridPlan plan, size_t n_points) {
+    if (threadIdx.x == 0) {
+        validate_inputs(header, expected, plan, n_points);
+    }
+}
+
+/// Bounds of the points; with `validate` the block that finishes last also
+/// checks the speculative plan (the bounds are final by then).
+__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(
+    const RealView points, size_t n, DeviceHeader* header, const int validate, const ExpectedInputs expected, const GridPlan plan
+) {
     double lo[3] = {DBL_MAX, DBL_MAX, DBL_MAX};
     double hi[3] = {-DBL_MAX, -DBL_MAX, -DBL_MAX};
     unsigned long long bad = NO_BAD_POINT;
@@ -207,73 +292,17 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const RealView poin
         if (bad != NO_BAD_POINT) {
             atomicMin(&header->first_bad, bad);
         }
+        if (validate) {
+            __threadfence();
+            const unsigned ticket = atomicAdd(&header->ticket, 1u);
+            if (ticket == gridDim.x - 1) {
+                __threadfence();
+                validate_inputs(header, expected, plan, n);
+            }
+        }
     }
 }
 
-
-// ---------------------------------------------------------------------------
-// validation of a speculative plan
-// The host builds the grid plan from the box, periodicity and bounds it saw at
-// the end of the PREVIOUS build on the same list, and launches the whole build
-// without waiting for a read-back. This kernel compares that assumption with
-// what is in device memory now; when it does not hold it sets
-// STATUS_PLAN_STALE, every later kernel of the build returns at once, and the
-// host plans again from the header it reads back. Replaces the two blocking
-// read-backs of check_box (vesin/src/vesin_cuda.cpp:393-399).
-// ---------------------------------------------------------------------------
-
-struct ExpectedInputs {
-    double box[9];
-    int periodic[3];
-};
-
-__global__ void validate_kernel(DeviceHeader* header, const ExpectedInputs expected, const GridPlan plan, size_t n_points) {
-    if (threadIdx.x != 0) {
-        return;
-    }
-    unsigned status = 0;
-    for (int k = 0; k < 9; k++) {
-        if (__double_as_longlong(header->box[k]) != __double_as_longlong(expected.box[k])) {
-            status |= STATUS_PLAN_STALE;
-        }
-    }
-    for (int k = 0; k < 3; k++) {
-        if ((header->periodic[k] != 0) != (expected.periodic[k] != 0)) {
-            status |= STATUS_PLAN_STALE;
-        }
-    }
-    if (header->first_bad != NO_BAD_POINT) {
-        status |= STATUS_BAD_POINT;
-    } else if (n_points != 0) {
-        // along non-periodic directions the cells only cover a window around
-        // the points the plan was made for: every point must still be inside
-        for (int k = 0; k < 3; k++) {
-            if (plan.periodic[k]) {
-                continue;
-            }
-            double lo = 0.0;
-            double hi = 0.0;
-            for (int c = 0; c < 3; c++) {
-                unsigned long long min_key = header->min_key[c];
-                unsigned long long max_key = header->max_key[c];
-                unsigned long long min_bits = (min_key >> 63) ? (min_key & 0x7fffffffffffffffull) : ~min_key;
-                unsigned long long max_bits = (max_key >> 63) ? (max_key & 0x7fffffffffffffffull) : ~max_key;
-                double u = plan.Hinv[c][k];
-                double a = u * __longlong_as_double(static_cast<long long>(min_bits));
-                double b = u * __longlong_as_double(static_cast<long long>(max_bits));
-                lo += fmin(a, b);
-                hi += fmax(a, b);
-            }
-            double window = plan.n_cells[k] / plan.scale[k];
-            if (!(lo >= plan.t0[k]) || !(hi <= plan.t0[k] + window)) {
-                status |= STATUS_PLAN_STALE;
-            }
-        }
-    }
-    if (status != 0) {
-        atomicOr(&header->status, status);
-    }
-}
 
 // ---------------------------------------------------------------------------
 // bin: wrap + cell + histogram
@@ -436,9 +465,12 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_spine_kernel(unsigned long l
     }
 }
 
-template <typename TIn, typename TOut>
+/// SPINE: `tile_offsets` still holds the sums of the tiles (the spine kernel
+/// did not run): every block adds up the sums of the tiles before its own.
+template <typename TIn, typename TOut, bool SPINE>
 __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
-    const TIn* __restrict__ in, TOut* __restrict__ out, size_t n, const unsigned long long* __restrict__ tile_offsets
+    const TIn* __restrict__ in, TOut* __restrict__ out, size_t n, const unsigned long long* __restrict__ tile_offsets,
+    unsigned long long* __restrict__ total_out
 ) {
     // each thread owns SCAN_ITEMS consecutive elements
     size_t base = static_cast<size_t>(blockIdx.x) * SCAN_TILE + static_cast<size_t>(threadIdx.x) * SCAN_ITEMS;
@@ -462,11 +494,34 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
         }
     }
     __shared__ unsigned long long s_warp[CTA_WARPS];
+    __shared__ unsigned long long s_before[CTA_WARPS];
     if (lane == 31) {
         s_warp[warp] = inclusive;
     }
+    unsigned long long tile_offset = 0;
+    if (SPINE) {
+        unsigned long long before = 0;
+        for (unsigned t = threadIdx.x; t < blockIdx.x; t += CTA_THREADS) {
+            before += tile_offsets[t];
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            before += __shfl_xor_sync(FULL_MASK, before, offset);
+        }
+        if (lane == 0) {
+            s_before[warp] = before;
+        }
+    } else {
+        tile_offset = tile_offsets[blockIdx.x];
+    }
     __syncthreads();
-    unsigned long long prefix = tile_offsets[blockIdx.x] + inclusive - local;
+    if (SPINE) {
+#pragma unroll
+        for (int w = 0; w < CTA_WARPS; w++) {
+            tile_offset += s_before[w];
+        }
+    }
+    unsigned long long prefix = tile_offset + inclusive - local;
     for (int w = 0; w < warp; w++) {
         prefix += s_warp[w];
     }
@@ -479,6 +534,9 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
         prefix += values[k];
         if (idx + 1 == n) {
             out[n] = static_cast<TOut>(prefix);
+            if (SPINE && total_out != nullptr) {
+                *total_out = prefix;
+            }
         }
     }
 }
@@ -1932,24 +1990,13 @@ void configure_kernels() {
     cudaFuncSetAttribute(pairs_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
 }
 
-void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, cudaStream_t stream) {
-    header_init_kernel<<<1, 32, 0, stream>>>(header, box, periodic);
+void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, int32_t* zero, size_t n_zero, cudaStream_t stream) {
+    size_t blocks = (n_zero + CTA_THREADS * 4 - 1) / (CTA_THREADS * 4);
+    blocks = std::max<size_t>(1, std::min<size_t>(blocks, 148 * 4));
+    header_init_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(header, box, periodic, zero, n_zero);
 }
 
-void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream) {
-    if (n == 0) {
-        return;
-    }
-    size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    if (blocks > 148 * 8) {
-        blocks = 148 * 8;
-    }
-    bounds_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, header);
-}
-
-void launch_validate(
-    DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan, size_t n_points, cudaStream_t stream
-) {
+static ExpectedInputs expected_inputs(const double box[9], const bool periodic[3]) {
     ExpectedInputs expected;
     for (int k = 0; k < 9; k++) {
         expected.box[k] = box[k];
@@ -1957,7 +2004,36 @@ void launch_validate(
     for (int k = 0; k < 3; k++) {
         expected.periodic[k] = periodic[k] ? 1 : 0;
     }
-    validate_kernel<<<1, 32, 0, stream>>>(header, expected, plan, n_points);
+    return expected;
+}
+
+static unsigned bounds_blocks(size_t n) {
+    size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
+    return static_cast<unsigned>(std::min<size_t>(blocks, 148 * 8));
+}
+
+void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream) {
+    if (n == 0) {
+        return;
+    }
+    bounds_kernel<<<bounds_blocks(n), CTA_THREADS, 0, stream>>>(points, n, header, 0, ExpectedInputs{}, GridPlan{});
+}
+
+void launch_validate(
+    DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan, size_t n_points, cudaStream_t stream
+) {
+    validate_kernel<<<1, 32, 0, stream>>>(header, expected_inputs(box, periodic), plan, n_points);
+}
+
+void launch_bounds_validate(
+    RealView points, size_t n, DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan,
+    cudaStream_t stream
+) {
+    if (n == 0) {
+        launch_validate(header, box, periodic, plan, n, stream);
+        return;
+    }
+    bounds_kernel<<<bounds_blocks(n), CTA_THREADS, 0, stream>>>(points, n, header, 1, expected_inputs(box, periodic), plan);
 }
 
 void launch_bin(
@@ -1978,8 +2054,13 @@ static void launch_scan(const TIn* counts, TOut* starts, size_t n, void* tmp, un
     auto* tile_sums = static_cast<unsigned long long*>(tmp);
     size_t tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
     scan_tile_sums_kernel<TIn><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, n, tile_sums);
-    scan_spine_kernel<<<1, CTA_THREADS, 0, stream>>>(tile_sums, tiles, total);
-    scan_apply_kernel<TIn, TOut><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, starts, n, tile_sums);
+    if (tiles <= 2048) {
+        // short spine: every block of the second kernel adds up the tile sums before it
+        scan_apply_kernel<TIn, TOut, true><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, starts, n, tile_sums, total);
+    } else {
+        scan_spine_kernel<<<1, CTA_THREADS, 0, stream>>>(tile_sums, tiles, total);
+        scan_apply_kernel<TIn, TOut, false><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, starts, n, tile_sums, nullptr);
+    }
 }
 
 void launch_scan_cells(const int32_t* counts, int32_t* starts, size_t n, void* tmp, cudaStream_t stream) {

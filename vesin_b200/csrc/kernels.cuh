@@ -24,7 +24,7 @@ struct DeviceHeader {
     unsigned long long mask_cursor;  // words of hit-mask storage claimed by the count pass
     unsigned long long pair_cursor;  // output elements claimed by the fused pass (= its pair total)
     unsigned int status;             // sticky error bits, see STATUS_*
-    unsigned int pad;
+    unsigned int ticket;             // blocks of the bounds kernel that are done (the last one validates the plan)
     double box[9];                   // copy of the caller's box
     unsigned char periodic[8];       // copy of the caller's periodic flags
 };
@@ -63,7 +63,9 @@ struct RealView {
 
 // ---- launch wrappers (all asynchronous on `stream`) ----
 
-void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, cudaStream_t stream);
+/// Also zeroes `n_zero` int32 counters at `zero` (the cell histogram) when
+/// the caller already knows where they are.
+void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, int32_t* zero, size_t n_zero, cudaStream_t stream);
 
 /// Min / max of every coordinate and the first non-finite point.
 void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream);
@@ -73,6 +75,13 @@ void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t
 /// On a mismatch the header's status makes every later kernel return at once.
 void launch_validate(
     DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan, size_t n_points, cudaStream_t stream
+);
+
+/// launch_bounds and launch_validate in one kernel: the block that finishes
+/// last checks the plan.
+void launch_bounds_validate(
+    RealView points, size_t n, DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan,
+    cudaStream_t stream
 );
 
 /// Wrap into the cell, pick the cell, histogram with warp-aggregated atomics.

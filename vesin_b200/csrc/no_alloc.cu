@@ -157,7 +157,7 @@ size_t build(
     cudaStream_t stream = nullptr; // legacy default stream
 
     // the header (cursor, status, bounds) is re-initialised by a kernel
-    launch_header_init(d_header, RealView{box, 0}, periodic, stream);
+    launch_header_init(d_header, RealView{box, 0}, periodic, nullptr, 0, stream);
     launch_bounds(RealView{points, 0}, n_points, d_header, stream);
     check(cudaGetLastError(), "launch");
     DeviceHeader header;
