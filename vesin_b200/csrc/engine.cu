@@ -570,7 +570,7 @@ void neighbors(
                     set_outputs(list, ws, options, total + total / 16 + 256);
                     capacity = common_capacity(ws, options);
                 }
-                VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, sizeof(unsigned long long), stream));
+                VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, 2 * sizeof(unsigned long long), stream)); // and run_cursor
             }
             if (refused) {
                 continue;
@@ -936,7 +936,7 @@ void neighbors_slab(
         }
         set_outputs(list, ws, options, total + total / 16 + 256);
         capacity = common_capacity(ws, options);
-        VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, sizeof(unsigned long long), stream));
+        VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, 2 * sizeof(unsigned long long), stream)); // and run_cursor
     }
     list.length = total;
     ws.timed = timer.enabled;

@@ -12,6 +12,7 @@
 // only walks the stored hit bits, so the passes can not disagree.
 #include "kernels.cuh"
 
+#include <algorithm>
 #include <cfloat>
 
 namespace vb200 {
@@ -153,6 +154,7 @@ __global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
         header->total_pairs = 0;
         header->mask_cursor = 0;
         header->pair_cursor = 0;
+        header->run_cursor = 0;
         header->status = 0;
         header->ticket = 0;
     }
@@ -1273,6 +1275,8 @@ struct FusedShared {
     double transpose[CTA_WARPS][192];         // per warp: 64 shifts, then 64 vectors, on their way to coalesced stores
     unsigned owned_word[FUSED_WORDS]; // slab decomposition: which slots of a word hold owned points
     unsigned long long claim;
+    double centre[3]; // centre of the unit: origin of the fp32 local frame
+    int next_run[2];  // run of units this CTA takes next (two slots: one is read while the other is written)
 };
 static_assert(TILE_POINTS * FUSED_BATCH < 65536, "hit counts of a tile are kept in 16 bits");
 static_assert(FUSED_BATCH <= 512 && TILE_POINTS <= 32, "a list entry packs (lane, slot) into 14 bits");
@@ -1524,9 +1528,17 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
 
     // Consecutive units share two thirds of their stencil: a CTA takes runs of
     // UNIT_RUN neighbouring units so that most of its loads hit in L1.
+    // Runs are handed out dynamically (the first one is the block index): the run after
+    // the current one is fetched while the current one is processed.
     const int n_runs = (plan.n_units + UNIT_RUN - 1) / UNIT_RUN;
-    for (int run = blockIdx.x; run < n_runs; run += gridDim.x)
-    for (int u = run * UNIT_RUN; u < min(plan.n_units, (run + 1) * UNIT_RUN); u++) {
+    int run = blockIdx.x;
+    int run_parity = 0;
+    while (run < n_runs) {
+    if (threadIdx.x == 0) {
+        sh.next_run[run_parity] = static_cast<int>(gridDim.x + atomicAdd(&header->run_cursor, 1ull));
+    }
+    const int run_end = min(plan.n_units, (run + 1) * UNIT_RUN);
+    for (int u = run * UNIT_RUN; u < run_end; u++) {
         Unit unit = unit_of(plan, cell_start, u);
         if (unit.n_home == 0) {
             continue;
@@ -1561,11 +1573,12 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
             }
         }
 
-        double centre[3];
-#pragma unroll
-        for (int c = 0; c < 3; c++) {
-            centre[c] = plan.origin[c] + (unit.c0 + 0.5 * unit.cells) * plan.cell_vec[0][c] + (unit.c1 + 0.5) * plan.cell_vec[1][c] +
-                        (unit.c2 + 0.5) * plan.cell_vec[2][c];
+        // centre of the pencil: origin of the fp32 local frame (shared memory: visible after
+        // the barriers of the segment setup, and not held in registers across the unit)
+        if (threadIdx.x < 3) {
+            const int c = threadIdx.x;
+            sh.centre[c] = plan.origin[c] + (unit.c0 + 0.5 * unit.cells) * plan.cell_vec[0][c] + (unit.c1 + 0.5) * plan.cell_vec[1][c] +
+                           (unit.c2 + 0.5) * plan.cell_vec[2][c];
         }
 
         PHASE_MARK(0); // unit setup
@@ -1617,9 +1630,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         index_j = sorted.index[p];
                     }
                     sh.sj[s] = make_int4(r0, r1, r2, index_j);
-                    const float fx = static_cast<float>(px + (r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0]) - centre[0]);
-                    const float fy = static_cast<float>(py + (r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1]) - centre[1]);
-                    const float fz = static_cast<float>(pz + (r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2]) - centre[2]);
+                    const float fx = static_cast<float>(px + (r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0]) - sh.centre[0]);
+                    const float fy = static_cast<float>(py + (r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1]) - sh.centre[1]);
+                    const float fz = static_cast<float>(pz + (r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2]) - sh.centre[2]);
                     sh.near32[s] = make_float4(fx, fy, fz, fx * fx + fy * fy + fz * fz);
                 }
                 for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
@@ -1664,9 +1677,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         si1 = sorted.shift[3 * pi + 1];
                         si2 = sorted.shift[3 * pi + 2];
                         index_i = SLAB ? static_cast<int>(global_index[sorted.index[pi]]) : sorted.index[pi];
-                        xi = valid ? static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - centre[0]) : nan;
-                        yi = valid ? static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - centre[1]) : nan;
-                        zi = valid ? static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - centre[2]) : nan;
+                        xi = valid ? static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - sh.centre[0]) : nan;
+                        yi = valid ? static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - sh.centre[1]) : nan;
+                        zi = valid ? static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - sh.centre[2]) : nan;
                         an = xi * xi + yi * yi + zi * zi;
                     }
                     if (warp == 0) {
@@ -1952,6 +1965,10 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
             }
         }
     }
+    __syncthreads(); // next_run is visible; nobody reads the other slot any more
+    run = sh.next_run[run_parity];
+    run_parity ^= 1;
+    }
 }
 
 } // namespace
@@ -2113,9 +2130,18 @@ void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
     DeviceHeader* header, const long long* global_index, cudaStream_t stream
 ) {
-    // two waves of CTAs (4 are resident per SM by registers and shared memory)
-    const int unit_run = DEFAULT_UNIT_RUN;
-    const int per_sm = 8;
+    // as many CTAs as are resident (4 per SM by registers and shared memory), which take
+    // runs of units from a shared counter; small systems give every unit its own CTA
+    // instead of runs of neighbouring units
+    const int per_sm = 4;
+    int sms = 148;
+    {
+        int device = 0;
+        if (cudaGetDevice(&device) == cudaSuccess) {
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        }
+    }
+    const int unit_run = std::max(1, std::min(DEFAULT_UNIT_RUN, plan.n_units / (sms * 4)));
     int grid = pair_grid((plan.n_units + unit_run - 1) / unit_run, per_sm);
     const size_t smem = sizeof(FusedShared);
     // paired stores of full lists: 32 bytes of indices, 16 of distances / vectors, 8 of shifts

@@ -23,6 +23,7 @@ struct DeviceHeader {
     unsigned long long total_pairs;  // written by the scan over per-point pair counts
     unsigned long long mask_cursor;  // words of hit-mask storage claimed by the count pass
     unsigned long long pair_cursor;  // output elements claimed by the fused pass (= its pair total)
+    unsigned long long run_cursor;   // runs of work units handed out by the fused pass (dynamic scheduling)
     unsigned int status;             // sticky error bits, see STATUS_*
     unsigned int ticket;             // blocks of the bounds kernel that are done (the last one validates the plan)
     double box[9];                   // copy of the caller's box
