@@ -1456,18 +1456,24 @@ __device__ __forceinline__ void store_both(
             }
         }
     }
+    const bool whole = n_valid == 32; // the usual case: no bounds to check on the way out
     if (out.shifts != nullptr) {
         int2* buffer = reinterpret_cast<int2*>(sh.transpose[warp]);
         buffer[3 * lane + 0] = make_int2(s0, s1);
         buffer[3 * lane + 1] = make_int2(s2, -s0);
         buffer[3 * lane + 2] = make_int2(-s1, -s2);
         __syncwarp();
-        int2* dst = reinterpret_cast<int2*>(out.shifts + 3 * first);
+        int2* dst = reinterpret_cast<int2*>(out.shifts + 3 * first) + lane;
+        if (whole) {
+            dst[0] = buffer[lane];
+            dst[32] = buffer[lane + 32];
+            dst[64] = buffer[lane + 64];
+        } else {
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            const int w = k * 32 + lane;
-            if (w < 3 * n_valid) {
-                dst[w] = buffer[w];
+            for (int k = 0; k < 3; k++) {
+                if (k * 32 + lane < 3 * n_valid) {
+                    dst[k * 32] = buffer[k * 32 + lane];
+                }
             }
         }
         __syncwarp();
@@ -1481,12 +1487,17 @@ __device__ __forceinline__ void store_both(
         buffer[3 * lane + 1] = make_float2(fz, -fx);
         buffer[3 * lane + 2] = make_float2(-fy, -fz);
         __syncwarp();
-        float2* dst = reinterpret_cast<float2*>(reinterpret_cast<float*>(out.vectors) + 3 * first);
+        float2* dst = reinterpret_cast<float2*>(reinterpret_cast<float*>(out.vectors) + 3 * first) + lane;
+        if (whole) {
+            dst[0] = buffer[lane];
+            dst[32] = buffer[lane + 32];
+            dst[64] = buffer[lane + 64];
+        } else {
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            const int w = k * 32 + lane;
-            if (w < 3 * n_valid) {
-                dst[w] = buffer[w];
+            for (int k = 0; k < 3; k++) {
+                if (k * 32 + lane < 3 * n_valid) {
+                    dst[k * 32] = buffer[k * 32 + lane];
+                }
             }
         }
         __syncwarp();
@@ -1496,12 +1507,17 @@ __device__ __forceinline__ void store_both(
         buffer[3 * lane + 1] = make_double2(vz, -vx);
         buffer[3 * lane + 2] = make_double2(-vy, -vz);
         __syncwarp();
-        double2* dst = reinterpret_cast<double2*>(out.vectors + 3 * first);
+        double2* dst = reinterpret_cast<double2*>(out.vectors + 3 * first) + lane;
+        if (whole) {
+            dst[0] = buffer[lane];
+            dst[32] = buffer[lane + 32];
+            dst[64] = buffer[lane + 64];
+        } else {
 #pragma unroll
-        for (int k = 0; k < 3; k++) {
-            const int w = k * 32 + lane;
-            if (w < 3 * n_valid) {
-                dst[w] = buffer[w];
+            for (int k = 0; k < 3; k++) {
+                if (k * 32 + lane < 3 * n_valid) {
+                    dst[k * 32] = buffer[k * 32 + lane];
+                }
             }
         }
         __syncwarp();
