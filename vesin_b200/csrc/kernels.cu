@@ -55,25 +55,30 @@ __device__ __forceinline__ unsigned lanemask_lt() {
 /// prefix and stores the CTA total in warp_sums[CTA_WARPS] (every thread
 /// stores the same value, so the total is visible to the caller at once).
 /// One barrier inside; two calls must be separated by another barrier.
+/// Only the first ACTIVE_WARPS warps may hold non-zero values (the others
+/// skip the shuffles).
+template <int ACTIVE_WARPS = CTA_WARPS>
 __device__ __forceinline__ int block_exclusive_scan(int value, int* warp_sums) {
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     int inclusive = value;
+    if (ACTIVE_WARPS == CTA_WARPS || warp < ACTIVE_WARPS) {
 #pragma unroll
-    for (int offset = 1; offset < 32; offset <<= 1) {
-        int up = __shfl_up_sync(FULL_MASK, inclusive, offset);
-        if (lane >= offset) {
-            inclusive += up;
+        for (int offset = 1; offset < 32; offset <<= 1) {
+            int up = __shfl_up_sync(FULL_MASK, inclusive, offset);
+            if (lane >= offset) {
+                inclusive += up;
+            }
         }
-    }
-    if (lane == 31) {
-        warp_sums[warp] = inclusive;
+        if (lane == 31) {
+            warp_sums[warp] = inclusive;
+        }
     }
     __syncthreads();
     int before = 0;
     int total = 0;
 #pragma unroll
-    for (int w = 0; w < CTA_WARPS; w++) {
+    for (int w = 0; w < ACTIVE_WARPS; w++) {
         const int sum = warp_sums[w];
         total += sum;
         if (w < warp) {
@@ -85,6 +90,26 @@ __device__ __forceinline__ int block_exclusive_scan(int value, int* warp_sums) {
     }
     __syncwarp();
     return before + inclusive - value;
+}
+
+// Packed fp32 arithmetic of sm_100: two independent IEEE operations per instruction.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+    unsigned long long packed;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(packed) : "f"(lo), "f"(hi));
+    return packed;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long packed, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(packed));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
 }
 
 /// Position of the n-th (counting from 0) set bit of w. For a word with n or
@@ -618,6 +643,23 @@ __device__ __forceinline__ Unit unit_of(const GridPlan& plan, const int32_t* __r
     return unit;
 }
 
+/// The unit after `unit` (u + 1) without the divisions of unit_of.
+__device__ __forceinline__ void next_unit(const GridPlan& plan, const int32_t* __restrict__ cell_start, Unit& unit) {
+    unit.c0 += plan.pencil;
+    if (unit.c0 >= plan.n_cells[0]) {
+        unit.c0 = 0;
+        unit.c1 += 1;
+        if (unit.c1 >= plan.n_cells[1]) {
+            unit.c1 = 0;
+            unit.c2 += 1;
+        }
+    }
+    unit.cells = min(plan.pencil, plan.n_cells[0] - unit.c0);
+    const int first = (unit.c2 * plan.n_cells[1] + unit.c1) * plan.n_cells[0] + unit.c0;
+    unit.begin = cell_start[first];
+    unit.n_home = cell_start[first + unit.cells] - unit.begin;
+}
+
 __device__ __forceinline__ bool half_rule(int s0, int s1, int s2) {
     // which of S / -S a half list keeps for a point paired with its own
     // image (vesin/src/cpu_cell_list.cpp:107-132)
@@ -679,7 +721,7 @@ __device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_
         table.q[2][t] = q2;
         table.self_ok[t] = self_ok;
     }
-    int prefix = block_exclusive_scan(length, table.scan_tmp);
+    int prefix = block_exclusive_scan<SEG_MAX / 32>(length, table.scan_tmp);
     if (t < SEG_MAX) {
         table.slot0[t] = prefix;
     }
@@ -1262,7 +1304,12 @@ constexpr int FUSED_TASKS = (TILE_POINTS * FUSED_WORDS + CTA_THREADS - 1) / CTA_
 
 struct FusedShared {
     SegmentTable table;
-    float4 near32[FUSED_BATCH];  // x, y, z relative to the unit centre, and their squared norm
+    // fp32 coordinates of the candidates relative to the unit centre and their squared norm,
+    // one array per component so that two candidates fill one packed fp32x2 operand
+    alignas(16) float near_x[FUSED_BATCH]; // read as 16-byte vectors
+    alignas(16) float near_y[FUSED_BATCH];
+    alignas(16) float near_z[FUSED_BATCH];
+    alignas(16) float near_n[FUSED_BATCH];
     double x[FUSED_BATCH];       // original positions of the candidates
     double y[FUSED_BATCH];
     double z[FUSED_BATCH];
@@ -1272,14 +1319,47 @@ struct FusedShared {
     unsigned mask[FUSED_WORDS * TILE_POINTS]; // [word][lane]
     unsigned short list[FUSED_LIST];          // (home lane << 9) | slot in batch
     unsigned short prefix[CTA_THREADS];       // hits of the tasks of the threads before this one in its warp
-    double transpose[CTA_WARPS][192];         // per warp: 64 shifts, then 64 vectors, on their way to coalesced stores
+    alignas(16) double transpose[CTA_WARPS][192];         // per warp: 64 shifts, then 64 vectors, on their way to coalesced stores
     unsigned owned_word[FUSED_WORDS]; // slab decomposition: which slots of a word hold owned points
     unsigned long long claim;
     double centre[3]; // centre of the unit: origin of the fp32 local frame
+    int stencil_cached;          // are the packed offsets below usable?
+    int stencil_offset[SEG_MAX]; // first SEG_MAX entries of the stencil of a full-length unit, 10 bits per direction
     int next_run[2];  // run of units this CTA takes next (two slots: one is read while the other is written)
 };
+static_assert(
+    offsetof(FusedShared, near_x) % 16 == 0 && offsetof(FusedShared, near_y) % 16 == 0 && offsetof(FusedShared, near_z) % 16 == 0 &&
+        offsetof(FusedShared, near_n) % 16 == 0 && offsetof(FusedShared, transpose) % 16 == 0 && offsetof(FusedShared, sj) % 16 == 0 &&
+        offsetof(FusedShared, home_sj) % 16 == 0,
+    "members read or written as 16-byte vectors"
+);
 static_assert(TILE_POINTS * FUSED_BATCH < 65536, "hit counts of a tile are kept in 16 bits");
 static_assert(FUSED_BATCH <= 512 && TILE_POINTS <= 32, "a list entry packs (lane, slot) into 14 bits");
+
+/// Offset (in cells, relative to the first cell of the unit) of entry `index`
+/// of the half-shell stencil of a unit of `cells` cells.
+__device__ __forceinline__ void half_stencil_offset(const GridPlan& plan, int cells, int index, int& ox, int& oy, int& oz) {
+    const int own_row = cells + plan.n_search[0];
+    if (index < own_row) {
+        ox = index;
+        oy = 0;
+        oz = 0;
+        return;
+    }
+    const int row_width = cells + 2 * plan.n_search[0];
+    const int rows_y = 2 * plan.n_search[1] + 1;
+    const int rest = index - own_row;
+    const int row = rest / row_width;
+    ox = rest % row_width - plan.n_search[0];
+    if (row < plan.n_search[1]) {
+        oy = row + 1;
+        oz = 0;
+    } else {
+        const int upper = row - plan.n_search[1];
+        oz = 1 + upper / rows_y;
+        oy = upper % rows_y - plan.n_search[1];
+    }
+}
 
 /// Segments of the half-shell stencil of a unit. Order: the unit's own row
 /// first (its own cells, then the n_search[0] cells after them), then the rows
@@ -1291,8 +1371,6 @@ __device__ __forceinline__ int setup_half_segments(
     SegmentTable& table = sh.table;
     const int t = threadIdx.x;
     const int own_row = unit.cells + plan.n_search[0];
-    const int row_width = unit.cells + 2 * plan.n_search[0];
-    const int rows_y = 2 * plan.n_search[1] + 1;
     int length = 0;
     if (t < SEG_MAX) {
         const int global_t = group * SEG_MAX + t;
@@ -1301,22 +1379,14 @@ __device__ __forceinline__ int setup_half_segments(
         int owned = 1;
         if (global_t < unit.n_stencil) {
             int ox, oy, oz;
-            if (global_t < own_row) {
-                ox = global_t;
-                oy = 0;
-                oz = 0;
+            if (group == 0 && unit.cells == plan.pencil && sh.stencil_cached) {
+                // the usual unit: offsets decoded once per CTA
+                const int packed = sh.stencil_offset[t];
+                ox = (packed & 1023) - 512;
+                oy = ((packed >> 10) & 1023) - 512;
+                oz = (packed >> 20) - 512;
             } else {
-                const int rest = global_t - own_row;
-                const int row = rest / row_width;
-                ox = rest % row_width - plan.n_search[0];
-                if (row < plan.n_search[1]) {
-                    oy = row + 1;
-                    oz = 0;
-                } else {
-                    const int upper = row - plan.n_search[1];
-                    oz = 1 + upper / rows_y;
-                    oy = upper % rows_y - plan.n_search[1];
-                }
+                half_stencil_offset(plan, unit.cells, global_t, ox, oy, oz);
             }
             int nb[3] = {unit.c0 + ox, unit.c1 + oy, unit.c2 + oz};
             int q[3] = {0, 0, 0};
@@ -1352,7 +1422,7 @@ __device__ __forceinline__ int setup_half_segments(
         table.q[2][t] = q2;
         table.self_ok[t] = owned; // slab decomposition: does the segment hold owned points?
     }
-    const int prefix = block_exclusive_scan(length, table.scan_tmp);
+    const int prefix = block_exclusive_scan<SEG_MAX / 32>(length, table.scan_tmp);
     if (t < SEG_MAX) {
         table.slot0[t] = prefix;
     }
@@ -1541,6 +1611,17 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
         return; // the validation kernel refused the plan: the host will redo the build
     }
     PHASE_CLOCK_START();
+    if (threadIdx.x == 0) {
+        // 10 bits per direction hold the offsets unless the stencil reaches very far
+        sh.stencil_cached = (plan.pencil + plan.n_search[0] < 500 && plan.n_search[1] < 500 && plan.n_search[2] < 500) ? 1 : 0;
+    }
+    if (threadIdx.x < SEG_MAX) {
+        // entries beyond the stencil are never read
+        int ox, oy, oz;
+        half_stencil_offset(plan, plan.pencil, threadIdx.x, ox, oy, oz);
+        sh.stencil_offset[threadIdx.x] = ((ox + 512) & 1023) | (((oy + 512) & 1023) << 10) | (((oz + 512) & 1023) << 20);
+    }
+    __syncthreads();
 
     // Consecutive units share two thirds of their stencil: a CTA takes runs of
     // UNIT_RUN neighbouring units so that most of its loads hit in L1.
@@ -1554,8 +1635,11 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
         sh.next_run[run_parity] = static_cast<int>(gridDim.x + atomicAdd(&header->run_cursor, 1ull));
     }
     const int run_end = min(plan.n_units, (run + 1) * UNIT_RUN);
+    Unit unit = unit_of(plan, cell_start, run * UNIT_RUN);
     for (int u = run * UNIT_RUN; u < run_end; u++) {
-        Unit unit = unit_of(plan, cell_start, u);
+        if (u != run * UNIT_RUN) {
+            next_unit(plan, cell_start, unit);
+        }
         if (unit.n_home == 0) {
             continue;
         }
@@ -1649,10 +1733,16 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     const float fx = static_cast<float>(px + (r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0]) - sh.centre[0]);
                     const float fy = static_cast<float>(py + (r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1]) - sh.centre[1]);
                     const float fz = static_cast<float>(pz + (r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2]) - sh.centre[2]);
-                    sh.near32[s] = make_float4(fx, fy, fz, fx * fx + fy * fy + fz * fz);
+                    sh.near_x[s] = fx;
+                    sh.near_y[s] = fy;
+                    sh.near_z[s] = fz;
+                    sh.near_n[s] = fx * fx + fy * fy + fz * fz;
                 }
                 for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
-                    sh.near32[s] = make_float4(0.0f, 0.0f, 0.0f, __int_as_float(0x7f800000)); // never a hit
+                    sh.near_x[s] = 0.0f;
+                    sh.near_y[s] = 0.0f;
+                    sh.near_z[s] = 0.0f;
+                    sh.near_n[s] = __int_as_float(0x7f800000); // never a hit
                 }
 
                 for (int tile = 0; tile < n_tiles; tile++) {
@@ -1679,11 +1769,10 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         si1 = -packed.y;
                         si2 = -packed.z;
                         index_i = packed.w;
-                        const float4 local = sh.near32[slot];
-                        xi = valid ? local.x : nan;
-                        yi = valid ? local.y : nan;
-                        zi = valid ? local.z : nan;
-                        an = local.w;
+                        xi = valid ? sh.near_x[slot] : nan;
+                        yi = valid ? sh.near_y[slot] : nan;
+                        zi = valid ? sh.near_z[slot] : nan;
+                        an = sh.near_n[slot];
                     } else {
                         const size_t pi = static_cast<size_t>(unit.begin) + (valid ? il : 0);
                         rix = sorted.pos[3 * pi + 0];
@@ -1708,20 +1797,38 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     const float ax = -2.0f * xi;
                     const float ay = -2.0f * yi;
                     const float az = -2.0f * zi;
+                    const unsigned long long ax2 = pack_f32x2(ax, ax);
+                    const unsigned long long ay2 = pack_f32x2(ay, ay);
+                    const unsigned long long az2 = pack_f32x2(az, az);
+                    const unsigned long long an2 = pack_f32x2(an, an);
 
                     for (int w = warp; w < batch_words; w += CTA_WARPS) {
                         unsigned inside = 0; // surely inside the cutoff
                         unsigned near = 0;   // inside, or too close to the cutoff for fp32
-                        const float4* candidates = sh.near32 + w * 32;
+                        // four candidates per (broadcast) load, two per packed instruction; every
+                        // component goes through the same roundings as the scalar expression
+                        // fma(cx, ax, fma(cy, ay, fma(cz, az, cn + an)))
+                        const ulonglong2* cx = reinterpret_cast<const ulonglong2*>(sh.near_x + w * 32);
+                        const ulonglong2* cy = reinterpret_cast<const ulonglong2*>(sh.near_y + w * 32);
+                        const ulonglong2* cz = reinterpret_cast<const ulonglong2*>(sh.near_z + w * 32);
+                        const ulonglong2* cn = reinterpret_cast<const ulonglong2*>(sh.near_n + w * 32);
 #pragma unroll
-                        for (int b = 0; b < 32; b++) {
-                            const float4 cand = candidates[b]; // broadcast
-                            const float d2 = fmaf(cand.x, ax, fmaf(cand.y, ay, fmaf(cand.z, az, cand.w + an)));
-                            if (d2 < cutoff2_lo) {
-                                inside |= 1u << b;
-                            }
-                            if (d2 <= cutoff2_hi) {
-                                near |= 1u << b;
+                        for (int k = 0; k < 8; k++) {
+                            const ulonglong2 x4 = cx[k];
+                            const ulonglong2 y4 = cy[k];
+                            const ulonglong2 z4 = cz[k];
+                            const ulonglong2 n4 = cn[k];
+                            float d2[4];
+                            unpack_f32x2(fma_f32x2(x4.x, ax2, fma_f32x2(y4.x, ay2, fma_f32x2(z4.x, az2, add_f32x2(n4.x, an2)))), d2[0], d2[1]);
+                            unpack_f32x2(fma_f32x2(x4.y, ax2, fma_f32x2(y4.y, ay2, fma_f32x2(z4.y, az2, add_f32x2(n4.y, an2)))), d2[2], d2[3]);
+#pragma unroll
+                            for (int c = 0; c < 4; c++) {
+                                if (d2[c] < cutoff2_lo) {
+                                    inside |= 1u << (4 * k + c);
+                                }
+                                if (d2[c] <= cutoff2_hi) {
+                                    near |= 1u << (4 * k + c);
+                                }
                             }
                         }
                         // half shell inside the unit's own row: only slots after the point's own
