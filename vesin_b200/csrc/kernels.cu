@@ -572,26 +572,38 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
 // scatter
 // Replaces scatter_particles (vesin/src/cuda/cell_list.cu:392-421); the slot
 // inside the cell was already handed out by the histogram, so there is no
-// second atomic.
+// second atomic. Two kernels: indices are scattered, records are gathered.
 // ---------------------------------------------------------------------------
 
-__global__ void __launch_bounds__(CTA_THREADS) scatter_kernel(
-    const RealView points, size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank,
-    const int32_t* __restrict__ shift, const int32_t* __restrict__ cell_start, SortedPoints sorted,
-    const DeviceHeader* __restrict__ header
+/// Step 1: where does point i go? Only its index is scattered (4 bytes per point).
+__global__ void __launch_bounds__(CTA_THREADS) scatter_index_kernel(
+    size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank, const int32_t* __restrict__ cell_start,
+    int32_t* __restrict__ sorted_index, const DeviceHeader* __restrict__ header
 ) {
     size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n || (header->status & STATUS_ABORT_MASK)) {
         return;
     }
     size_t p = static_cast<size_t>(cell_start[cell_of[i]]) + rank[i];
-    sorted.pos[3 * p + 0] = load_real(points, 3 * i + 0);
-    sorted.pos[3 * p + 1] = load_real(points, 3 * i + 1);
-    sorted.pos[3 * p + 2] = load_real(points, 3 * i + 2);
-    sorted.index[p] = static_cast<int32_t>(i);
-    sorted.shift[3 * p + 0] = shift[3 * i + 0];
-    sorted.shift[3 * p + 1] = shift[3 * i + 1];
-    sorted.shift[3 * p + 2] = shift[3 * i + 2];
+    sorted_index[p] = static_cast<int32_t>(i);
+}
+
+/// Step 2: the records are gathered, one coordinate per thread, so that every
+/// store instruction writes one contiguous span whatever the order of the
+/// input (a scatter of whole records writes partial sectors all over the
+/// arrays when neighbouring points are far apart in the input).
+__global__ void __launch_bounds__(CTA_THREADS) gather_records_kernel(
+    const RealView points, size_t n, const int32_t* __restrict__ shift, SortedPoints sorted, const DeviceHeader* __restrict__ header
+) {
+    size_t f = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (f >= 3 * n || (header->status & STATUS_ABORT_MASK)) {
+        return;
+    }
+    size_t p = f / 3;
+    size_t c = f - 3 * p;
+    size_t i = static_cast<size_t>(sorted.index[p]);
+    sorted.pos[f] = load_real(points, 3 * i + c);
+    sorted.shift[f] = shift[3 * i + c];
 }
 
 // ---------------------------------------------------------------------------
@@ -2218,7 +2230,9 @@ void launch_scatter(
     SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
 ) {
     size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    scatter_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, cell_of, rank, shift, cell_start, sorted, header);
+    scatter_index_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(n, cell_of, rank, cell_start, sorted.index, header);
+    blocks = (3 * n + CTA_THREADS - 1) / CTA_THREADS;
+    gather_records_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, shift, sorted, header);
 }
 
 void launch_count(
