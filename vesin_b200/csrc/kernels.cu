@@ -2278,7 +2278,8 @@ void launch_pairs(
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         }
     }
-    const int unit_run = std::max(1, std::min(DEFAULT_UNIT_RUN, plan.n_units / (sms * 4)));
+    // at least 8 runs per CTA, so that the last runs do not leave most of the GPU idle
+    const int unit_run = std::max(1, std::min(DEFAULT_UNIT_RUN, plan.n_units / (sms * 4 * 8)));
     int grid = pair_grid((plan.n_units + unit_run - 1) / unit_run, per_sm);
     const size_t smem = sizeof(FusedShared);
     // paired stores of full lists: 32 bytes of indices, 16 of distances / vectors, 8 of shifts
