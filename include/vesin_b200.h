@@ -185,6 +185,9 @@ VESIN_API int vesin_b200_pack_halo(
  * each; shifts / distances / vectors may be NULL to skip them); the scratch of
  * the kernels is a fixed array of about 2.3 MB that every GPU holds from
  * library load to process exit. Hence:
+ *   - `pairs` must be aligned to 16 bytes (the other arrays to their element:
+ *     4 and 8 bytes); full lists are written fastest when `pairs` is aligned to
+ *     32 bytes and `distances` / `vectors` to 16;
  *   - at most VESIN_B200_NO_ALLOC_MAX_POINTS points, larger systems get an error;
  *   - the list is unsorted, same pair set as vesin_neighbors;
  *   - when the list has more than `capacity` pairs the call fails, `*length`

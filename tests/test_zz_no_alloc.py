@@ -35,7 +35,9 @@ def _existing_entry_point(torch, points, box, periodic, cutoff, full):
     return gpu_compute(points, box, periodic, cutoff, full, "ijSdD")
 
 
-def _no_alloc(torch, lib, points, box, periodic, cutoff, full, capacity):
+def _no_alloc(torch, lib, points, box, periodic, cutoff, full, capacity, offset_bytes=(0, 0, 0, 0)):
+    """`offset_bytes`: start the four output arrays that many bytes into their
+    allocation (pairs, shifts, distances, vectors), to test alignment handling."""
     from vesin_b200._c_api import get_library
 
     lib = get_library()
@@ -44,10 +46,15 @@ def _no_alloc(torch, lib, points, box, periodic, cutoff, full, capacity):
     d_box = torch.tensor(np.asarray(box, dtype=np.float64), device=device)
     d_periodic = torch.tensor(np.asarray(periodic, dtype=bool), device=device)
     # the caller owns the outputs
-    pairs = torch.full((capacity, 2), -1, dtype=torch.int64, device=device)
-    shifts = torch.full((capacity, 3), 99, dtype=torch.int32, device=device)
-    distances = torch.full((capacity,), -1.0, dtype=torch.float64, device=device)
-    vectors = torch.full((capacity, 3), -1.0, dtype=torch.float64, device=device)
+    def shifted(count, dtype, fill, offset):
+        item = torch.empty((), dtype=dtype).element_size()
+        assert offset % item == 0
+        return torch.full((count + offset // item,), fill, dtype=dtype, device=device)[offset // item :]
+
+    pairs = shifted(2 * capacity, torch.int64, -1, offset_bytes[0]).view(capacity, 2)
+    shifts = shifted(3 * capacity, torch.int32, 99, offset_bytes[1]).view(capacity, 3)
+    distances = shifted(capacity, torch.float64, -1.0, offset_bytes[2])
+    vectors = shifted(3 * capacity, torch.float64, -1.0, offset_bytes[3]).view(capacity, 3)
     torch.cuda.synchronize()
     length = ctypes.c_size_t(0)
     error = ctypes.c_char_p()
@@ -98,3 +105,21 @@ def test_limits_are_reported():
     too_many = np.zeros((NO_ALLOC_MAX_POINTS + 1, 3))
     status, message, _, _ = _no_alloc(torch, None, too_many, np.eye(3) * 10, [True] * 3, 1.0, True, 10)
     assert status == 1 and f"at most {NO_ALLOC_MAX_POINTS} points" in message
+
+
+def test_output_alignment():
+    """Full lists use paired stores when the arrays allow it (pairs on 32 bytes,
+    distances / vectors on 16, shifts on 8) and single stores otherwise: both
+    give the same list. A `pairs` array off its 16-byte boundary is refused."""
+    import torch
+
+    points, box, periodic = W.diamond(6, seed=23)
+    expected = _existing_entry_point(torch, points, box, periodic, 5.0, True)
+    capacity = len(expected["i"]) + 64
+    for offsets in [(16, 4, 8, 8), (0, 4, 0, 0), (16, 0, 0, 8)]:
+        status, message, length, got = _no_alloc(torch, None, points, box, periodic, 5.0, True, capacity, offsets)
+        assert status == 0, message
+        assert length == len(expected["i"])
+        O.assert_same(got, expected, RTOL_FP64, f"no-alloc build with output offsets {offsets}")
+    status, message, _, _ = _no_alloc(torch, None, points, box, periodic, 5.0, True, capacity, (8, 0, 0, 0))
+    assert status == 1 and "aligned to 16 bytes" in message

@@ -25,6 +25,7 @@
 //     (cudaGetSymbolAddress) and opts the kernels into large shared memory;
 //     make that first call before any stream capture begins.
 #include <cmath>
+#include <cstdint>
 #include <cstring>
 #include <mutex>
 #include <stdexcept>
@@ -222,6 +223,12 @@ extern "C" int vesin_b200_neighbors_no_alloc(
     }
     if (capacity > 0 && pairs == nullptr) {
         *error_message = "`pairs` can not be a NULL pointer when capacity is not zero";
+        return 1;
+    }
+    // a pair of indices is written with one 16-byte store; the other arrays need the alignment of their elements
+    if (reinterpret_cast<uintptr_t>(pairs) % 16 != 0 || reinterpret_cast<uintptr_t>(shifts) % 4 != 0 ||
+        reinterpret_cast<uintptr_t>(distances) % 8 != 0 || reinterpret_cast<uintptr_t>(vectors) % 8 != 0) {
+        *error_message = "`pairs` must be aligned to 16 bytes, `shifts` to 4, `distances` and `vectors` to 8";
         return 1;
     }
     try {
