@@ -198,8 +198,10 @@ class ReferenceCPU:
         except Exception:
             pass
 
-    def run(self, points, box, periodic, cutoff, full_list, quantities="ijSdD", n_threads=0, sorted=False):
-        """Only runs the calculation; returns the number of pairs."""
+    def run(self, points, box, periodic, cutoff, full_list, quantities="ijSdD", n_threads=0, sorted=False, skin=0.0):
+        """Only runs the calculation; returns the number of pairs. With
+        ``skin > 0`` the reference re-uses the candidates it cached on this
+        list (vesin/src/verlet.cpp:82-191) while the points have moved little."""
         points, box, periodic = _prepare(points, box, periodic)
         options = _VesinOptions()
         options.cutoff = float(cutoff)
@@ -210,7 +212,7 @@ class ReferenceCPU:
         options.return_shifts = "S" in quantities
         options.return_distances = "d" in quantities
         options.return_vectors = "D" in quantities
-        options.skin = 0.0
+        options.skin = float(skin)
         error = ctypes.c_char_p()
         status = self._lib.vesin_neighbors(
             points.ctypes.data,
@@ -226,8 +228,8 @@ class ReferenceCPU:
             raise RuntimeError(error.value.decode("utf8"))
         return self._list.length
 
-    def compute(self, points, box, periodic, cutoff, full_list, quantities="ijSdD", n_threads=0, sorted=False):
-        n = self.run(points, box, periodic, cutoff, full_list, quantities, n_threads, sorted)
+    def compute(self, points, box, periodic, cutoff, full_list, quantities="ijSdD", n_threads=0, sorted=False, skin=0.0):
+        n = self.run(points, box, periodic, cutoff, full_list, quantities, n_threads, sorted, skin)
         return _collect(self._list, n, quantities)
 
 

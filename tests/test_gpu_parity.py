@@ -192,6 +192,36 @@ def test_reused_list_follows_changing_inputs():
         O.assert_same(got, O.restated_neighbors(p, b, per, 4.0, False, "ijSdD"), RTOL_FP64, "sorted")
 
 
+@pytest.mark.parametrize("full", [True, False])
+def test_skin_gives_the_list_at_the_cutoff(full):
+    """`skin > 0`: the reference re-filters cached candidates while the atoms
+    have moved less than skin / 2 (vesin/src/verlet.cpp:82-191; tests:
+    python/vesin/tests/test_numpy.py:405-551), this engine rebuilds; both give
+    the exact list at `cutoff` on every step of a trajectory with small moves, a
+    jump, a box change and a change of the number of points."""
+    import vesin_b200
+
+    rng = np.random.default_rng(2024)
+    points, box, periodic = W.diamond(4, seed=41)
+    calculator = vesin_b200.NeighborList(cutoff=4.0, full_list=full, skin=1.0)
+    reference = O.ReferenceCPU() if O.reference_available() else None
+    trajectory = [(points, box)]
+    for _ in range(4):  # small moves: the reference keeps its candidates
+        trajectory.append((trajectory[-1][0] + rng.normal(0, 0.03, points.shape), box))
+    jumped = trajectory[-1][0].copy()
+    jumped[5] += 0.9  # more than skin / 2: the reference rebuilds
+    trajectory.append((jumped, box))
+    trajectory.append((jumped, box * 1.01))  # the box breathes
+    trajectory.append((jumped[:-3], box * 1.01))  # three points fewer
+    for step, (p, b) in enumerate(trajectory):
+        got = gpu_compute(p, b, periodic, 4.0, full, "ijSdD", calculator=calculator)
+        if reference is not None:
+            expected = reference.compute(p, b, periodic, 4.0, full, "ijSdD", n_threads=1, skin=1.0)
+        else:
+            expected = O.restated_neighbors(p, b, periodic, 4.0, full, "ijSdD")
+        O.assert_same(got, expected, RTOL_FP64, f"skin, step {step}")
+
+
 @pytest.mark.parametrize("sorted", [False, True])
 @pytest.mark.parametrize("full", [True, False])
 def test_float32_entry_point(full, sorted):

@@ -74,3 +74,21 @@ def test_config_pair_counts():
     assert len(_restated(*W.diamond(5), 5.0, True, "ij")["i"]) == 89072
     assert len(_restated(*W.diamond(5), 5.0, False, "ij")["i"]) == 44536
     assert len(_restated(*W.small_triclinic(), 9.0, True, "ij")["i"]) == 45676
+
+
+def test_reference_with_skin_gives_the_plain_list():
+    """The reference's Verlet cache (vesin/src/verlet.cpp:82-191) is an
+    optimisation: with `skin > 0` every call still returns the exact list at
+    `cutoff`. Pinned here because the engine serves `skin > 0` by rebuilding."""
+    if not O.reference_available():
+        pytest.skip("reference CPU library not built")
+    from vesin_b200 import workloads as W
+
+    rng = np.random.default_rng(99)
+    points, box, periodic = W.diamond(3, seed=2)
+    reference = O.ReferenceCPU()
+    for step in range(6):
+        cached = reference.compute(points, box, periodic, 4.0, step % 2 == 0, "ijSdD", n_threads=1, skin=1.5)
+        plain = O.restated_neighbors(points, box, periodic, 4.0, step % 2 == 0, "ijSdD")
+        O.assert_same(cached, plain, 1e-12, f"skin, step {step}")
+        points = points + rng.normal(0, 0.05 if step != 3 else 0.6, points.shape)
