@@ -463,7 +463,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": n_points * bytes_per_point,
                 "d2h_bytes_per_step": int(n_pairs) * bytes_per_pair,
             },
-            "gpu_launches": 8 * args.steps,  # header + zero, bounds + validate, bin, 2 x scan, 2 x scatter, pairs
+            "gpu_launches": 7 * args.steps,  # header (reset, zero, box check), bin (+ point checks), 2 x scan, 2 x scatter, pairs
             "wall_ms_per_step": wall_ms / args.steps,
             "clocks": clocks.summary(),
         }

@@ -427,15 +427,17 @@ void neighbors(
         timer.begin(VesinB200StageBounds);
         bool histogram_zeroed = false;
         if (speculative) {
-            // the plan is known already: the first kernel also zeroes the cell histogram and
-            // the last block of the bounds kernel checks the plan
+            // the plan is known already: no pass over the points for their bounds. The first
+            // kernel zeroes the cell histogram and checks box and periodicity, the binning
+            // kernel checks every point against the plan
             const size_t cached_cells = static_cast<size_t>(ws.cache.plan.n_cells_total);
             ws.cell_count.reserve(cached_cells * sizeof(int32_t));
-            launch_header_init(ws.d_header, flat_box, periodic, ws.cell_count.as<int32_t>(), cached_cells, stream);
-            launch_bounds_validate(flat_points, n_points, ws.d_header, ws.cache.box, ws.cache.periodic, ws.cache.plan, stream);
+            launch_header_init_speculative(
+                ws.d_header, flat_box, periodic, ws.cell_count.as<int32_t>(), cached_cells, ws.cache.box, ws.cache.periodic, stream
+            );
             histogram_zeroed = true;
         } else {
-            launch_header_init(ws.d_header, flat_box, periodic, nullptr, 0, stream);
+            launch_header_init(ws.d_header, flat_box, periodic, stream);
             launch_bounds(flat_points, n_points, ws.d_header, stream);
         }
         timer.end(VesinB200StageBounds);
@@ -445,7 +447,6 @@ void neighbors(
                 read_header(ws);
             }
             plan_from_header();
-            launch_validate(ws.d_header, ws.cache.box, ws.cache.periodic, ws.cache.plan, n_points, stream);
         }
         const GridPlan& plan = ws.cache.plan;
 
@@ -489,7 +490,7 @@ void neighbors(
         }
         launch_bin(
             flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
-            ws.cell_count.as<int32_t>(), ws.d_header, stream
+            ws.cell_count.as<int32_t>(), ws.d_header, speculative, stream
         );
         timer.end(VesinB200StageBin);
         timer.begin(VesinB200StageScanCells);
@@ -507,7 +508,7 @@ void neighbors(
             timer.collect(VesinB200StageScanCells);
             timer.collect(VesinB200StageScatter);
         };
-        // after a read-back: did the validation kernel accept the plan?
+        // after a read-back: did the kernels accept the plan?
         const auto plan_was_refused = [&]() {
             if ((header.status & STATUS_ABORT_MASK) == 0) {
                 return false;
@@ -517,7 +518,7 @@ void neighbors(
                 throw bad_point_error();
             }
             speculative = false;
-            header_is_fresh = true; // box, periodicity and bounds were just read
+            header_is_fresh = false; // the speculative round did not compute the bounds of the points
             return true;
         };
 
@@ -840,7 +841,7 @@ void neighbors_slab(
     const DeviceHeader& header = *ws.h_header;
 
     timer.begin(VesinB200StageBounds);
-    launch_header_init(ws.d_header, RealView{box, 0}, periodic, nullptr, 0, stream);
+    launch_header_init(ws.d_header, RealView{box, 0}, periodic, stream);
     launch_bounds(flat_points, n_points, ws.d_header, stream);
     timer.end(VesinB200StageBounds);
     VB200_CUDA(cudaGetLastError());
@@ -883,7 +884,7 @@ void neighbors_slab(
     VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
     launch_bin(
         flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_count.as<int32_t>(),
-        ws.d_header, stream
+        ws.d_header, false, stream
     );
     timer.end(VesinB200StageBin);
     timer.begin(VesinB200StageScanCells);

@@ -154,9 +154,30 @@ __device__ __forceinline__ int select_bit(unsigned w, int n) {
 // (vesin/src/types.hpp:159-178).
 // ---------------------------------------------------------------------------
 
-/// Resets the header (block 0) and zeroes `n_zero` counters (all blocks).
+// ---------------------------------------------------------------------------
+// validation of a speculative plan
+// The host builds the grid plan from the box, periodicity and bounds it saw at
+// the end of the PREVIOUS build on the same list, and launches the whole build
+// without waiting for a read-back. The kernels compare that assumption with
+// what is in device memory now: the first kernel checks box and periodicity
+// bit for bit, the binning kernel checks every point (finite, inside the cell
+// window of non-periodic directions). When it does not hold they set
+// STATUS_PLAN_STALE or STATUS_BAD_POINT, every later kernel of the build
+// returns at once, and the host plans again from bounds it then has computed.
+// Replaces the two blocking read-backs of check_box
+// (vesin/src/vesin_cuda.cpp:393-399).
+// ---------------------------------------------------------------------------
+
+struct ExpectedInputs {
+    double box[9];
+    int periodic[3];
+};
+
+/// Resets the header (block 0) and zeroes `n_zero` counters (all blocks). With
+/// `validate`, box and periodicity are compared with what the plan was made for.
 __global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
-    DeviceHeader* header, const RealView box, const bool* periodic, int32_t* __restrict__ zero, size_t n_zero
+    DeviceHeader* header, const RealView box, const bool* periodic, int32_t* __restrict__ zero, size_t n_zero, const int validate,
+    const ExpectedInputs expected
 ) {
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t k = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; k < n_zero; k += stride) {
@@ -181,85 +202,23 @@ __global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
         header->pair_cursor = 0;
         header->run_cursor = 0;
         header->status = 0;
-        header->ticket = 0;
+    }
+    if (validate) {
+        __syncthreads(); // the status word has been reset
+        bool same = true;
+        if (t < 9) {
+            same = __double_as_longlong(load_real(box, t)) == __double_as_longlong(expected.box[t]);
+        }
+        if (t < 3) {
+            same = same && ((periodic[t] ? 1 : 0) == (expected.periodic[t] != 0 ? 1 : 0));
+        }
+        if (!same) {
+            atomicOr(&header->status, STATUS_PLAN_STALE);
+        }
     }
 }
 
-// ---------------------------------------------------------------------------
-// validation of a speculative plan
-// The host builds the grid plan from the box, periodicity and bounds it saw at
-// the end of the PREVIOUS build on the same list, and launches the whole build
-// without waiting for a read-back. The check (the last block of the bounds kernel, or a kernel of its own) compares that assumption with
-// what is in device memory now; when it does not hold it sets
-// STATUS_PLAN_STALE, every later kernel of the build returns at once, and the
-// host plans again from the header it reads back. Replaces the two blocking
-// read-backs of check_box (vesin/src/vesin_cuda.cpp:393-399).
-// ---------------------------------------------------------------------------
-
-struct ExpectedInputs {
-    double box[9];
-    int periodic[3];
-};
-
-/// Run by one thread once the bounds are final.
-__device__ void validate_inputs(DeviceHeader* header_in, const ExpectedInputs& expected, const GridPlan& plan, size_t n_points) {
-    // the bounds were written by other blocks with atomics: read them past L1
-    volatile DeviceHeader* header = header_in;
-    unsigned status = 0;
-    for (int k = 0; k < 9; k++) {
-        if (__double_as_longlong(header->box[k]) != __double_as_longlong(expected.box[k])) {
-            status |= STATUS_PLAN_STALE;
-        }
-    }
-    for (int k = 0; k < 3; k++) {
-        if ((header->periodic[k] != 0) != (expected.periodic[k] != 0)) {
-            status |= STATUS_PLAN_STALE;
-        }
-    }
-    if (header->first_bad != NO_BAD_POINT) {
-        status |= STATUS_BAD_POINT;
-    } else if (n_points != 0) {
-        // along non-periodic directions the cells only cover a window around
-        // the points the plan was made for: every point must still be inside
-        for (int k = 0; k < 3; k++) {
-            if (plan.periodic[k]) {
-                continue;
-            }
-            double lo = 0.0;
-            double hi = 0.0;
-            for (int c = 0; c < 3; c++) {
-                unsigned long long min_key = header->min_key[c];
-                unsigned long long max_key = header->max_key[c];
-                unsigned long long min_bits = (min_key >> 63) ? (min_key & 0x7fffffffffffffffull) : ~min_key;
-                unsigned long long max_bits = (max_key >> 63) ? (max_key & 0x7fffffffffffffffull) : ~max_key;
-                double u = plan.Hinv[c][k];
-                double a = u * __longlong_as_double(static_cast<long long>(min_bits));
-                double b = u * __longlong_as_double(static_cast<long long>(max_bits));
-                lo += fmin(a, b);
-                hi += fmax(a, b);
-            }
-            double window = plan.n_cells[k] / plan.scale[k];
-            if (!(lo >= plan.t0[k]) || !(hi <= plan.t0[k] + window)) {
-                status |= STATUS_PLAN_STALE;
-            }
-        }
-    }
-    if (status != 0) {
-        atomicOr(&header_in->status, status);
-    }
-}
-
-__global__ void validate_kernel(DeviceHeader* header, const ExpectedInputs expected, const GridPlan plan, size_t n_points) {
-    if (threadIdx.x == 0) {
-        validate_inputs(header, expected, plan, n_points);
-    }
-}
-
-/// Bounds of the points; with `validate` the block that finishes last also
-/// checks the speculative plan (the bounds are final by then).
-__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(
-    const RealView points, size_t n, DeviceHeader* header, const int validate, const ExpectedInputs expected, const GridPlan plan
-) {
+__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const RealView points, size_t n, DeviceHeader* header) {
     double lo[3] = {DBL_MAX, DBL_MAX, DBL_MAX};
     double hi[3] = {-DBL_MAX, -DBL_MAX, -DBL_MAX};
     unsigned long long bad = NO_BAD_POINT;
@@ -319,14 +278,6 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(
         if (bad != NO_BAD_POINT) {
             atomicMin(&header->first_bad, bad);
         }
-        if (validate) {
-            __threadfence();
-            const unsigned ticket = atomicAdd(&header->ticket, 1u);
-            if (ticket == gridDim.x - 1) {
-                __threadfence();
-                validate_inputs(header, expected, plan, n);
-            }
-        }
     }
 }
 
@@ -338,9 +289,11 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(
 // (vesin/src/cpu_cell_list.cpp:353-374).
 // ---------------------------------------------------------------------------
 
+/// `check`: the plan is speculative. A point with a non-finite coordinate or
+/// outside the cells of a non-periodic direction refuses it.
 __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
     const RealView points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
-    int32_t* __restrict__ shift, int32_t* __restrict__ cell_count, const DeviceHeader* __restrict__ header
+    int32_t* __restrict__ shift, int32_t* __restrict__ cell_count, DeviceHeader* header, const int check
 ) {
     if (header->status & STATUS_ABORT_MASK) {
         return;
@@ -355,6 +308,10 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
     double rx = load_real(points, 3 * i + 0);
     double ry = load_real(points, 3 * i + 1);
     double rz = load_real(points, 3 * i + 2);
+    if (check && !(isfinite(rx) && isfinite(ry) && isfinite(rz))) {
+        atomicMin(&header->first_bad, static_cast<unsigned long long>(i));
+        atomicOr(&header->status, STATUS_BAD_POINT);
+    }
 
     int cell[3];
     int wrap[3];
@@ -386,6 +343,9 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
         } else {
             wrap[k] = 0;
             cell[k] = min(max(gi, 0), plan.n_cells[k] - 1);
+            if (check && cell[k] != gi && (*reinterpret_cast<volatile unsigned*>(&header->status) & STATUS_PLAN_STALE) == 0) {
+                atomicOr(&header->status, STATUS_PLAN_STALE); // the point left the window the plan covers
+            }
         }
     }
     int linear = (cell[2] * plan.n_cells[1] + cell[1]) * plan.n_cells[0] + cell[0];
@@ -2142,12 +2102,6 @@ void configure_kernels() {
     cudaFuncSetAttribute(pairs_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
 }
 
-void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, int32_t* zero, size_t n_zero, cudaStream_t stream) {
-    size_t blocks = (n_zero + CTA_THREADS * 4 - 1) / (CTA_THREADS * 4);
-    blocks = std::max<size_t>(1, std::min<size_t>(blocks, 148 * 4));
-    header_init_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(header, box, periodic, zero, n_zero);
-}
-
 static ExpectedInputs expected_inputs(const double box[9], const bool periodic[3]) {
     ExpectedInputs expected;
     for (int k = 0; k < 9; k++) {
@@ -2159,41 +2113,43 @@ static ExpectedInputs expected_inputs(const double box[9], const bool periodic[3
     return expected;
 }
 
-static unsigned bounds_blocks(size_t n) {
-    size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    return static_cast<unsigned>(std::min<size_t>(blocks, 148 * 8));
+static unsigned header_blocks(size_t n_zero) {
+    size_t blocks = (n_zero + CTA_THREADS * 4 - 1) / (CTA_THREADS * 4);
+    return static_cast<unsigned>(std::max<size_t>(1, std::min<size_t>(blocks, 148 * 4)));
+}
+
+void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, cudaStream_t stream) {
+    header_init_kernel<<<1, CTA_THREADS, 0, stream>>>(header, box, periodic, nullptr, 0, 0, ExpectedInputs{});
+}
+
+void launch_header_init_speculative(
+    DeviceHeader* header, RealView box, const bool* periodic, int32_t* zero, size_t n_zero, const double expected_box[9],
+    const bool expected_periodic[3], cudaStream_t stream
+) {
+    header_init_kernel<<<header_blocks(n_zero), CTA_THREADS, 0, stream>>>(
+        header, box, periodic, zero, n_zero, 1, expected_inputs(expected_box, expected_periodic)
+    );
 }
 
 void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream) {
     if (n == 0) {
         return;
     }
-    bounds_kernel<<<bounds_blocks(n), CTA_THREADS, 0, stream>>>(points, n, header, 0, ExpectedInputs{}, GridPlan{});
-}
-
-void launch_validate(
-    DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan, size_t n_points, cudaStream_t stream
-) {
-    validate_kernel<<<1, 32, 0, stream>>>(header, expected_inputs(box, periodic), plan, n_points);
-}
-
-void launch_bounds_validate(
-    RealView points, size_t n, DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan,
-    cudaStream_t stream
-) {
-    if (n == 0) {
-        launch_validate(header, box, periodic, plan, n, stream);
-        return;
-    }
-    bounds_kernel<<<bounds_blocks(n), CTA_THREADS, 0, stream>>>(points, n, header, 1, expected_inputs(box, periodic), plan);
+    // every block ends with seven atomics on the same few words of the header: few blocks,
+    // eight points or more per thread
+    size_t blocks = (n + 8 * CTA_THREADS - 1) / (8 * CTA_THREADS);
+    blocks = std::max<size_t>(1, std::min<size_t>(blocks, 148 * 2));
+    bounds_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, header);
 }
 
 void launch_bin(
     RealView points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift, int32_t* cell_count,
-    const DeviceHeader* header, cudaStream_t stream
+    DeviceHeader* header, bool check_points, cudaStream_t stream
 ) {
     size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    bin_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, plan, cell_of, rank, shift, cell_count, header);
+    bin_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(
+        points, n, plan, cell_of, rank, shift, cell_count, header, check_points ? 1 : 0
+    );
 }
 
 size_t scan_tmp_bytes(size_t n) {

@@ -25,7 +25,7 @@ struct DeviceHeader {
     unsigned long long pair_cursor;  // output elements claimed by the fused pass (= its pair total)
     unsigned long long run_cursor;   // runs of work units handed out by the fused pass (dynamic scheduling)
     unsigned int status;             // sticky error bits, see STATUS_*
-    unsigned int ticket;             // blocks of the bounds kernel that are done (the last one validates the plan)
+    unsigned int pad;
     double box[9];                   // copy of the caller's box
     unsigned char periodic[8];       // copy of the caller's periodic flags
 };
@@ -64,31 +64,27 @@ struct RealView {
 
 // ---- launch wrappers (all asynchronous on `stream`) ----
 
-/// Also zeroes `n_zero` int32 counters at `zero` (the cell histogram) when
-/// the caller already knows where they are.
-void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, int32_t* zero, size_t n_zero, cudaStream_t stream);
+void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, cudaStream_t stream);
+
+/// The same for a build that starts from the plan of the previous one: also
+/// zeroes the `n_zero` counters of the cell histogram and compares box and
+/// periodicity in device memory with what that plan was made for (a
+/// difference sets STATUS_PLAN_STALE and every later kernel returns at once).
+void launch_header_init_speculative(
+    DeviceHeader* header, RealView box, const bool* periodic, int32_t* zero, size_t n_zero, const double expected_box[9],
+    const bool expected_periodic[3], cudaStream_t stream
+);
 
 /// Min / max of every coordinate and the first non-finite point.
 void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream);
 
-/// Checks the inputs in device memory against what `plan` was made for (box,
-/// periodicity, extent along non-periodic directions, finite coordinates).
-/// On a mismatch the header's status makes every later kernel return at once.
-void launch_validate(
-    DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan, size_t n_points, cudaStream_t stream
-);
-
-/// launch_bounds and launch_validate in one kernel: the block that finishes
-/// last checks the plan.
-void launch_bounds_validate(
-    RealView points, size_t n, DeviceHeader* header, const double box[9], const bool periodic[3], const GridPlan& plan,
-    cudaStream_t stream
-);
-
 /// Wrap into the cell, pick the cell, histogram with warp-aggregated atomics.
+/// `check_points`: the plan is speculative; a non-finite point sets
+/// STATUS_BAD_POINT (and first_bad), a point outside the cells of a
+/// non-periodic direction STATUS_PLAN_STALE.
 void launch_bin(
     RealView points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift,
-    int32_t* cell_count, const DeviceHeader* header, cudaStream_t stream
+    int32_t* cell_count, DeviceHeader* header, bool check_points, cudaStream_t stream
 );
 
 /// Exclusive scan of int32 counts into int32 starts (n + 1 entries).

@@ -158,7 +158,7 @@ size_t build(
     cudaStream_t stream = nullptr; // legacy default stream
 
     // the header (cursor, status, bounds) is re-initialised by a kernel
-    launch_header_init(d_header, RealView{box, 0}, periodic, nullptr, 0, stream);
+    launch_header_init(d_header, RealView{box, 0}, periodic, stream);
     launch_bounds(RealView{points, 0}, n_points, d_header, stream);
     check(cudaGetLastError(), "launch");
     DeviceHeader header;
@@ -183,7 +183,7 @@ size_t build(
 
     // the histogram is the one array that has to start at zero
     check(cudaMemsetAsync(cell_count, 0, static_cast<size_t>(plan.n_cells_total) * sizeof(int32_t), stream), "cudaMemsetAsync");
-    launch_bin(RealView{points, 0}, n_points, plan, cell_of, rank, shift, cell_count, d_header, stream);
+    launch_bin(RealView{points, 0}, n_points, plan, cell_of, rank, shift, cell_count, d_header, false, stream);
     launch_scan_cells(cell_count, cell_start, static_cast<size_t>(plan.n_cells_total), scan_tmp, stream);
     launch_scatter(RealView{points, 0}, n_points, cell_of, rank, shift, cell_start, sorted, d_header, stream);
     launch_pairs(plan, cell_start, sorted, out, capacity, d_header, nullptr, stream);
