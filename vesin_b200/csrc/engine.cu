@@ -426,7 +426,11 @@ void neighbors(
     for (int round = 0;; round++) {
         timer.begin(VesinB200StageBounds);
         bool histogram_zeroed = false;
-        if (speculative) {
+        // small systems: one CTA resets the header, checks the plan, bins, scans and scatters
+        const bool fused_front = speculative && small_front_fits(n_points, ws.cache.plan);
+        if (fused_front) {
+            // launched below, once the scratch arrays are there
+        } else if (speculative) {
             // the plan is known already: no pass over the points for their bounds. The first
             // kernel zeroes the cell histogram and checks box and periodicity, the binning
             // kernel checks every point against the plan
@@ -484,24 +488,37 @@ void neighbors(
         SortedPoints sorted{ws.sorted_pos.as<double>(), ws.sorted_index.as<int32_t>(), ws.sorted_shift.as<int32_t>()};
 
         // ---- cell list ----
-        timer.begin(VesinB200StageBin);
-        if (!histogram_zeroed) {
-            VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
+        if (fused_front || (!speculative && small_front_fits(n_points, plan))) {
+            timer.begin(VesinB200StageBin);
+            launch_small_front(
+                flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
+                ws.cell_start.as<int32_t>(), sorted, ws.d_header, flat_box, periodic, speculative, ws.cache.box, ws.cache.periodic, stream
+            );
+            timer.end(VesinB200StageBin);
+            timer.begin(VesinB200StageScanCells);
+            timer.end(VesinB200StageScanCells);
+            timer.begin(VesinB200StageScatter);
+            timer.end(VesinB200StageScatter);
+        } else {
+            timer.begin(VesinB200StageBin);
+            if (!histogram_zeroed) {
+                VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
+            }
+            launch_bin(
+                flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
+                ws.cell_count.as<int32_t>(), ws.d_header, speculative, stream
+            );
+            timer.end(VesinB200StageBin);
+            timer.begin(VesinB200StageScanCells);
+            launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
+            timer.end(VesinB200StageScanCells);
+            timer.begin(VesinB200StageScatter);
+            launch_scatter(
+                flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(),
+                sorted, ws.d_header, stream
+            );
+            timer.end(VesinB200StageScatter);
         }
-        launch_bin(
-            flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
-            ws.cell_count.as<int32_t>(), ws.d_header, speculative, stream
-        );
-        timer.end(VesinB200StageBin);
-        timer.begin(VesinB200StageScanCells);
-        launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
-        timer.end(VesinB200StageScanCells);
-        timer.begin(VesinB200StageScatter);
-        launch_scatter(
-            flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(),
-            sorted, ws.d_header, stream
-        );
-        timer.end(VesinB200StageScatter);
         const auto collect_front_stages = [&]() {
             timer.collect(VesinB200StageBounds);
             timer.collect(VesinB200StageBin);

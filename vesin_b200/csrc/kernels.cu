@@ -173,20 +173,9 @@ struct ExpectedInputs {
     int periodic[3];
 };
 
-/// Resets the header (block 0) and zeroes `n_zero` counters (all blocks). With
-/// `validate`, box and periodicity are compared with what the plan was made for.
-__global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
-    DeviceHeader* header, const RealView box, const bool* periodic, int32_t* __restrict__ zero, size_t n_zero, const int validate,
-    const ExpectedInputs expected
-) {
-    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t k = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; k < n_zero; k += stride) {
-        zero[k] = 0;
-    }
-    if (blockIdx.x != 0) {
-        return;
-    }
-    int t = threadIdx.x;
+/// Reset of the header by the first threads of one block: box and periodicity
+/// are copied, cursors and status cleared.
+__device__ __forceinline__ void reset_header(DeviceHeader* header, const RealView& box, const bool* periodic, int t) {
     if (t < 3) {
         header->min_key[t] = ~0ull;
         header->max_key[t] = 0ull;
@@ -203,18 +192,40 @@ __global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
         header->run_cursor = 0;
         header->status = 0;
     }
+}
+
+/// Box and periodicity in device memory against what the plan was made for;
+/// call after a barrier that follows reset_header.
+__device__ __forceinline__ void check_box(DeviceHeader* header, const RealView& box, const bool* periodic, const ExpectedInputs& expected, int t) {
+    bool same = true;
+    if (t < 9) {
+        same = __double_as_longlong(load_real(box, t)) == __double_as_longlong(expected.box[t]);
+    }
+    if (t < 3) {
+        same = same && ((periodic[t] ? 1 : 0) == (expected.periodic[t] != 0 ? 1 : 0));
+    }
+    if (!same) {
+        atomicOr(&header->status, STATUS_PLAN_STALE);
+    }
+}
+
+/// Resets the header (block 0) and zeroes `n_zero` counters (all blocks). With
+/// `validate`, box and periodicity are compared with what the plan was made for.
+__global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
+    DeviceHeader* header, const RealView box, const bool* periodic, int32_t* __restrict__ zero, size_t n_zero, const int validate,
+    const ExpectedInputs expected
+) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t k = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; k < n_zero; k += stride) {
+        zero[k] = 0;
+    }
+    if (blockIdx.x != 0) {
+        return;
+    }
+    reset_header(header, box, periodic, threadIdx.x);
     if (validate) {
         __syncthreads(); // the status word has been reset
-        bool same = true;
-        if (t < 9) {
-            same = __double_as_longlong(load_real(box, t)) == __double_as_longlong(expected.box[t]);
-        }
-        if (t < 3) {
-            same = same && ((periodic[t] ? 1 : 0) == (expected.periodic[t] != 0 ? 1 : 0));
-        }
-        if (!same) {
-            atomicOr(&header->status, STATUS_PLAN_STALE);
-        }
+        check_box(header, box, periodic, expected, threadIdx.x);
     }
 }
 
@@ -289,22 +300,12 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const RealView poin
 // (vesin/src/cpu_cell_list.cpp:353-374).
 // ---------------------------------------------------------------------------
 
-/// `check`: the plan is speculative. A point with a non-finite coordinate or
-/// outside the cells of a non-periodic direction refuses it.
-__global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
-    const RealView points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
-    int32_t* __restrict__ shift, int32_t* __restrict__ cell_count, DeviceHeader* header, const int check
+/// Cell (linear index) and wrap shift of point i. `check`: the plan is
+/// speculative; a point with a non-finite coordinate or outside the cells of a
+/// non-periodic direction refuses it.
+__device__ __forceinline__ int locate_point(
+    const RealView& points, size_t i, const GridPlan& plan, DeviceHeader* header, const int check, int wrap[3]
 ) {
-    if (header->status & STATUS_ABORT_MASK) {
-        return;
-    }
-    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    bool active = i < n;
-    unsigned active_mask = __ballot_sync(FULL_MASK, active);
-    if (!active) {
-        return;
-    }
-
     double rx = load_real(points, 3 * i + 0);
     double ry = load_real(points, 3 * i + 1);
     double rz = load_real(points, 3 * i + 2);
@@ -314,7 +315,6 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
     }
 
     int cell[3];
-    int wrap[3];
 #pragma unroll
     for (int k = 0; k < 3; k++) {
         double t = rx * plan.Hinv[0][k] + ry * plan.Hinv[1][k] + rz * plan.Hinv[2][k];
@@ -348,7 +348,24 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
             }
         }
     }
-    int linear = (cell[2] * plan.n_cells[1] + cell[1]) * plan.n_cells[0] + cell[0];
+    return (cell[2] * plan.n_cells[1] + cell[1]) * plan.n_cells[0] + cell[0];
+}
+
+__global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
+    const RealView points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
+    int32_t* __restrict__ shift, int32_t* __restrict__ cell_count, DeviceHeader* header, const int check
+) {
+    if (header->status & STATUS_ABORT_MASK) {
+        return;
+    }
+    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    bool active = i < n;
+    unsigned active_mask = __ballot_sync(FULL_MASK, active);
+    if (!active) {
+        return;
+    }
+    int wrap[3];
+    const int linear = locate_point(points, i, plan, header, check, wrap);
 
     // warp-aggregated histogram: one atomic per distinct cell in the warp
     unsigned peers = __match_any_sync(active_mask, linear);
@@ -564,6 +581,119 @@ __global__ void __launch_bounds__(CTA_THREADS) gather_records_kernel(
     size_t i = static_cast<size_t>(sorted.index[p]);
     sorted.pos[f] = load_real(points, 3 * i + c);
     sorted.shift[f] = shift[3 * i + c];
+}
+
+// ---------------------------------------------------------------------------
+// cell list of a small system in one launch
+// A few thousand points do not fill the GPU; what their build costs is the
+// chain of launches. One CTA does what header_init, bin, the scan and the two
+// scatter kernels do for large systems: histogram in shared memory, scan,
+// scatter, with the same arithmetic per point.
+// ---------------------------------------------------------------------------
+
+constexpr int SMALL_FRONT_THREADS = 1024;
+constexpr int SMALL_FRONT_MAX_CELLS = 4096;
+constexpr size_t SMALL_FRONT_MAX_POINTS = 16384;
+
+__global__ void __launch_bounds__(SMALL_FRONT_THREADS) small_front_kernel(
+    const RealView points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
+    int32_t* __restrict__ shift, int32_t* __restrict__ cell_start, SortedPoints sorted, DeviceHeader* header, const RealView box,
+    const bool* periodic, const int speculative, const ExpectedInputs expected
+) {
+    __shared__ int hist[SMALL_FRONT_MAX_CELLS];
+    __shared__ int warp_sums[SMALL_FRONT_THREADS / 32];
+    __shared__ unsigned s_status;
+    const int t = threadIdx.x;
+    const int n_cells = plan.n_cells_total;
+    if (speculative) {
+        // the build starts here: reset the header, then check the plan's assumptions
+        reset_header(header, box, periodic, t);
+    }
+    for (int c = t; c < n_cells; c += SMALL_FRONT_THREADS) {
+        hist[c] = 0;
+    }
+    __syncthreads();
+    if (speculative) {
+        check_box(header, box, periodic, expected, t);
+        __syncthreads();
+    }
+    // one thread reads the status for all: the binning below may set bits while others still look
+    if (t == 0) {
+        s_status = *reinterpret_cast<volatile unsigned*>(&header->status);
+    }
+    __syncthreads();
+    if (s_status & STATUS_ABORT_MASK) {
+        return;
+    }
+
+    // ---- histogram: the value the atomic returns is the slot of the point in its cell ----
+    for (size_t i = t; i < n; i += SMALL_FRONT_THREADS) {
+        int wrap[3];
+        const int linear = locate_point(points, i, plan, header, speculative, wrap);
+        cell_of[i] = linear;
+        rank[i] = atomicAdd(&hist[linear], 1);
+        shift[3 * i + 0] = wrap[0];
+        shift[3 * i + 1] = wrap[1];
+        shift[3 * i + 2] = wrap[2];
+    }
+    __syncthreads();
+
+    // ---- exclusive scan of the histogram: consecutive cells per thread ----
+    const int per_thread = (n_cells + SMALL_FRONT_THREADS - 1) / SMALL_FRONT_THREADS; // at most 4
+    const int first = t * per_thread;
+    int counts[SMALL_FRONT_MAX_CELLS / SMALL_FRONT_THREADS];
+    int mine = 0;
+#pragma unroll
+    for (int k = 0; k < SMALL_FRONT_MAX_CELLS / SMALL_FRONT_THREADS; k++) {
+        const int c = first + k;
+        counts[k] = (k < per_thread && c < n_cells) ? hist[c] : 0;
+        mine += counts[k];
+    }
+    const int lane = t & 31;
+    const int warp = t >> 5;
+    int inclusive = mine;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+        const int up = __shfl_up_sync(FULL_MASK, inclusive, offset);
+        if (lane >= offset) {
+            inclusive += up;
+        }
+    }
+    if (lane == 31) {
+        warp_sums[warp] = inclusive;
+    }
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < warp; w++) {
+        before += warp_sums[w];
+    }
+    int prefix = before + inclusive - mine;
+    __syncthreads(); // every thread has read its counts: the histogram becomes the table of cell starts
+#pragma unroll
+    for (int k = 0; k < SMALL_FRONT_MAX_CELLS / SMALL_FRONT_THREADS; k++) {
+        const int c = first + k;
+        if (k < per_thread && c < n_cells) {
+            hist[c] = prefix;
+            cell_start[c] = prefix;
+            prefix += counts[k];
+        }
+    }
+    if (t == SMALL_FRONT_THREADS - 1) {
+        cell_start[n_cells] = prefix;
+    }
+    __syncthreads();
+
+    // ---- scatter into the cell-sorted records (cell_of, rank, shift were written by this thread) ----
+    for (size_t i = t; i < n; i += SMALL_FRONT_THREADS) {
+        const size_t p = static_cast<size_t>(hist[cell_of[i]]) + rank[i];
+        sorted.pos[3 * p + 0] = load_real(points, 3 * i + 0);
+        sorted.pos[3 * p + 1] = load_real(points, 3 * i + 1);
+        sorted.pos[3 * p + 2] = load_real(points, 3 * i + 2);
+        sorted.index[p] = static_cast<int32_t>(i);
+        sorted.shift[3 * p + 0] = shift[3 * i + 0];
+        sorted.shift[3 * p + 1] = shift[3 * i + 1];
+        sorted.shift[3 * p + 2] = shift[3 * i + 2];
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -2254,6 +2384,21 @@ void launch_pairs(
     } else {
         pairs_kernel<false, false><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, nullptr);
     }
+}
+
+bool small_front_fits(size_t n_points, const GridPlan& plan) {
+    return n_points != 0 && n_points <= SMALL_FRONT_MAX_POINTS && plan.n_cells_total <= SMALL_FRONT_MAX_CELLS;
+}
+
+void launch_small_front(
+    RealView points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift, int32_t* cell_start,
+    SortedPoints sorted, DeviceHeader* header, RealView box, const bool* periodic, bool speculative, const double expected_box[9],
+    const bool expected_periodic[3], cudaStream_t stream
+) {
+    small_front_kernel<<<1, SMALL_FRONT_THREADS, 0, stream>>>(
+        points, n, plan, cell_of, rank, shift, cell_start, sorted, header, box, periodic, speculative ? 1 : 0,
+        expected_inputs(expected_box, expected_periodic)
+    );
 }
 
 void launch_scan_units(

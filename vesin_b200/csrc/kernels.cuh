@@ -103,6 +103,18 @@ void launch_scatter(
     const int32_t* cell_start, SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
 );
 
+/// Small systems: header reset and plan check (when `speculative`), binning,
+/// scan and scatter in one launch of one CTA. Same results as
+/// launch_header_init_speculative + launch_bin + launch_scan_cells +
+/// launch_scatter (the order of the points inside a cell may differ, as it may
+/// between two runs of those). Use when small_front_fits().
+bool small_front_fits(size_t n_points, const GridPlan& plan);
+void launch_small_front(
+    RealView points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift, int32_t* cell_start,
+    SortedPoints sorted, DeviceHeader* header, RealView box, const bool* periodic, bool speculative, const double expected_box[9],
+    const bool expected_periodic[3], cudaStream_t stream
+);
+
 /// Exclusive scan of uint64 counts into uint64 starts (n + 1 entries); the
 /// grand total also goes to *total.
 void launch_scan_units(
