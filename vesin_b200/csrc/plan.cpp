@@ -286,9 +286,7 @@ void make_slab_window(GridPlan& plan, int axis, double lower, double upper, size
     if ((upper - lower) + 2.0 * width > 1.0) {
         throw std::runtime_error("slab plus halo is longer than the box: the box must span at least two slabs plus two cutoffs");
     }
-    // undo the contribution of the old grid along `axis` ...
-    const int old_cells = plan.n_cells[axis];
-    // ... and install the window: one halo layer, the owned layers, one halo layer
+    // install the window: one halo layer, the owned layers, one halo layer
     plan.n_cells[axis] = static_cast<int32_t>(layers) + 2;
     plan.n_search[axis] = 1;
     plan.t0[axis] = lower - width;
@@ -297,7 +295,6 @@ void make_slab_window(GridPlan& plan, int axis, double lower, double upper, size
         plan.cell_vec[axis][c] = plan.H[axis][c] * width;
         plan.origin[c] += plan.t0[axis] * plan.H[axis][c];
     }
-    (void)old_cells;
     plan.window_axis = axis;
     plan.n_owned = static_cast<int32_t>(n_owned);
     plan.n_cells_total = plan.n_cells[0] * plan.n_cells[1] * plan.n_cells[2];
