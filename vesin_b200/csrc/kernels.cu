@@ -44,6 +44,19 @@ __device__ __forceinline__ double load_real(const RealView& view, size_t k) {
     return view.is_float ? static_cast<double>(static_cast<const float*>(view.data)[k]) : static_cast<const double*>(view.data)[k];
 }
 
+// Programmatic dependent launch: the kernels of a build form a chain on one
+// stream, each reading what the one before wrote. A kernel lets the next one
+// be scheduled as soon as all of its own blocks are running, and waits for the
+// one before it (complete, memory visible) before it touches anything. Launch
+// latency and block scheduling of the short kernels then overlap with the tail
+// of their predecessor. Both instructions do nothing in a plain launch.
+__device__ __forceinline__ void let_next_kernel_start() {
+    asm volatile("griddepcontrol.launch_dependents;");
+}
+__device__ __forceinline__ void wait_for_previous_kernel() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ unsigned lanemask_lt() {
     unsigned mask;
     asm("mov.u32 %0, %%lanemask_lt;" : "=r"(mask));
@@ -215,6 +228,7 @@ __global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
     DeviceHeader* header, const RealView box, const bool* periodic, int32_t* __restrict__ zero, size_t n_zero, const int validate,
     const ExpectedInputs expected
 ) {
+    let_next_kernel_start();
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t k = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; k < n_zero; k += stride) {
         zero[k] = 0;
@@ -355,6 +369,8 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
     const RealView points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
     int32_t* __restrict__ shift, int32_t* __restrict__ cell_count, DeviceHeader* header, const int check
 ) {
+    let_next_kernel_start();
+    wait_for_previous_kernel();
     if (header->status & STATUS_ABORT_MASK) {
         return;
     }
@@ -398,6 +414,8 @@ constexpr int SCAN_TILE = CTA_THREADS * SCAN_ITEMS;
 
 template <typename TIn>
 __global__ void __launch_bounds__(CTA_THREADS) scan_tile_sums_kernel(const TIn* __restrict__ in, size_t n, unsigned long long* __restrict__ tile_sums) {
+    let_next_kernel_start();
+    wait_for_previous_kernel();
     size_t base = static_cast<size_t>(blockIdx.x) * SCAN_TILE;
     unsigned long long sum = 0;
 #pragma unroll
@@ -476,6 +494,8 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
     const TIn* __restrict__ in, TOut* __restrict__ out, size_t n, const unsigned long long* __restrict__ tile_offsets,
     unsigned long long* __restrict__ total_out
 ) {
+    let_next_kernel_start();
+    wait_for_previous_kernel();
     // each thread owns SCAN_ITEMS consecutive elements
     size_t base = static_cast<size_t>(blockIdx.x) * SCAN_TILE + static_cast<size_t>(threadIdx.x) * SCAN_ITEMS;
     unsigned long long values[SCAN_ITEMS];
@@ -557,6 +577,8 @@ __global__ void __launch_bounds__(CTA_THREADS) scatter_index_kernel(
     size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank, const int32_t* __restrict__ cell_start,
     int32_t* __restrict__ sorted_index, const DeviceHeader* __restrict__ header
 ) {
+    let_next_kernel_start();
+    wait_for_previous_kernel();
     size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n || (header->status & STATUS_ABORT_MASK)) {
         return;
@@ -572,6 +594,8 @@ __global__ void __launch_bounds__(CTA_THREADS) scatter_index_kernel(
 __global__ void __launch_bounds__(CTA_THREADS) gather_records_kernel(
     const RealView points, size_t n, const int32_t* __restrict__ shift, SortedPoints sorted, const DeviceHeader* __restrict__ header
 ) {
+    let_next_kernel_start();
+    wait_for_previous_kernel();
     size_t f = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (f >= 3 * n || (header->status & STATUS_ABORT_MASK)) {
         return;
@@ -603,6 +627,8 @@ __global__ void __launch_bounds__(SMALL_FRONT_THREADS) small_front_kernel(
     __shared__ int hist[SMALL_FRONT_MAX_CELLS];
     __shared__ int warp_sums[SMALL_FRONT_THREADS / 32];
     __shared__ unsigned s_status;
+    let_next_kernel_start();
+    wait_for_previous_kernel();
     const int t = threadIdx.x;
     const int n_cells = plan.n_cells_total;
     if (speculative) {
@@ -1709,8 +1735,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     const float cutoff2_lo = plan.cutoff2_lo;
     const float cutoff2_hi = plan.cutoff2_hi;
 
+    wait_for_previous_kernel();
     if (header->status & STATUS_ABORT_MASK) {
-        return; // the validation kernel refused the plan: the host will redo the build
+        return; // the plan was refused: the host will redo the build
     }
     PHASE_CLOCK_START();
     if (threadIdx.x == 0) {
@@ -2207,6 +2234,22 @@ extern "C" __attribute__((visibility("default"))) void vesin_b200_debug_phase_cl
 }
 #endif
 namespace {
+/// Launch as a link of the chain of a build (see let_next_kernel_start).
+template <typename... KernelArgs, typename... Args>
+void launch_chained(void (*kernel)(KernelArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(block);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 int pair_grid(int n_units, int per_sm) {
     int device = 0;
     int sms = 148;
@@ -2277,8 +2320,9 @@ void launch_bin(
     DeviceHeader* header, bool check_points, cudaStream_t stream
 ) {
     size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    bin_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(
-        points, n, plan, cell_of, rank, shift, cell_count, header, check_points ? 1 : 0
+    launch_chained(
+        bin_kernel, static_cast<unsigned>(blocks), CTA_THREADS, 0, stream, points, n, plan, cell_of, rank, shift, cell_count, header,
+        check_points ? 1 : 0
     );
 }
 
@@ -2291,10 +2335,10 @@ template <typename TIn, typename TOut>
 static void launch_scan(const TIn* counts, TOut* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream) {
     auto* tile_sums = static_cast<unsigned long long*>(tmp);
     size_t tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
-    scan_tile_sums_kernel<TIn><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, n, tile_sums);
+    launch_chained(scan_tile_sums_kernel<TIn>, static_cast<unsigned>(tiles), CTA_THREADS, 0, stream, counts, n, tile_sums);
     if (tiles <= 2048) {
         // short spine: every block of the second kernel adds up the tile sums before it
-        scan_apply_kernel<TIn, TOut, true><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, starts, n, tile_sums, total);
+        launch_chained(scan_apply_kernel<TIn, TOut, true>, static_cast<unsigned>(tiles), CTA_THREADS, 0, stream, counts, starts, n, tile_sums, total);
     } else {
         scan_spine_kernel<<<1, CTA_THREADS, 0, stream>>>(tile_sums, tiles, total);
         scan_apply_kernel<TIn, TOut, false><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, starts, n, tile_sums, nullptr);
@@ -2316,9 +2360,9 @@ void launch_scatter(
     SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
 ) {
     size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    scatter_index_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(n, cell_of, rank, cell_start, sorted.index, header);
+    launch_chained(scatter_index_kernel, static_cast<unsigned>(blocks), CTA_THREADS, 0, stream, n, cell_of, rank, cell_start, sorted.index, header);
     blocks = (3 * n + CTA_THREADS - 1) / CTA_THREADS;
-    gather_records_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, shift, sorted, header);
+    launch_chained(gather_records_kernel, static_cast<unsigned>(blocks), CTA_THREADS, 0, stream, points, n, shift, sorted, header);
 }
 
 void launch_count(
@@ -2380,9 +2424,15 @@ void launch_pairs(
             pairs_kernel<false, true><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, global_index);
         }
     } else if (plan.full) {
-        pairs_kernel<true, false><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, nullptr);
+        launch_chained(
+            pairs_kernel<true, false>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run,
+            static_cast<const long long*>(nullptr)
+        );
     } else {
-        pairs_kernel<false, false><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, nullptr);
+        launch_chained(
+            pairs_kernel<false, false>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run,
+            static_cast<const long long*>(nullptr)
+        );
     }
 }
 
