@@ -406,7 +406,9 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
 // block whose 8192-cell limit caps the reference's grid) and the pre-sized
 // output + global append counter (vesin/src/vesin_cuda.cpp:866-886,
 // cell_list.cu:643-668): per-point counts are scanned into private rows.
-// Three launches (tile sums, spine, apply) and no inter-CTA waiting.
+// Two launches (tile sums; apply, every block adding up the sums of the tiles
+// before its own) up to 2048 tiles, three beyond (tile sums, spine, apply); no
+// inter-CTA waiting.
 // ---------------------------------------------------------------------------
 
 constexpr int SCAN_ITEMS = 8;
