@@ -863,12 +863,16 @@ __device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_
     return total;
 }
 
-/// Segment that holds `slot`: last t with slot0[t] <= slot.
+/// Segment that holds `slot`: last t with slot0[t] <= slot, among the first
+/// 2^STEPS segments (entries past the stencil hold the total, so any power of
+/// two that covers the stencil will do).
+template <int STEPS = 7>
 __device__ __forceinline__ int find_segment(const SegmentTable& table, int slot) {
+    static_assert((1 << STEPS) <= SEG_MAX, "the table has SEG_MAX entries");
     int lo = 0;
-    int hi = SEG_MAX; // slot0[hi] > slot always holds for slot < total
+    int hi = 1 << STEPS; // slot0[hi] > slot always holds for slot < total
 #pragma unroll
-    for (int step = 0; step < 7; step++) {
+    for (int step = 0; step < STEPS; step++) {
         int mid = (lo + hi) >> 1;
         if (table.slot0[mid] <= slot) {
             lo = mid;
@@ -1566,6 +1570,72 @@ __device__ __forceinline__ int setup_half_segments(
     return total;
 }
 
+/// Decisions of one lane's home point on BITS consecutive candidates of word `w`
+/// of the staged batch, starting at bit `first_bit`: fp32 screen of every
+/// candidate, the exact fp64 predicate for those too close to the cutoff for
+/// fp32. Returns one bit per candidate that is a pair.
+template <int BITS>
+__device__ __forceinline__ unsigned decide_piece(
+    const FusedShared& sh, const GridPlan& plan, int w, int first_bit, int batch0, int home_row_slots, int il, unsigned long long ax2,
+    unsigned long long ay2, unsigned long long az2, unsigned long long an2, float cutoff2_lo, float cutoff2_hi, double rix, double riy,
+    double riz, int si0, int si1, int si2
+) {
+    constexpr unsigned ALL = (BITS == 32) ? 0xffffffffu : ((1u << (BITS & 31)) - 1u);
+    unsigned inside = 0; // surely inside the cutoff
+    unsigned near = 0;   // inside, or too close to the cutoff for fp32
+    // four candidates per (broadcast) load, two per packed instruction; every component goes
+    // through the same roundings as the scalar expression fma(cx, ax, fma(cy, ay, fma(cz, az, cn + an)))
+    const int first_slot = w * 32 + first_bit;
+    const ulonglong2* cx = reinterpret_cast<const ulonglong2*>(sh.near_x + first_slot);
+    const ulonglong2* cy = reinterpret_cast<const ulonglong2*>(sh.near_y + first_slot);
+    const ulonglong2* cz = reinterpret_cast<const ulonglong2*>(sh.near_z + first_slot);
+    const ulonglong2* cn = reinterpret_cast<const ulonglong2*>(sh.near_n + first_slot);
+#pragma unroll
+    for (int k = 0; k < BITS / 4; k++) {
+        const ulonglong2 x4 = cx[k];
+        const ulonglong2 y4 = cy[k];
+        const ulonglong2 z4 = cz[k];
+        const ulonglong2 n4 = cn[k];
+        float d2[4];
+        unpack_f32x2(fma_f32x2(x4.x, ax2, fma_f32x2(y4.x, ay2, fma_f32x2(z4.x, az2, add_f32x2(n4.x, an2)))), d2[0], d2[1]);
+        unpack_f32x2(fma_f32x2(x4.y, ax2, fma_f32x2(y4.y, ay2, fma_f32x2(z4.y, az2, add_f32x2(n4.y, an2)))), d2[2], d2[3]);
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            if (d2[c] < cutoff2_lo) {
+                inside |= 1u << (4 * k + c);
+            }
+            if (d2[c] <= cutoff2_hi) {
+                near |= 1u << (4 * k + c);
+            }
+        }
+    }
+    // half shell inside the unit's own row: only slots after the point's own
+    unsigned keep = ALL;
+    const int piece_slot = batch0 + first_slot;
+    if (piece_slot < home_row_slots) {
+        const int own = il - piece_slot; // bit of the point itself in this piece
+        const unsigned after = (own < 0) ? ALL : ((own >= BITS - 1) ? 0u : ((ALL << (own + 1)) & ALL));
+        const int row_bits = home_row_slots - piece_slot; // bits of this piece inside the row
+        const unsigned in_row = (row_bits >= BITS) ? ALL : ((1u << row_bits) - 1u);
+        keep = (after | ~in_row) & ALL;
+    }
+    inside &= keep;
+    unsigned band = near & keep & ~inside;
+    while (band != 0) {
+        // the exact fp64 predicate of the reference decides
+        const int b = __ffs(band) - 1;
+        band &= band - 1;
+        const int s = first_slot + b;
+        double vx, vy, vz;
+        const int4 cand = sh.sj[s];
+        const double d2_exact = exact_pair(plan, rix, riy, riz, sh.x[s], sh.y[s], sh.z[s], cand.x + si0, cand.y + si1, cand.z + si2, vx, vy, vz);
+        if (d2_exact < plan.cutoff2) {
+            inside |= 1u << b;
+        }
+    }
+    return inside;
+}
+
 /// Write `n_valid` consecutive pairs starting at output element `first`:
 /// lane l holds pair l. 12- and 24-byte elements are transposed through
 /// shared memory so that every store instruction covers one contiguous span.
@@ -1840,7 +1910,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                 //      found by bisection), so all loads of a batch are in flight at once ----
                 for (int s = threadIdx.x; s < batch_slots; s += CTA_THREADS) {
                     const int slot = batch0 + s;
-                    const int t = find_segment(sh.table, slot);
+                    const int t = (unit.n_stencil <= 32) ? find_segment<5>(sh.table, slot) : find_segment<7>(sh.table, slot);
                     const size_t p = static_cast<size_t>(sh.table.start[t]) + (slot - sh.table.slot0[t]);
                     const double px = sorted.pos[3 * p + 0];
                     const double py = sorted.pos[3 * p + 1];
@@ -1861,9 +1931,18 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         index_j = sorted.index[p];
                     }
                     sh.sj[s] = make_int4(r0, r1, r2, index_j);
-                    const float fx = static_cast<float>(px + (r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0]) - sh.centre[0]);
-                    const float fy = static_cast<float>(py + (r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1]) - sh.centre[1]);
-                    const float fz = static_cast<float>(pz + (r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2]) - sh.centre[2]);
+                    // image of the candidate seen from this unit (most candidates of a large box have none)
+                    double ix = px;
+                    double iy = py;
+                    double iz = pz;
+                    if ((r0 | r1 | r2) != 0) {
+                        ix += r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0];
+                        iy += r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1];
+                        iz += r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2];
+                    }
+                    const float fx = static_cast<float>(ix - sh.centre[0]);
+                    const float fy = static_cast<float>(iy - sh.centre[1]);
+                    const float fz = static_cast<float>(iz - sh.centre[2]);
                     sh.near_x[s] = fx;
                     sh.near_y[s] = fy;
                     sh.near_z[s] = fz;
@@ -1933,62 +2012,24 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     const unsigned long long az2 = pack_f32x2(az, az);
                     const unsigned long long an2 = pack_f32x2(an, an);
 
-                    for (int w = warp; w < batch_words; w += CTA_WARPS) {
-                        unsigned inside = 0; // surely inside the cutoff
-                        unsigned near = 0;   // inside, or too close to the cutoff for fp32
-                        // four candidates per (broadcast) load, two per packed instruction; every
-                        // component goes through the same roundings as the scalar expression
-                        // fma(cx, ax, fma(cy, ay, fma(cz, az, cn + an)))
-                        const ulonglong2* cx = reinterpret_cast<const ulonglong2*>(sh.near_x + w * 32);
-                        const ulonglong2* cy = reinterpret_cast<const ulonglong2*>(sh.near_y + w * 32);
-                        const ulonglong2* cz = reinterpret_cast<const ulonglong2*>(sh.near_z + w * 32);
-                        const ulonglong2* cn = reinterpret_cast<const ulonglong2*>(sh.near_n + w * 32);
-#pragma unroll
-                        for (int k = 0; k < 8; k++) {
-                            const ulonglong2 x4 = cx[k];
-                            const ulonglong2 y4 = cy[k];
-                            const ulonglong2 z4 = cz[k];
-                            const ulonglong2 n4 = cn[k];
-                            float d2[4];
-                            unpack_f32x2(fma_f32x2(x4.x, ax2, fma_f32x2(y4.x, ay2, fma_f32x2(z4.x, az2, add_f32x2(n4.x, an2)))), d2[0], d2[1]);
-                            unpack_f32x2(fma_f32x2(x4.y, ax2, fma_f32x2(y4.y, ay2, fma_f32x2(z4.y, az2, add_f32x2(n4.y, an2)))), d2[2], d2[3]);
-#pragma unroll
-                            for (int c = 0; c < 4; c++) {
-                                if (d2[c] < cutoff2_lo) {
-                                    inside |= 1u << (4 * k + c);
-                                }
-                                if (d2[c] <= cutoff2_hi) {
-                                    near |= 1u << (4 * k + c);
-                                }
-                            }
-                        }
-                        // half shell inside the unit's own row: only slots after the point's own
-                        unsigned keep = 0xffffffffu;
-                        const int word_slot = batch0 + w * 32;
-                        if (word_slot < home_row_slots) {
-                            const int own = il - word_slot; // bit of the point itself in this word
-                            const unsigned after = (own < 0) ? 0xffffffffu : ((own >= 31) ? 0u : (0xffffffffu << (own + 1)));
-                            const int row_bits = home_row_slots - word_slot; // bits of this word inside the row
-                            const unsigned in_row = (row_bits >= 32) ? 0xffffffffu : ((1u << row_bits) - 1u);
-                            keep = after | ~in_row;
-                        }
-                        inside &= keep;
-                        unsigned band = near & keep & ~inside;
-                        while (band != 0) {
-                            // the exact fp64 predicate of the reference decides
-                            const int b = __ffs(band) - 1;
-                            band &= band - 1;
-                            const int s = w * 32 + b;
-                            double vx, vy, vz;
-                            const int4 cand = sh.sj[s];
-                            const double d2_exact = exact_pair(
-                                plan, rix, riy, riz, sh.x[s], sh.y[s], sh.z[s], cand.x + si0, cand.y + si1, cand.z + si2, vx, vy, vz
+                    if (batch_words <= CTA_WARPS) {
+                        // a word of 32 candidates per warp
+                        if (warp < batch_words) {
+                            sh.mask[warp * TILE_POINTS + lane] = decide_piece<32>(
+                                sh, plan, warp, 0, batch0, home_row_slots, il, ax2, ay2, az2, an2, cutoff2_lo, cutoff2_hi, rix, riy, riz, si0, si1, si2
                             );
-                            if (d2_exact < plan.cutoff2) {
-                                inside |= 1u << b;
-                            }
                         }
-                        sh.mask[w * TILE_POINTS + lane] = inside;
+                    } else {
+                        // more words than warps: halves of words, so that no warp does two words while others do one
+                        unsigned short* halves = reinterpret_cast<unsigned short*>(sh.mask);
+                        for (int piece = warp; piece < 2 * batch_words; piece += CTA_WARPS) {
+                            const int half = (piece >= batch_words) ? 1 : 0;
+                            const int w = piece - half * batch_words;
+                            halves[2 * (w * TILE_POINTS + lane) + half] = static_cast<unsigned short>(decide_piece<16>(
+                                sh, plan, w, 16 * half, batch0, home_row_slots, il, ax2, ay2, az2, an2, cutoff2_lo, cutoff2_hi, rix, riy, riz, si0, si1,
+                                si2
+                            ));
+                        }
                     }
                     PHASE_MARK(4); // home points + decisions
                     __syncthreads();
