@@ -447,9 +447,9 @@ def run_ours(args):
                 "frac": (achieved / peak) if achieved else None,
                 "peak_source": peak_source,
                 # dram__bytes_read + dram__bytes_write of pairs_kernel in the ncu capture of the 110 592-atom
-                # case of the same kernel (profiles/pairs_kernel_diamond110k.md: 538.9 MB for 9 856 828 pairs),
+                # case of the same kernel (profiles/pairs_kernel_diamond110k.md: 536.6 MB for 9 856 828 pairs),
                 # scaled by the pairs of this launch; only for the quantities that capture wrote
-                "traffic": (538.92e6 / 9856828 * int(n_pairs)) if (full and not float_io) else None,
+                "traffic": (536.55e6 / 9856828 * int(n_pairs)) if (full and not float_io) else None,
                 "traffic_unit": "bytes per launch, scaled from the 110k-atom ncu capture",
                 "bytes_per_launch": bytes_per_build,
                 "kernel_ms": emit_ms,
