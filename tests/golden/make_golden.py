@@ -68,7 +68,12 @@ def digest(result):
 
 
 def main():
-    reference_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) > 1:
+        reference_root = sys.argv[1]
+    elif os.environ.get("VESIN_REFERENCE_ROOT"):
+        reference_root = os.environ["VESIN_REFERENCE_ROOT"]
+    else:  # a checkout named "reference" beside this repository
+        reference_root = os.path.join(os.path.dirname(ROOT), "reference")
     data_dir = os.path.join(reference_root, "python", "vesin", "tests", "data")
     O.build()
     assert O.reference_available(), "oracle/_ref/libvesin_ref.so is missing"

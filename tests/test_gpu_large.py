@@ -87,6 +87,38 @@ def test_diamond_512k(full):
     _compare(torch, gpu, cpu, len(points), 5.0)
 
 
+def test_diamond_512k_float32():
+    """The fp32 entry point at the size it is benchmarked on: float points and
+    box in, float d and D out. Pairs and shifts are the CPU reference's on the
+    upcast inputs; d and D are its fp64 values rounded once."""
+    import torch
+
+    import vesin_b200
+
+    device = torch.device("cuda", 0)
+    points, box, periodic = W.diamond(40)
+    points32, box32 = points.astype(np.float32), box.astype(np.float32)
+    calculator = vesin_b200.NeighborList(cutoff=5.0, full_list=True)
+    i, j, S, d, D = calculator.compute(
+        torch.tensor(points32, device=device), torch.tensor(box32, device=device), torch.tensor(periodic, device=device), "ijSdD", copy=False
+    )
+    assert d.dtype == torch.float32 and D.dtype == torch.float32
+    assert vesin_b200.get_library().vesin_b200_list_value_bytes(calculator._neighbors) == 4
+    cpu = _cpu_reference(points32.astype(np.float64), box32.astype(np.float64), periodic, 5.0, True)
+    n_points = len(points)
+    s_range = int(max(int(S.abs().max().item()), int(np.abs(cpu["S"]).max())))
+    assert len(i) == len(cpu["i"])
+    keys = _keys(torch, i.view(torch.int64), j.view(torch.int64), S, n_points, s_range)
+    order = torch.argsort(keys)
+    cpu_keys = _keys(
+        torch, torch.from_numpy(cpu["i"]).to(device), torch.from_numpy(cpu["j"]).to(device), torch.from_numpy(cpu["S"]).to(device), n_points, s_range
+    )
+    cpu_order = torch.argsort(cpu_keys)
+    assert torch.equal(keys[order], cpu_keys[cpu_order]), "(i, j, S) differ"
+    assert torch.equal(d[order], torch.from_numpy(cpu["d"].astype(np.float32)).to(device)[cpu_order])
+    assert torch.equal(D[order], torch.from_numpy(cpu["D"].astype(np.float32)).to(device)[cpu_order])
+
+
 def test_diamond_512k_sorted_half():
     import torch
 

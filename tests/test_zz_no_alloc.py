@@ -2,13 +2,14 @@
 (vesin_b200_neighbors_no_alloc, include/vesin_b200.h).
 
 That entry point exists for callers that may not call cudaMalloc when they
-need a neighbor list (a step running next to a CUDA-graph capture, an
-application that owns all device memory through its own pool, a loop with a
-hard latency bound): the caller brings the output arrays and the kernels work
-in a fixed scratch array inside the library. The test calls it through the C
-ABI and checks the result against vesin_neighbors on the same inputs: indices
-and shifts bit for bit after canonical sorting, distances and vectors within
-the 1e-12 relative tolerance of the other fp64 tests. Two calls are made in a
+need a neighbor list (an application that owns all device memory through its
+own pool, a loop with a hard latency bound, a plugin inside a framework that
+forbids allocations outside its allocator): the caller brings the output
+arrays and the kernels work in a fixed scratch array inside the library. The
+test calls it through the C ABI and checks the result against vesin_neighbors
+on the same inputs and against the CPU oracle: indices and shifts bit for bit
+after canonical sorting, distances and vectors within the 1e-12 relative
+tolerance of the other fp64 tests. Two calls are made in a
 row on different systems, the second smaller than the first, so that data left
 in the shared scratch by the first call would show up as wrong pairs.
 
@@ -89,6 +90,9 @@ def test_two_calls_in_a_row_match_vesin_neighbors():
         assert status == 0, message
         assert length == len(expected["i"])
         O.assert_same(got, expected, RTOL_FP64, "no-alloc build against vesin_neighbors")
+        # both entry points share kernels: the CPU oracle is the independent check
+        oracle = O.restated_neighbors(points, box, periodic, cutoff, full, "ijSdD")
+        O.assert_same(got, oracle, RTOL_FP64, "no-alloc build against the CPU oracle")
 
 
 def test_limits_are_reported():
@@ -115,11 +119,13 @@ def test_output_alignment():
 
     points, box, periodic = W.diamond(6, seed=23)
     expected = _existing_entry_point(torch, points, box, periodic, 5.0, True)
+    oracle = O.restated_neighbors(points, box, periodic, 5.0, True, "ijSdD")
     capacity = len(expected["i"]) + 64
     for offsets in [(16, 4, 8, 8), (0, 4, 0, 0), (16, 0, 0, 8)]:
         status, message, length, got = _no_alloc(torch, None, points, box, periodic, 5.0, True, capacity, offsets)
         assert status == 0, message
         assert length == len(expected["i"])
         O.assert_same(got, expected, RTOL_FP64, f"no-alloc build with output offsets {offsets}")
+        O.assert_same(got, oracle, RTOL_FP64, f"no-alloc build with output offsets {offsets} against the CPU oracle")
     status, message, _, _ = _no_alloc(torch, None, points, box, periodic, 5.0, True, capacity, (8, 0, 0, 0))
     assert status == 1 and "aligned to 16 bytes" in message

@@ -69,7 +69,21 @@ EXPORTED_SYMBOLS = (
     "vesin_b200_neighbors_slab",
     "vesin_b200_pack_halo",
     "vesin_b200_neighbors_f32",
+    "vesin_b200_neighbors_slab_f32",
+    "vesin_b200_slab_geometry",
+    "vesin_b200_sharded_unique_id",
+    "vesin_b200_sharded_create",
+    "vesin_b200_sharded_free",
+    "vesin_b200_sharded_set_halo_capacity",
+    "vesin_b200_sharded_neighbors",
+    "vesin_b200_sharded_neighbors_f32",
+    "vesin_b200_sharded_pack",
+    "vesin_b200_sharded_build",
+    "vesin_b200_sharded_stage_times",
+    "vesin_b200_list_value_bytes",
+    "vesin_b200_list_checksum",
 )
+UNIQUE_ID_BYTES = 128
 NO_ALLOC_MAX_POINTS = 32768
 
 
@@ -160,6 +174,70 @@ def get_library():
     ]
     lib.vesin_b200_neighbors_f32.restype = ctypes.c_int
     lib.vesin_b200_neighbors_f32.argtypes = lib.vesin_neighbors.argtypes
+    lib.vesin_b200_neighbors_slab_f32.restype = ctypes.c_int
+    lib.vesin_b200_neighbors_slab_f32.argtypes = lib.vesin_b200_neighbors_slab.argtypes
+    lib.vesin_b200_slab_geometry.restype = ctypes.c_int
+    lib.vesin_b200_slab_geometry.argtypes = [
+        ctypes.c_void_p,  # box (host, 3x3 double)
+        ctypes.c_void_p,  # periodic (host, 3 bool)
+        ctypes.c_double,  # cutoff
+        ctypes.POINTER(ctypes.c_int),  # axis
+        ctypes.POINTER(ctypes.c_double),  # inverse_column (3)
+        ctypes.POINTER(ctypes.c_double),  # reach
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
+    lib.vesin_b200_sharded_unique_id.restype = ctypes.c_int
+    lib.vesin_b200_sharded_unique_id.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_char_p)]
+    lib.vesin_b200_sharded_create.restype = ctypes.c_int
+    lib.vesin_b200_sharded_create.argtypes = [
+        ctypes.c_void_p,  # id (128 bytes) or NULL
+        ctypes.c_int,  # rank
+        ctypes.c_int,  # world_size
+        ctypes.c_int,  # device_id
+        ctypes.POINTER(ctypes.c_void_p),  # handle (out)
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
+    lib.vesin_b200_sharded_free.restype = None
+    lib.vesin_b200_sharded_free.argtypes = [ctypes.c_void_p]
+    lib.vesin_b200_sharded_set_halo_capacity.restype = ctypes.c_int
+    lib.vesin_b200_sharded_set_halo_capacity.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_char_p)]
+    sharded_build = [
+        ctypes.c_void_p,  # handle
+        ctypes.c_void_p,  # points (device): the points this rank owns
+        ctypes.c_void_p,  # global_index (device, int64)
+        ctypes.c_size_t,  # n_owned
+        ctypes.c_void_p,  # box (HOST)
+        ctypes.c_void_p,  # periodic (HOST)
+        VesinOptions,
+        ctypes.POINTER(VesinNeighborList),
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
+    for function in (lib.vesin_b200_sharded_neighbors, lib.vesin_b200_sharded_neighbors_f32, lib.vesin_b200_sharded_build):
+        function.restype = ctypes.c_int
+        function.argtypes = sharded_build
+    lib.vesin_b200_sharded_pack.restype = ctypes.c_int
+    lib.vesin_b200_sharded_pack.argtypes = [
+        ctypes.c_void_p,  # handle
+        ctypes.c_void_p,  # points (device)
+        ctypes.c_void_p,  # global_index (device)
+        ctypes.c_size_t,  # n_owned
+        ctypes.c_void_p,  # box (HOST)
+        ctypes.c_void_p,  # periodic (HOST)
+        ctypes.c_double,  # cutoff
+        ctypes.POINTER(ctypes.c_void_p),  # messages (out, 4 device addresses)
+        ctypes.POINTER(ctypes.c_size_t),  # rows (out)
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
+    lib.vesin_b200_sharded_stage_times.restype = ctypes.c_int
+    lib.vesin_b200_sharded_stage_times.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
+    lib.vesin_b200_list_value_bytes.restype = ctypes.c_int
+    lib.vesin_b200_list_value_bytes.argtypes = [ctypes.POINTER(VesinNeighborList)]
+    lib.vesin_b200_list_checksum.restype = ctypes.c_int
+    lib.vesin_b200_list_checksum.argtypes = [
+        ctypes.POINTER(VesinNeighborList),
+        ctypes.POINTER(ctypes.c_uint64),  # checksum (4)
+        ctypes.POINTER(ctypes.c_char_p),
+    ]
     lib.vesin_b200_pack_halo.restype = ctypes.c_int
     lib.vesin_b200_pack_halo.argtypes = [
         ctypes.c_void_p,  # points (device)
@@ -172,7 +250,7 @@ def get_library():
         ctypes.c_void_p,  # to_lower (device)
         ctypes.c_void_p,  # to_upper (device)
         ctypes.c_size_t,  # capacity
-        ctypes.c_void_p,  # counts (device, 2 x uint64)
+        ctypes.c_void_p,  # counts (device, 3 x uint64)
         ctypes.POINTER(ctypes.c_char_p),
     ]
     lib.vesin_b200_version.restype = ctypes.c_char_p

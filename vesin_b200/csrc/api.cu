@@ -274,12 +274,13 @@ extern "C" int vesin_b200_neighbors_batch(
     return EXIT_SUCCESS;
 }
 
-extern "C" int vesin_b200_neighbors_slab(
-    const double (*points)[3],
+static int slab_entry(
+    const void* points,
+    bool float_io,
     size_t n_points,
     size_t n_owned,
     const int64_t* global_index,
-    const double box[3][3],
+    const void* box,
     const bool periodic[3],
     VesinB200Slab slab,
     VesinDevice device,
@@ -318,12 +319,73 @@ extern "C" int vesin_b200_neighbors_slab(
     neighbors->device = device;
     try {
         vb200::neighbors_slab(
-            points, n_points, n_owned, global_index, box, periodic, slab.axis, slab.lower, slab.upper, options, *neighbors
+            points, float_io, n_points, n_owned, global_index, box, periodic, slab.axis, slab.lower, slab.upper, options, *neighbors
         );
     } catch (const std::bad_alloc&) {
         LAST_ERROR = "failed to allocate memory";
         *error_message = LAST_ERROR.c_str();
         return EXIT_FAILURE;
+    } catch (const std::exception& e) {
+        LAST_ERROR = e.what();
+        *error_message = LAST_ERROR.c_str();
+        return EXIT_FAILURE;
+    }
+    return EXIT_SUCCESS;
+}
+
+extern "C" int vesin_b200_neighbors_slab(
+    const double (*points)[3],
+    size_t n_points,
+    size_t n_owned,
+    const int64_t* global_index,
+    const double box[3][3],
+    const bool periodic[3],
+    VesinB200Slab slab,
+    VesinDevice device,
+    VesinOptions options,
+    VesinNeighborList* neighbors,
+    const char** error_message
+) {
+    return slab_entry(points, false, n_points, n_owned, global_index, box, periodic, slab, device, options, neighbors, error_message);
+}
+
+extern "C" int vesin_b200_neighbors_slab_f32(
+    const float (*points)[3],
+    size_t n_points,
+    size_t n_owned,
+    const int64_t* global_index,
+    const float box[3][3],
+    const bool periodic[3],
+    VesinB200Slab slab,
+    VesinDevice device,
+    VesinOptions options,
+    VesinNeighborList* neighbors,
+    const char** error_message
+) {
+    return slab_entry(points, true, n_points, n_owned, global_index, box, periodic, slab, device, options, neighbors, error_message);
+}
+
+extern "C" int vesin_b200_list_value_bytes(const VesinNeighborList* neighbors) {
+    if (neighbors == nullptr) {
+        return 0;
+    }
+    return vb200::list_value_bytes(*neighbors);
+}
+
+extern "C" int vesin_b200_list_checksum(const VesinNeighborList* neighbors, uint64_t checksum[4], const char** error_message) {
+    if (error_message == nullptr) {
+        return EXIT_FAILURE;
+    }
+    if (neighbors == nullptr || checksum == nullptr) {
+        *error_message = "`neighbors` and `checksum` can not be NULL pointers";
+        return EXIT_FAILURE;
+    }
+    try {
+        unsigned long long result[4];
+        vb200::list_checksum(*neighbors, result);
+        for (int k = 0; k < 4; k++) {
+            checksum[k] = result[k];
+        }
     } catch (const std::exception& e) {
         LAST_ERROR = e.what();
         *error_message = LAST_ERROR.c_str();

@@ -99,6 +99,18 @@ struct Workspace {
     DeviceBuffer masks, unit_mask_base, unit_words, unit_count, unit_start;
     DeviceBuffer row_count, row_start, row_fill, scan_tmp;
     DeviceBuffer batch_offsets; // batches: where each system starts in the points array
+    DeviceBuffer sorted_global; // slabs: index of every cell-sorted record in the whole system
+    DeviceBuffer checksum;      // 4 words of vesin_b200_list_checksum
+    bool values_float = false;  // element type of `distances` / `vectors` of the last build
+
+    // Slab builds: extent of the local points along non-periodic directions as the last build
+    // that looked found it (the binning kernel checks every point against it), and the number
+    // of local points of the last build (sizes the pencils of the next one).
+    struct SlabCache {
+        bool bounds_valid = false;
+        PointBounds bounds{};
+        size_t n_local = 0;
+    } slab;
 
     // output arrays (capacity in pairs); kept allocated when not requested
     DeviceBuffer out_pairs, out_shifts, out_distances, out_vectors;
@@ -124,7 +136,8 @@ struct Workspace {
     ~Workspace() {
         for (DeviceBuffer* buffer :
              {&cell_of, &rank, &shift, &cell_count, &cell_start, &sorted_pos, &sorted_index, &sorted_shift, &masks, &unit_mask_base,
-              &unit_words, &unit_count, &unit_start, &row_count, &row_start, &row_fill, &scan_tmp, &batch_offsets, &out_pairs, &out_shifts, &out_distances, &out_vectors}) {
+              &unit_words, &unit_count, &unit_start, &row_count, &row_start, &row_fill, &scan_tmp, &batch_offsets, &sorted_global, &checksum, &out_pairs,
+              &out_shifts, &out_distances, &out_vectors}) {
             buffer->release();
         }
         if (d_header != nullptr) {
@@ -318,6 +331,10 @@ void set_profiling(bool enabled) {
     PROFILING.store(enabled);
 }
 
+bool profiling_enabled() {
+    return PROFILING.load();
+}
+
 bool stage_times(const VesinNeighborList& list, double* stage_ms) {
     if (list.opaque == nullptr || list.device.type != VesinCUDA) {
         return false;
@@ -358,6 +375,8 @@ void neighbors(
     cudaStream_t stream = ws.stream;
     const RealView flat_points{points, float_io ? 1 : 0};
     const RealView flat_box{box, float_io ? 1 : 0};
+    const PointSource source = flat_source(flat_points, n_points);
+    ws.values_float = float_io;
 
     const DeviceHeader& header = *ws.h_header;
     const size_t max_cells = size_t(1) << 27;
@@ -442,7 +461,7 @@ void neighbors(
             histogram_zeroed = true;
         } else {
             launch_header_init(ws.d_header, flat_box, periodic, stream);
-            launch_bounds(flat_points, n_points, ws.d_header, stream);
+            launch_bounds(source, ws.d_header, stream);
         }
         timer.end(VesinB200StageBounds);
         if (!speculative) {
@@ -505,8 +524,8 @@ void neighbors(
                 VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
             }
             launch_bin(
-                flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
-                ws.cell_count.as<int32_t>(), ws.d_header, speculative, stream
+                source, 0, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
+                ws.cell_count.as<int32_t>(), ws.d_header, speculative, true, stream
             );
             timer.end(VesinB200StageBin);
             timer.begin(VesinB200StageScanCells);
@@ -514,8 +533,8 @@ void neighbors(
             timer.end(VesinB200StageScanCells);
             timer.begin(VesinB200StageScatter);
             launch_scatter(
-                flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(),
-                sorted, ws.d_header, stream
+                source, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells,
+                sorted, nullptr, ws.d_header, stream
             );
             timer.end(VesinB200StageScatter);
         }
@@ -561,7 +580,7 @@ void neighbors(
                 };
                 const size_t pass_capacity = count_only ? 0 : capacity;
                 timer.begin(VesinB200StageEmit);
-                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, pass_capacity, ws.d_header, nullptr, stream);
+                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, pass_capacity, ws.d_header, stream);
                 timer.end(VesinB200StageEmit);
                 VB200_CUDA(cudaGetLastError());
                 read_header(ws);
@@ -743,6 +762,7 @@ void neighbors_batch(
     DeviceGuard guard(list.device.device_id);
     Workspace& ws = workspace_of(list);
     ws.cache.valid = false; // the list was used for something else than a single system
+    ws.values_float = false;
     const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
     cudaStream_t stream = ws.stream;
     const DeviceHeader& header = *ws.h_header;
@@ -818,12 +838,221 @@ void neighbors_batch(
     }
 }
 
+cudaStream_t list_stream(VesinNeighborList& list) {
+    DeviceGuard guard(list.device.device_id);
+    return workspace_of(list).stream;
+}
+
+void neighbors_slab_core(
+    const void* points,
+    bool float_io,
+    size_t n_array,
+    size_t n_owned,
+    const int64_t* global_index,
+    const HaloMessages* halo,
+    const double box[9],
+    const bool periodic[3],
+    int axis,
+    double lower,
+    double upper,
+    VesinOptions options,
+    VesinNeighborList& list
+) {
+    if (n_owned > n_array) {
+        throw std::runtime_error("`n_owned` can not be larger than `n_points`");
+    }
+    if (options.sorted) {
+        throw std::runtime_error("sorted lists are not available for slab-decomposed systems");
+    }
+    const bool with_messages = halo != nullptr && halo->capacity > 0;
+    PointSource source = flat_source(RealView{points, float_io ? 1 : 0}, n_array);
+    source.global_index = reinterpret_cast<const long long*>(global_index);
+    if (with_messages) {
+        source.message[0] = halo->from_upper;
+        source.message[1] = halo->from_lower;
+        source.capacity = halo->capacity;
+    }
+    const size_t n_index = source.n_index();
+    if (n_index >= (1ull << 31) - 1) {
+        throw std::runtime_error("this engine indexes points with 31 bits: too many points");
+    }
+
+    DeviceGuard guard(list.device.device_id);
+    Workspace& ws = workspace_of(list);
+    ws.cache.valid = false; // this list is not used for plain single-system builds
+    ws.values_float = float_io;
+    const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
+    StageTimer timer(ws, PROFILING.load());
+    cudaStream_t stream = ws.stream;
+    const DeviceHeader& header = *ws.h_header;
+    const size_t max_cells = size_t(1) << 27;
+
+    // the halo messages arrive on another stream: this stream waits for them once,
+    // as late as the work allows
+    bool messages_awaited = !(with_messages && halo->received != nullptr);
+    const auto await_messages = [&]() {
+        if (!messages_awaited) {
+            VB200_CUDA(cudaStreamWaitEvent(stream, halo->received, 0));
+            messages_awaited = true;
+        }
+    };
+
+    const bool any_open = !(periodic[0] && periodic[1] && periodic[2]);
+    size_t n_estimate = ws.slab.n_local != 0 ? ws.slab.n_local : n_array + (with_messages ? halo->expected_records : 0);
+
+    for (int round = 0;; round++) {
+        // ---- extent of the points along non-periodic directions: taken from the last
+        // build that computed it (the binning kernel checks every point against it) ----
+        const bool bounds_cached = ws.slab.bounds_valid;
+        if (any_open && !bounds_cached) {
+            await_messages();
+            timer.begin(VesinB200StageBounds);
+            launch_header_reset(ws.d_header, nullptr, 0, stream);
+            launch_bounds(source, ws.d_header, stream);
+            timer.end(VesinB200StageBounds);
+            VB200_CUDA(cudaGetLastError());
+            read_header(ws);
+            timer.collect(VesinB200StageBounds);
+            if (header.first_bad != NO_BAD_POINT) {
+                throw std::runtime_error("local point " + std::to_string(header.first_bad) + " has a non-finite coordinate");
+            }
+            for (int c = 0; c < 3; c++) {
+                const bool have = header.min_key[c] != ~0ull;
+                ws.slab.bounds.min[c] = have ? key_to_double(header.min_key[c]) : 0.0;
+                ws.slab.bounds.max[c] = have ? key_to_double(header.max_key[c]) : 0.0;
+            }
+            ws.slab.bounds_valid = true;
+        }
+        const PointBounds bounds = any_open ? ws.slab.bounds : PointBounds{};
+        GridPlan plan = make_plan(box, periodic, bounds, std::max<size_t>(n_estimate, 1), options.cutoff, options.full, false, max_cells);
+        make_slab_window(plan, axis, lower, upper, std::max<size_t>(n_estimate, 1), n_owned, options.cutoff);
+
+        const size_t n_cells = static_cast<size_t>(plan.n_cells_total);
+        const size_t n_slots = std::max<size_t>(n_index, 1);
+        ws.cell_of.reserve(n_slots * sizeof(int32_t));
+        ws.rank.reserve(n_slots * sizeof(int32_t));
+        ws.shift.reserve(n_slots * 3 * sizeof(int32_t));
+        ws.cell_count.reserve(n_cells * sizeof(int32_t));
+        ws.cell_start.reserve((n_cells + 1) * sizeof(int32_t));
+        ws.sorted_pos.reserve(n_slots * 3 * sizeof(double));
+        ws.sorted_index.reserve(n_slots * sizeof(int32_t));
+        ws.sorted_shift.reserve(n_slots * 3 * sizeof(int32_t));
+        ws.sorted_global.reserve(n_slots * sizeof(int32_t));
+        ws.scan_tmp.reserve(scan_tmp_bytes(std::max(n_slots, n_cells)));
+        SortedPoints sorted{ws.sorted_pos.as<double>(), ws.sorted_index.as<int32_t>(), ws.sorted_shift.as<int32_t>()};
+        // the pair pass writes global indices: it reads them where a plain build keeps local ones
+        SortedPoints sorted_for_pairs{sorted.pos, ws.sorted_global.as<int32_t>(), sorted.shift};
+
+        timer.begin(VesinB200StageBin);
+        launch_header_reset(ws.d_header, ws.cell_count.as<int32_t>(), n_cells, stream);
+        // points of the caller's array first: their binning runs while the messages are on their way
+        launch_bin(
+            source, 0, n_array, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_count.as<int32_t>(),
+            ws.d_header, true, true, stream
+        );
+        if (with_messages) {
+            await_messages();
+            launch_bin(
+                source, n_array, n_index, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
+                ws.cell_count.as<int32_t>(), ws.d_header, true, false, stream
+            );
+        }
+        timer.end(VesinB200StageBin);
+        timer.begin(VesinB200StageScanCells);
+        launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
+        timer.end(VesinB200StageScanCells);
+        timer.begin(VesinB200StageScatter);
+        launch_scatter(
+            source, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, sorted,
+            ws.sorted_global.as<int32_t>(), ws.d_header, stream
+        );
+        timer.end(VesinB200StageScatter);
+
+        set_outputs(list, ws, options, std::max<size_t>(common_capacity(ws, options), 256));
+        size_t capacity = common_capacity(ws, options);
+        size_t total = 0;
+        bool refused = false;
+        bool count_only = capacity <= 256 && n_owned >= 4096;
+        for (int attempt = 0;; attempt++) {
+            PairOutput out{
+                reinterpret_cast<unsigned long long*>(list.pairs),
+                reinterpret_cast<int32_t*>(list.shifts),
+                list.distances,
+                reinterpret_cast<double*>(list.vectors),
+                float_io ? 1 : 0,
+            };
+            const size_t pass_capacity = count_only ? 0 : capacity;
+            timer.begin(VesinB200StageEmit);
+            launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted_for_pairs, out, pass_capacity, ws.d_header, stream);
+            timer.end(VesinB200StageEmit);
+            VB200_CUDA(cudaGetLastError());
+            read_header(ws);
+            if (attempt == 0) {
+                timer.collect(VesinB200StageBin);
+                timer.collect(VesinB200StageScanCells);
+                timer.collect(VesinB200StageScatter);
+                if (header.status & STATUS_BAD_POINT) {
+                    throw std::runtime_error("local point " + std::to_string(header.first_bad) + " has a non-finite coordinate");
+                }
+                if (header.status & STATUS_HALO_OVERFLOW) {
+                    throw std::runtime_error(
+                        "a halo message brought " + std::to_string(std::max(header.halo_count[0], header.halo_count[1])) +
+                        " records but holds " + std::to_string(source.capacity) + ": raise the halo capacity (the same value on every rank)"
+                    );
+                }
+                if (header.status & STATUS_INDEX_RANGE) {
+                    throw std::runtime_error("a global index is negative or does not fit 31 bits");
+                }
+                if (header.status & STATUS_PLAN_STALE) {
+                    if (!bounds_cached || round >= 2) {
+                        throw std::runtime_error("internal error: a plan made from the bounds of these very points was refused");
+                    }
+                    ws.slab.bounds_valid = false; // the points left the extent of an earlier build: look again
+                    refused = true;
+                    break;
+                }
+            }
+            timer.collect(VesinB200StageEmit);
+            total = static_cast<size_t>(header.pair_cursor);
+            if (total > std::max<size_t>(n_owned, 1) * 2 * pair_limit_per_point) {
+                throw std::runtime_error(
+                    "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_owned * pair_limit_per_point) +
+                    " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_owned) + "). " +
+                    "Consider reducing the cutoff distance, or explicitly setting " +
+                    "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable."
+                );
+            }
+            if (total <= pass_capacity) {
+                break;
+            }
+            if (attempt >= 2) {
+                throw std::runtime_error("internal error: the pair total kept changing between passes");
+            }
+            count_only = false;
+            if (total > capacity) {
+                set_outputs(list, ws, options, total + total / 16 + 256);
+                capacity = common_capacity(ws, options);
+            }
+            VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, 2 * sizeof(unsigned long long), stream)); // and run_cursor
+        }
+        if (refused) {
+            continue;
+        }
+        ws.slab.n_local = n_array + static_cast<size_t>(std::min<unsigned long long>(header.halo_count[0], source.capacity)) +
+                          static_cast<size_t>(std::min<unsigned long long>(header.halo_count[1], source.capacity));
+        list.length = total;
+        ws.timed = timer.enabled;
+        return;
+    }
+}
+
 void neighbors_slab(
-    const double (*points)[3],
+    const void* points,
+    bool float_io,
     size_t n_points,
     size_t n_owned,
     const int64_t* global_index,
-    const double box[3][3],
+    const void* box,
     const bool periodic[3],
     int axis,
     double lower,
@@ -832,132 +1061,55 @@ void neighbors_slab(
     VesinNeighborList& list
 ) {
     validate_pointers(points, box, periodic, list);
-    if (n_owned > n_points) {
-        throw std::runtime_error("`n_owned` can not be larger than `n_points`");
-    }
-    if (n_points >= (1ull << 31) - 1) {
-        throw std::runtime_error("this engine indexes points with 31 bits: too many points");
-    }
-    if (options.sorted) {
-        throw std::runtime_error("sorted lists are not available for slab-decomposed systems");
-    }
     {
         PointerInfo info = inspect(global_index);
         if (n_points > 0 && !(info.resolved && info.on_device && info.device == list.device.device_id)) {
             throw std::runtime_error("`global_index` pointer is not allocated on the CUDA device of `neighbors`");
         }
     }
+    // box and periodicity live in device memory (the convention of vesin_neighbors): bring them over
+    double host_box[9];
+    bool host_periodic[3];
+    {
+        DeviceGuard guard(list.device.device_id);
+        if (float_io) {
+            float box32[9];
+            VB200_CUDA(cudaMemcpy(box32, box, sizeof(box32), cudaMemcpyDeviceToHost));
+            for (int k = 0; k < 9; k++) {
+                host_box[k] = box32[k];
+            }
+        } else {
+            VB200_CUDA(cudaMemcpy(host_box, box, sizeof(host_box), cudaMemcpyDeviceToHost));
+        }
+        VB200_CUDA(cudaMemcpy(host_periodic, periodic, sizeof(host_periodic), cudaMemcpyDeviceToHost));
+    }
+    neighbors_slab_core(
+        points, float_io, n_points, n_owned, global_index, nullptr, host_box, host_periodic, axis, lower, upper, options, list
+    );
+}
 
+int list_value_bytes(const VesinNeighborList& list) {
+    if (list.opaque == nullptr || list.device.type != VesinCUDA) {
+        return 0;
+    }
+    return static_cast<const Workspace*>(list.opaque)->values_float ? 4 : 8;
+}
+
+void list_checksum(const VesinNeighborList& list, unsigned long long result[4]) {
+    if (list.opaque == nullptr || list.device.type != VesinCUDA) {
+        throw std::runtime_error("the list holds nothing: build it first");
+    }
     DeviceGuard guard(list.device.device_id);
-    Workspace& ws = workspace_of(list);
-    ws.cache.valid = false; // this list is not used for plain single-system builds
-    const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
-    StageTimer timer(ws, PROFILING.load());
-    cudaStream_t stream = ws.stream;
-    const RealView flat_points{points, 0};
-    const DeviceHeader& header = *ws.h_header;
-
-    timer.begin(VesinB200StageBounds);
-    launch_header_init(ws.d_header, RealView{box, 0}, periodic, stream);
-    launch_bounds(flat_points, n_points, ws.d_header, stream);
-    timer.end(VesinB200StageBounds);
+    Workspace& ws = *static_cast<Workspace*>(list.opaque);
+    ws.checksum.reserve(4 * sizeof(unsigned long long));
+    launch_checksum(
+        reinterpret_cast<const unsigned long long*>(list.pairs), reinterpret_cast<const int32_t*>(list.shifts), list.distances,
+        ws.values_float ? 1 : 0, list.length, ws.checksum.as<unsigned long long>(), ws.stream
+    );
     VB200_CUDA(cudaGetLastError());
-    read_header(ws);
-    timer.collect(VesinB200StageBounds);
-
-    bool host_periodic[3] = {header.periodic[0] != 0, header.periodic[1] != 0, header.periodic[2] != 0};
-    PointBounds bounds{};
-    for (int c = 0; c < 3; c++) {
-        bool have = n_points != 0 && header.min_key[c] != ~0ull;
-        bounds.min[c] = have ? key_to_double(header.min_key[c]) : 0.0;
-        bounds.max[c] = have ? key_to_double(header.max_key[c]) : 0.0;
-    }
-    GridPlan plan = make_plan(header.box, host_periodic, bounds, n_points, options.cutoff, options.full, false, size_t(1) << 27);
-    if (header.first_bad != NO_BAD_POINT) {
-        throw std::runtime_error("local point " + std::to_string(header.first_bad) + " has a non-finite coordinate");
-    }
-    make_slab_window(plan, axis, lower, upper, n_points, n_owned, options.cutoff);
-
-    if (n_points == 0) {
-        set_outputs(list, ws, options, 256);
-        list.length = 0;
-        ws.timed = timer.enabled;
-        return;
-    }
-
-    const size_t n_cells = static_cast<size_t>(plan.n_cells_total);
-    ws.cell_of.reserve(n_points * sizeof(int32_t));
-    ws.rank.reserve(n_points * sizeof(int32_t));
-    ws.shift.reserve(n_points * 3 * sizeof(int32_t));
-    ws.cell_count.reserve(n_cells * sizeof(int32_t));
-    ws.cell_start.reserve((n_cells + 1) * sizeof(int32_t));
-    ws.sorted_pos.reserve(n_points * 3 * sizeof(double));
-    ws.sorted_index.reserve(n_points * sizeof(int32_t));
-    ws.sorted_shift.reserve(n_points * 3 * sizeof(int32_t));
-    ws.scan_tmp.reserve(scan_tmp_bytes(std::max(n_points, n_cells)));
-    SortedPoints sorted{ws.sorted_pos.as<double>(), ws.sorted_index.as<int32_t>(), ws.sorted_shift.as<int32_t>()};
-
-    timer.begin(VesinB200StageBin);
-    VB200_CUDA(cudaMemsetAsync(ws.cell_count.ptr, 0, n_cells * sizeof(int32_t), stream));
-    launch_bin(
-        flat_points, n_points, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_count.as<int32_t>(),
-        ws.d_header, false, stream
-    );
-    timer.end(VesinB200StageBin);
-    timer.begin(VesinB200StageScanCells);
-    launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
-    timer.end(VesinB200StageScanCells);
-    timer.begin(VesinB200StageScatter);
-    launch_scatter(
-        flat_points, n_points, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), sorted,
-        ws.d_header, stream
-    );
-    timer.end(VesinB200StageScatter);
-
-    set_outputs(list, ws, options, std::max<size_t>(common_capacity(ws, options), 256));
-    size_t capacity = common_capacity(ws, options);
-    size_t total = 0;
-    for (int attempt = 0;; attempt++) {
-        PairOutput out{
-            reinterpret_cast<unsigned long long*>(list.pairs),
-            reinterpret_cast<int32_t*>(list.shifts),
-            list.distances,
-            reinterpret_cast<double*>(list.vectors),
-        };
-        timer.begin(VesinB200StageEmit);
-        launch_pairs(
-            plan, ws.cell_start.as<int32_t>(), sorted, out, capacity, ws.d_header, reinterpret_cast<const long long*>(global_index), stream
-        );
-        timer.end(VesinB200StageEmit);
-        VB200_CUDA(cudaGetLastError());
-        read_header(ws);
-        if (attempt == 0) {
-            timer.collect(VesinB200StageBin);
-            timer.collect(VesinB200StageScanCells);
-            timer.collect(VesinB200StageScatter);
-        }
-        timer.collect(VesinB200StageEmit);
-        total = static_cast<size_t>(header.pair_cursor);
-        if (total > std::max<size_t>(n_owned, 1) * 2 * pair_limit_per_point) {
-            throw std::runtime_error(
-                "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_owned * pair_limit_per_point) +
-                " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_owned) + "). " +
-                "Consider reducing the cutoff distance, or explicitly setting " +
-                "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable."
-            );
-        }
-        if (total <= capacity) {
-            break;
-        }
-        if (attempt >= 2) {
-            throw std::runtime_error("internal error: the pair total kept changing between passes");
-        }
-        set_outputs(list, ws, options, total + total / 16 + 256);
-        capacity = common_capacity(ws, options);
-        VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, 2 * sizeof(unsigned long long), stream)); // and run_cursor
-    }
-    list.length = total;
-    ws.timed = timer.enabled;
+    VB200_CUDA(cudaMemcpyAsync(result, ws.checksum.ptr, 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, ws.stream));
+    VB200_CUDA(cudaStreamSynchronize(ws.stream));
+    result[3] = list.length;
 }
 
 void free_neighbors(VesinNeighborList& list) {

@@ -5,6 +5,8 @@
 #include <cstddef>
 #include <cstdint>
 
+#include <cuda_runtime.h>
+
 #include "vesin.h"
 
 namespace vb200 {
@@ -39,14 +41,28 @@ void neighbors_batch(
     const size_t** pair_offsets
 );
 
+/// Halo of a slab that arrives as two messages (see PointSource in
+/// kernels.cuh for their layout) instead of sitting behind the owned points.
+struct HaloMessages {
+    const double* from_upper;
+    const double* from_lower;
+    size_t capacity;         // records a message can hold
+    cudaEvent_t received;    // recorded after the receives on their stream, or null
+    size_t expected_records; // guess of the records both messages bring (sizes the work units of a first build)
+};
+
 /// One rank's share of a slab-decomposed periodic system (no counterpart in
-/// the reference). Throws like neighbors().
-void neighbors_slab(
-    const double (*points)[3],
-    size_t n_points,
+/// the reference). `points` holds n_array points, the first n_owned of them
+/// owned, the rest halo; more halo may come in `halo`. `box` and `periodic`
+/// are HOST values. Throws like neighbors().
+void neighbors_slab_core(
+    const void* points,
+    bool float_io,
+    size_t n_array,
     size_t n_owned,
     const int64_t* global_index,
-    const double box[3][3],
+    const HaloMessages* halo,
+    const double box[9],
     const bool periodic[3],
     int axis,
     double lower,
@@ -55,11 +71,39 @@ void neighbors_slab(
     VesinNeighborList& list
 );
 
+/// The same with box and periodicity in device memory and the whole halo in
+/// `points` (float or double data, like neighbors()).
+void neighbors_slab(
+    const void* points,
+    bool float_io,
+    size_t n_points,
+    size_t n_owned,
+    const int64_t* global_index,
+    const void* box,
+    const bool periodic[3],
+    int axis,
+    double lower,
+    double upper,
+    VesinOptions options,
+    VesinNeighborList& list
+);
+
+/// The stream the builds of this list run on (creates the list's workspace).
+cudaStream_t list_stream(VesinNeighborList& list);
+
+/// Bytes per element of `distances` / `vectors` of the list's last build (4 or
+/// 8), 0 for a list that holds nothing.
+int list_value_bytes(const VesinNeighborList& list);
+
+/// Order-independent checksum of the list, see vesin_b200_list_checksum.
+void list_checksum(const VesinNeighborList& list, unsigned long long result[4]);
+
 /// Release everything a list holds on its device. Replaces
 /// vesin::cuda::free_neighbors (vesin/src/vesin_cuda.cpp:129-138).
 void free_neighbors(VesinNeighborList& list);
 
 void set_profiling(bool enabled);
+bool profiling_enabled();
 bool stage_times(const VesinNeighborList& list, double* stage_ms);
 
 } // namespace vb200

@@ -44,6 +44,60 @@ __device__ __forceinline__ double load_real(const RealView& view, size_t k) {
     return view.is_float ? static_cast<double>(static_cast<const float*>(view.data)[k]) : static_cast<const double*>(view.data)[k];
 }
 
+/// Records a halo message holds: its row 0, bounded by the capacity.
+__device__ __forceinline__ unsigned long long message_records(const PointSource& source, int k) {
+    const double claimed = (k ? source.message[1] : source.message[0])[0];
+    const unsigned long long count = (claimed > 0.0) ? static_cast<unsigned long long>(claimed) : 0ull;
+    return (count < source.capacity) ? count : source.capacity;
+}
+
+/// Point with local index i; false for an empty slot of a halo message.
+/// Without HALO the source is a plain array.
+template <bool HALO>
+__device__ __forceinline__ bool load_point(const PointSource& source, size_t i, double& x, double& y, double& z) {
+    if (!HALO || i < source.n0) {
+        x = load_real(source.points, 3 * i + 0);
+        y = load_real(source.points, 3 * i + 1);
+        z = load_real(source.points, 3 * i + 2);
+        return true;
+    }
+    size_t r = i - source.n0;
+    const int k = (r >= source.capacity) ? 1 : 0;
+    r -= k * source.capacity;
+    if (r >= message_records(source, k)) {
+        return false;
+    }
+    const double* row = (k ? source.message[1] : source.message[0]) + 4 * (r + 1);
+    x = row[0];
+    y = row[1];
+    z = row[2];
+    return true;
+}
+
+/// One coordinate of the point with local index i (which is not an empty slot).
+template <bool HALO>
+__device__ __forceinline__ double load_coordinate(const PointSource& source, size_t i, size_t c) {
+    if (!HALO || i < source.n0) {
+        return load_real(source.points, 3 * i + c);
+    }
+    size_t r = i - source.n0;
+    const int k = (r >= source.capacity) ? 1 : 0;
+    r -= k * source.capacity;
+    return (k ? source.message[1] : source.message[0])[4 * (r + 1) + c];
+}
+
+/// Index of the point in the whole system.
+template <bool HALO>
+__device__ __forceinline__ long long global_index_of(const PointSource& source, size_t i) {
+    if (!HALO || i < source.n0) {
+        return (source.global_index != nullptr) ? source.global_index[i] : static_cast<long long>(i);
+    }
+    size_t r = i - source.n0;
+    const int k = (r >= source.capacity) ? 1 : 0;
+    r -= k * source.capacity;
+    return __double_as_longlong((k ? source.message[1] : source.message[0])[4 * (r + 1) + 3]);
+}
+
 // Programmatic dependent launch: the kernels of a build form a chain on one
 // stream, each reading what the one before wrote. A kernel lets the next one
 // be scheduled as soon as all of its own blocks are running, and waits for the
@@ -192,10 +246,15 @@ __device__ __forceinline__ void reset_header(DeviceHeader* header, const RealVie
     if (t < 3) {
         header->min_key[t] = ~0ull;
         header->max_key[t] = 0ull;
-        header->periodic[t] = periodic[t] ? 1 : 0;
+        if (periodic != nullptr) {
+            header->periodic[t] = periodic[t] ? 1 : 0;
+        }
     }
-    if (t < 9) {
+    if (t < 9 && box.data != nullptr) {
         header->box[t] = load_real(box, t);
+    }
+    if (t < 2) {
+        header->halo_count[t] = 0;
     }
     if (t == 0) {
         header->first_bad = NO_BAD_POINT;
@@ -243,16 +302,21 @@ __global__ void __launch_bounds__(CTA_THREADS) header_init_kernel(
     }
 }
 
-__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const RealView points, size_t n, DeviceHeader* header) {
+template <bool HALO>
+__global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const PointSource source, size_t n, DeviceHeader* header) {
     double lo[3] = {DBL_MAX, DBL_MAX, DBL_MAX};
     double hi[3] = {-DBL_MAX, -DBL_MAX, -DBL_MAX};
     unsigned long long bad = NO_BAD_POINT;
 
     size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        double r[3];
+        if (!load_point<HALO>(source, i, r[0], r[1], r[2])) {
+            continue;
+        }
 #pragma unroll
         for (int c = 0; c < 3; c++) {
-            double x = load_real(points, 3 * i + c);
+            double x = r[c];
             if (isfinite(x)) {
                 lo[c] = fmin(lo[c], x);
                 hi[c] = fmax(hi[c], x);
@@ -318,11 +382,8 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const RealView poin
 /// speculative; a point with a non-finite coordinate or outside the cells of a
 /// non-periodic direction refuses it.
 __device__ __forceinline__ int locate_point(
-    const RealView& points, size_t i, const GridPlan& plan, DeviceHeader* header, const int check, int wrap[3]
+    double rx, double ry, double rz, size_t i, const GridPlan& plan, DeviceHeader* header, const int check, int wrap[3]
 ) {
-    double rx = load_real(points, 3 * i + 0);
-    double ry = load_real(points, 3 * i + 1);
-    double rz = load_real(points, 3 * i + 2);
     if (check && !(isfinite(rx) && isfinite(ry) && isfinite(rz))) {
         atomicMin(&header->first_bad, static_cast<unsigned long long>(i));
         atomicOr(&header->status, STATUS_BAD_POINT);
@@ -365,8 +426,9 @@ __device__ __forceinline__ int locate_point(
     return (cell[2] * plan.n_cells[1] + cell[1]) * plan.n_cells[0] + cell[0];
 }
 
+template <bool HALO>
 __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
-    const RealView points, size_t n, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
+    const PointSource source, size_t first, size_t last, const GridPlan plan, int32_t* __restrict__ cell_of, int32_t* __restrict__ rank,
     int32_t* __restrict__ shift, int32_t* __restrict__ cell_count, DeviceHeader* header, const int check
 ) {
     let_next_kernel_start();
@@ -374,14 +436,25 @@ __global__ void __launch_bounds__(CTA_THREADS) bin_kernel(
     if (header->status & STATUS_ABORT_MASK) {
         return;
     }
-    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    bool active = i < n;
+    size_t i = first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    double rx = 0.0, ry = 0.0, rz = 0.0;
+    bool active = i < last && load_point<HALO>(source, i, rx, ry, rz);
+    if (HALO && i < last && i >= source.n0 && (i - source.n0) % source.capacity == 0) {
+        // first slot of a message: report how many records it brought
+        const int k = (i - source.n0 >= source.capacity) ? 1 : 0;
+        const double claimed = (k ? source.message[1] : source.message[0])[0];
+        const unsigned long long count = (claimed > 0.0) ? static_cast<unsigned long long>(claimed) : 0ull;
+        header->halo_count[k] = count;
+        if (count > source.capacity) {
+            atomicOr(&header->status, STATUS_HALO_OVERFLOW);
+        }
+    }
     unsigned active_mask = __ballot_sync(FULL_MASK, active);
     if (!active) {
         return;
     }
     int wrap[3];
-    const int linear = locate_point(points, i, plan, header, check, wrap);
+    const int linear = locate_point(rx, ry, rz, i, plan, header, check, wrap);
 
     // warp-aggregated histogram: one atomic per distinct cell in the warp
     unsigned peers = __match_any_sync(active_mask, linear);
@@ -575,15 +648,23 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
 // ---------------------------------------------------------------------------
 
 /// Step 1: where does point i go? Only its index is scattered (4 bytes per point).
+template <bool HALO>
 __global__ void __launch_bounds__(CTA_THREADS) scatter_index_kernel(
-    size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank, const int32_t* __restrict__ cell_start,
-    int32_t* __restrict__ sorted_index, const DeviceHeader* __restrict__ header
+    const PointSource source, size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank,
+    const int32_t* __restrict__ cell_start, int32_t* __restrict__ sorted_index, const DeviceHeader* __restrict__ header
 ) {
     let_next_kernel_start();
     wait_for_previous_kernel();
     size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n || (header->status & STATUS_ABORT_MASK)) {
         return;
+    }
+    if (HALO && i >= source.n0) {
+        const size_t r = i - source.n0;
+        const int k = (r >= source.capacity) ? 1 : 0;
+        if (r - k * source.capacity >= message_records(source, k)) {
+            return; // empty slot of a halo message
+        }
     }
     size_t p = static_cast<size_t>(cell_start[cell_of[i]]) + rank[i];
     sorted_index[p] = static_cast<int32_t>(i);
@@ -593,8 +674,12 @@ __global__ void __launch_bounds__(CTA_THREADS) scatter_index_kernel(
 /// store instruction writes one contiguous span whatever the order of the
 /// input (a scatter of whole records writes partial sectors all over the
 /// arrays when neighbouring points are far apart in the input).
+/// `n_records` (device): number of records, i.e. cell_start[n_cells]; the
+/// grid covers the whole local index space, which may hold empty slots.
+template <bool HALO>
 __global__ void __launch_bounds__(CTA_THREADS) gather_records_kernel(
-    const RealView points, size_t n, const int32_t* __restrict__ shift, SortedPoints sorted, const DeviceHeader* __restrict__ header
+    const PointSource source, size_t n, const int32_t* __restrict__ n_records, const int32_t* __restrict__ shift, SortedPoints sorted,
+    int32_t* __restrict__ sorted_global, DeviceHeader* __restrict__ header
 ) {
     let_next_kernel_start();
     wait_for_previous_kernel();
@@ -604,9 +689,19 @@ __global__ void __launch_bounds__(CTA_THREADS) gather_records_kernel(
     }
     size_t p = f / 3;
     size_t c = f - 3 * p;
+    if (HALO && p >= static_cast<size_t>(*n_records)) {
+        return;
+    }
     size_t i = static_cast<size_t>(sorted.index[p]);
-    sorted.pos[f] = load_real(points, 3 * i + c);
+    sorted.pos[f] = load_coordinate<HALO>(source, i, c);
     sorted.shift[f] = shift[3 * i + c];
+    if (c == 0 && sorted_global != nullptr) {
+        const long long global = global_index_of<HALO>(source, i);
+        if (global < 0 || global > 0x7fffffffll) {
+            atomicOr(&header->status, STATUS_INDEX_RANGE);
+        }
+        sorted_global[p] = static_cast<int32_t>(global);
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -657,7 +752,9 @@ __global__ void __launch_bounds__(SMALL_FRONT_THREADS) small_front_kernel(
     // ---- histogram: the value the atomic returns is the slot of the point in its cell ----
     for (size_t i = t; i < n; i += SMALL_FRONT_THREADS) {
         int wrap[3];
-        const int linear = locate_point(points, i, plan, header, speculative, wrap);
+        const int linear = locate_point(
+            load_real(points, 3 * i + 0), load_real(points, 3 * i + 1), load_real(points, 3 * i + 2), i, plan, header, speculative, wrap
+        );
         cell_of[i] = linear;
         rank[i] = atomicAdd(&hist[linear], 1);
         shift[3 * i + 0] = wrap[0];
@@ -1797,7 +1894,7 @@ __device__ __forceinline__ void store_both(
 template <bool FULL, bool SLAB>
 __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, const int UNIT_RUN, const long long* __restrict__ global_index
+    DeviceHeader* header, const int UNIT_RUN
 ) {
     extern __shared__ __align__(16) unsigned char fused_smem[];
     FusedShared& sh = *reinterpret_cast<FusedShared*>(fused_smem);
@@ -1921,16 +2018,10 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     sh.x[s] = px;
                     sh.y[s] = py;
                     sh.z[s] = pz;
-                    int index_j;
-                    if (SLAB) {
-                        index_j = static_cast<int>(global_index[sorted.index[p]]);
-                        if (sh.table.self_ok[t]) {
-                            atomicOr(&sh.owned_word[s >> 5], 1u << (s & 31));
-                        }
-                    } else {
-                        index_j = sorted.index[p];
+                    if (SLAB && sh.table.self_ok[t]) {
+                        atomicOr(&sh.owned_word[s >> 5], 1u << (s & 31));
                     }
-                    sh.sj[s] = make_int4(r0, r1, r2, index_j);
+                    sh.sj[s] = make_int4(r0, r1, r2, sorted.index[p]);
                     // image of the candidate seen from this unit (most candidates of a large box have none)
                     double ix = px;
                     double iy = py;
@@ -1991,7 +2082,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         si0 = sorted.shift[3 * pi + 0];
                         si1 = sorted.shift[3 * pi + 1];
                         si2 = sorted.shift[3 * pi + 2];
-                        index_i = SLAB ? static_cast<int>(global_index[sorted.index[pi]]) : sorted.index[pi];
+                        index_i = sorted.index[pi];
                         xi = valid ? static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - sh.centre[0]) : nan;
                         yi = valid ? static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - sh.centre[1]) : nan;
                         zi = valid ? static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - sh.centre[2]) : nan;
@@ -2338,6 +2429,10 @@ void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic
     header_init_kernel<<<1, CTA_THREADS, 0, stream>>>(header, box, periodic, nullptr, 0, 0, ExpectedInputs{});
 }
 
+void launch_header_reset(DeviceHeader* header, int32_t* zero, size_t n_zero, cudaStream_t stream) {
+    header_init_kernel<<<header_blocks(n_zero), CTA_THREADS, 0, stream>>>(header, RealView{nullptr, 0}, nullptr, zero, n_zero, 0, ExpectedInputs{});
+}
+
 void launch_header_init_speculative(
     DeviceHeader* header, RealView box, const bool* periodic, int32_t* zero, size_t n_zero, const double expected_box[9],
     const bool expected_periodic[3], cudaStream_t stream
@@ -2347,7 +2442,8 @@ void launch_header_init_speculative(
     );
 }
 
-void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream) {
+void launch_bounds(const PointSource& source, DeviceHeader* header, cudaStream_t stream) {
+    const size_t n = source.n_index();
     if (n == 0) {
         return;
     }
@@ -2355,18 +2451,32 @@ void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t
     // eight points or more per thread
     size_t blocks = (n + 8 * CTA_THREADS - 1) / (8 * CTA_THREADS);
     blocks = std::max<size_t>(1, std::min<size_t>(blocks, 148 * 2));
-    bounds_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(points, n, header);
+    if (source.message[0] != nullptr) {
+        bounds_kernel<true><<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(source, n, header);
+    } else {
+        bounds_kernel<false><<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(source, n, header);
+    }
 }
 
 void launch_bin(
-    RealView points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift, int32_t* cell_count,
-    DeviceHeader* header, bool check_points, cudaStream_t stream
+    const PointSource& source, size_t first, size_t last, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift,
+    int32_t* cell_count, DeviceHeader* header, bool check_points, bool chained, cudaStream_t stream
 ) {
-    size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    launch_chained(
-        bin_kernel, static_cast<unsigned>(blocks), CTA_THREADS, 0, stream, points, n, plan, cell_of, rank, shift, cell_count, header,
-        check_points ? 1 : 0
-    );
+    if (last <= first) {
+        return;
+    }
+    const unsigned blocks = static_cast<unsigned>((last - first + CTA_THREADS - 1) / CTA_THREADS);
+    const int check = check_points ? 1 : 0;
+    const bool halo = source.message[0] != nullptr && source.capacity > 0;
+    if (halo && chained) {
+        launch_chained(bin_kernel<true>, blocks, CTA_THREADS, 0, stream, source, first, last, plan, cell_of, rank, shift, cell_count, header, check);
+    } else if (halo) {
+        bin_kernel<true><<<blocks, CTA_THREADS, 0, stream>>>(source, first, last, plan, cell_of, rank, shift, cell_count, header, check);
+    } else if (chained) {
+        launch_chained(bin_kernel<false>, blocks, CTA_THREADS, 0, stream, source, first, last, plan, cell_of, rank, shift, cell_count, header, check);
+    } else {
+        bin_kernel<false><<<blocks, CTA_THREADS, 0, stream>>>(source, first, last, plan, cell_of, rank, shift, cell_count, header, check);
+    }
 }
 
 size_t scan_tmp_bytes(size_t n) {
@@ -2399,13 +2509,21 @@ void launch_scan_rows(
 }
 
 void launch_scatter(
-    RealView points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
-    SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
+    const PointSource& source, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
+    size_t n_cells, SortedPoints sorted, int32_t* sorted_global, DeviceHeader* header, cudaStream_t stream
 ) {
-    size_t blocks = (n + CTA_THREADS - 1) / CTA_THREADS;
-    launch_chained(scatter_index_kernel, static_cast<unsigned>(blocks), CTA_THREADS, 0, stream, n, cell_of, rank, cell_start, sorted.index, header);
-    blocks = (3 * n + CTA_THREADS - 1) / CTA_THREADS;
-    launch_chained(gather_records_kernel, static_cast<unsigned>(blocks), CTA_THREADS, 0, stream, points, n, shift, sorted, header);
+    const size_t n = source.n_index();
+    const unsigned index_blocks = static_cast<unsigned>((n + CTA_THREADS - 1) / CTA_THREADS);
+    const unsigned record_blocks = static_cast<unsigned>((3 * n + CTA_THREADS - 1) / CTA_THREADS);
+    const int32_t* n_records = cell_start + n_cells;
+    const DeviceHeader* read_header = header;
+    if (source.message[0] != nullptr && source.capacity > 0) {
+        launch_chained(scatter_index_kernel<true>, index_blocks, CTA_THREADS, 0, stream, source, n, cell_of, rank, cell_start, sorted.index, read_header);
+        launch_chained(gather_records_kernel<true>, record_blocks, CTA_THREADS, 0, stream, source, n, n_records, shift, sorted, sorted_global, header);
+    } else {
+        launch_chained(scatter_index_kernel<false>, index_blocks, CTA_THREADS, 0, stream, source, n, cell_of, rank, cell_start, sorted.index, read_header);
+        launch_chained(gather_records_kernel<false>, record_blocks, CTA_THREADS, 0, stream, source, n, n_records, shift, sorted, sorted_global, header);
+    }
 }
 
 void launch_count(
@@ -2438,7 +2556,7 @@ void launch_emit(
 
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, const long long* global_index, cudaStream_t stream
+    DeviceHeader* header, cudaStream_t stream
 ) {
     // as many CTAs as are resident (4 per SM by registers and shared memory), which take
     // runs of units from a shared counter; small systems give every unit its own CTA
@@ -2462,20 +2580,81 @@ void launch_pairs(
     out.interleave_ok = aligned(out.pairs, 32) && aligned(out.shifts, 8) && aligned(out.distances, value_bytes) && aligned(out.vectors, value_bytes);
     if (plan.window_axis >= 0) {
         if (plan.full) {
-            pairs_kernel<true, true><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, global_index);
+            launch_chained(pairs_kernel<true, true>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run);
         } else {
-            pairs_kernel<false, true><<<grid, CTA_THREADS, smem, stream>>>(plan, cell_start, sorted, out, capacity, header, unit_run, global_index);
+            launch_chained(pairs_kernel<false, true>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run);
         }
     } else if (plan.full) {
-        launch_chained(
-            pairs_kernel<true, false>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run,
-            static_cast<const long long*>(nullptr)
-        );
+        launch_chained(pairs_kernel<true, false>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run);
     } else {
-        launch_chained(
-            pairs_kernel<false, false>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run,
-            static_cast<const long long*>(nullptr)
-        );
+        launch_chained(pairs_kernel<false, false>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// checksum of a list
+// Lists of the same system built by different decompositions (one GPU, slabs
+// over several GPUs, the CPU reference) hold the same rows in different orders;
+// a sum of per-row hashes compares them without sorting 10^8 rows.
+// ---------------------------------------------------------------------------
+
+namespace {
+
+__host__ __device__ __forceinline__ unsigned long long mix64(unsigned long long x) {
+    x ^= x >> 33;
+    x *= 0xff51afd7ed558ccdull;
+    x ^= x >> 33;
+    x *= 0xc4ceb9fe1a85ec53ull;
+    x ^= x >> 33;
+    return x;
+}
+
+__global__ void __launch_bounds__(CTA_THREADS) checksum_kernel(
+    const unsigned long long* __restrict__ pairs, const int32_t* __restrict__ shifts, const double* __restrict__ distances,
+    const int values_float, size_t n, unsigned long long* __restrict__ result
+) {
+    unsigned long long h0 = 0, h1 = 0, h2 = 0;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t r = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < n; r += stride) {
+        const ulonglong2 ij = reinterpret_cast<const ulonglong2*>(pairs)[r];
+        unsigned long long key = ij.x * 0x9e3779b97f4a7c15ull + ij.y * 0xc2b2ae3d27d4eb4full;
+        if (shifts != nullptr) {
+            key += static_cast<unsigned long long>(static_cast<unsigned>(shifts[3 * r + 0])) * 0x165667b19e3779f9ull;
+            key += static_cast<unsigned long long>(static_cast<unsigned>(shifts[3 * r + 1])) * 0x27d4eb2f165667c5ull;
+            key += static_cast<unsigned long long>(static_cast<unsigned>(shifts[3 * r + 2])) * 0x85ebca77c2b2ae63ull;
+        }
+        unsigned long long value_bits = 0;
+        if (distances != nullptr) {
+            value_bits = values_float ? static_cast<unsigned long long>(__float_as_uint(reinterpret_cast<const float*>(distances)[r]))
+                                      : static_cast<unsigned long long>(__double_as_longlong(distances[r]));
+        }
+        h0 += mix64(key);
+        h1 += mix64(key ^ 0x5555555555555555ull);
+        h2 += mix64(key + value_bits * 0xd6e8feb86659fd93ull);
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        h0 += __shfl_xor_sync(FULL_MASK, h0, offset);
+        h1 += __shfl_xor_sync(FULL_MASK, h1, offset);
+        h2 += __shfl_xor_sync(FULL_MASK, h2, offset);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(&result[0], h0);
+        atomicAdd(&result[1], h1);
+        atomicAdd(&result[2], h2);
+    }
+}
+
+} // namespace
+
+void launch_checksum(
+    const unsigned long long* pairs, const int32_t* shifts, const double* distances, int values_float, size_t n, unsigned long long* result,
+    cudaStream_t stream
+) {
+    cudaMemsetAsync(result, 0, 4 * sizeof(unsigned long long), stream);
+    if (n != 0) {
+        const size_t blocks = std::min<size_t>((n + CTA_THREADS - 1) / CTA_THREADS, 148 * 8);
+        checksum_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(pairs, shifts, distances, values_float, n, result);
     }
 }
 

@@ -28,6 +28,7 @@ struct DeviceHeader {
     unsigned int pad;
     double box[9];                   // copy of the caller's box
     unsigned char periodic[8];       // copy of the caller's periodic flags
+    unsigned long long halo_count[2]; // slab decomposition: records in the two halo messages of this build
 };
 
 constexpr unsigned int STATUS_MASK_OVERFLOW = 1u;
@@ -35,6 +36,8 @@ constexpr unsigned int STATUS_BAD_POINT = 2u;  // a point has a non-finite coord
 constexpr unsigned int STATUS_PLAN_STALE = 4u; // box / periodicity / extent differ from what the plan was made for
 constexpr unsigned int STATUS_ABORT_MASK = STATUS_BAD_POINT | STATUS_PLAN_STALE;
 constexpr unsigned int STATUS_SINGULAR_BOX = 8u; // batches: the box of a system is not invertible
+constexpr unsigned int STATUS_HALO_OVERFLOW = 16u; // slab decomposition: a halo message holds fewer records than were selected
+constexpr unsigned int STATUS_INDEX_RANGE = 32u;   // slab decomposition: a global index does not fit 31 bits
 constexpr unsigned long long NO_BAD_POINT = ~0ull;
 
 /// Cell-sorted copy of the points ("records"): original position, original
@@ -62,6 +65,32 @@ struct RealView {
     int is_float;
 };
 
+/// Where the points of a build come from. Segment 0 is an array of the
+/// caller (n0 points; `global_index`, when given, maps them to indices in a
+/// larger system). Segments 1 and 2 exist for slab-decomposed systems only:
+/// the halo messages received from the upper and the lower neighbour, rows of
+/// 4 doubles each, row 0 = number of records, every other row = x, y, z and the
+/// global index as raw 64 bits; a message holds at most `capacity` records.
+/// Local indices: [0, n0) segment 0, [n0, n0 + capacity) segment 1,
+/// [n0 + capacity, n0 + 2 capacity) segment 2; slots past a message's record
+/// count are empty.
+struct PointSource {
+    RealView points;
+    const long long* global_index;
+    unsigned long long n0;
+    const double* message[2];
+    unsigned long long capacity;
+
+    /// Size of the local index space.
+    size_t n_index() const {
+        return static_cast<size_t>(n0 + (message[0] != nullptr ? 2 * capacity : 0));
+    }
+};
+
+inline PointSource flat_source(RealView points, size_t n) {
+    return PointSource{points, nullptr, n, {nullptr, nullptr}, 0};
+}
+
 // ---- launch wrappers (all asynchronous on `stream`) ----
 
 void launch_header_init(DeviceHeader* header, RealView box, const bool* periodic, cudaStream_t stream);
@@ -75,16 +104,22 @@ void launch_header_init_speculative(
     const bool expected_periodic[3], cudaStream_t stream
 );
 
+/// Header reset for a build whose box is known on the host (nothing is read
+/// from device memory); also zeroes the `n_zero` counters of the cell histogram.
+void launch_header_reset(DeviceHeader* header, int32_t* zero, size_t n_zero, cudaStream_t stream);
+
 /// Min / max of every coordinate and the first non-finite point.
-void launch_bounds(RealView points, size_t n, DeviceHeader* header, cudaStream_t stream);
+void launch_bounds(const PointSource& source, DeviceHeader* header, cudaStream_t stream);
 
 /// Wrap into the cell, pick the cell, histogram with warp-aggregated atomics.
 /// `check_points`: the plan is speculative; a non-finite point sets
 /// STATUS_BAD_POINT (and first_bad), a point outside the cells of a
 /// non-periodic direction STATUS_PLAN_STALE.
+/// Bins the local indices [first, last). `chained`: the launch follows the
+/// previous kernel of the stream as a programmatic dependent launch.
 void launch_bin(
-    RealView points, size_t n, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift,
-    int32_t* cell_count, DeviceHeader* header, bool check_points, cudaStream_t stream
+    const PointSource& source, size_t first, size_t last, const GridPlan& plan, int32_t* cell_of, int32_t* rank, int32_t* shift,
+    int32_t* cell_count, DeviceHeader* header, bool check_points, bool chained, cudaStream_t stream
 );
 
 /// Exclusive scan of int32 counts into int32 starts (n + 1 entries).
@@ -97,10 +132,13 @@ void launch_scan_rows(
 /// Bytes of temporary storage the scans need for n elements.
 size_t scan_tmp_bytes(size_t n);
 
-/// Counting-sort scatter into the cell-sorted records.
+/// Counting-sort scatter into the cell-sorted records. `n_cells`: cells of the
+/// plan (cell_start[n_cells] is the number of records). `sorted_global`, when
+/// not null, receives the global index of every record (31 bits; a larger one
+/// sets STATUS_INDEX_RANGE).
 void launch_scatter(
-    RealView points, size_t n, const int32_t* cell_of, const int32_t* rank, const int32_t* shift,
-    const int32_t* cell_start, SortedPoints sorted, const DeviceHeader* header, cudaStream_t stream
+    const PointSource& source, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
+    size_t n_cells, SortedPoints sorted, int32_t* sorted_global, DeviceHeader* header, cudaStream_t stream
 );
 
 /// Small systems: header reset and plan check (when `speculative`), binning,
@@ -142,11 +180,12 @@ void launch_emit(
 /// stencil once and writes the pairs into ranges claimed from
 /// header->pair_cursor. Blocks whose range would pass `capacity` (in pairs)
 /// only count.
-/// With plan.window_axis >= 0 (slab decomposition) `global_index` maps the
-/// local index of a point to the index written into the pairs.
+/// The indices written into the pairs are sorted.index: for a slab of a
+/// decomposed system (plan.window_axis >= 0) the caller passes the records'
+/// global indices there.
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, const long long* global_index, cudaStream_t stream
+    DeviceHeader* header, cudaStream_t stream
 );
 
 // ---- batches of small systems (small_systems.cu) ----
@@ -173,6 +212,15 @@ void launch_small_count(const BatchInput& in, size_t max_points, unsigned long l
 /// Pass 2: every system writes its pairs at system_start[system].
 void launch_small_emit(
     const BatchInput& in, size_t max_points, const unsigned long long* system_start, PairOutput out, DeviceHeader* header,
+    cudaStream_t stream
+);
+
+/// Order-independent checksum of a list: result[0], result[1] = two sums
+/// (mod 2^64) of 64-bit hashes of every (i, j, S) row, result[2] = the same
+/// with the bits of the distance mixed in (result[3] is cleared). Null
+/// `shifts` count as zero shifts, null `distances` as zero distances.
+void launch_checksum(
+    const unsigned long long* pairs, const int32_t* shifts, const double* distances, int values_float, size_t n, unsigned long long* result,
     cudaStream_t stream
 );
 

@@ -1,17 +1,23 @@
 // An entry point that builds a neighbor list without allocating anything.
 //
-// Who needs it: code that is not allowed to call cudaMalloc at the moment it
-// needs a list. Typical cases are a step function that runs while a CUDA
-// graph is being captured or replayed elsewhere in the process (an allocation
-// synchronises the whole device), a host application that gave all device
-// memory to its own pool at start-up, and real-time loops that forbid
-// anything with unbounded latency. vesin_neighbors grows its workspace and
-// its output arrays with cudaMalloc whenever a system is larger than the last
-// one; this entry point never does: the caller brings the output arrays, and
-// the scratch the kernels need (cell histogram, cell offsets, the cell-sorted
-// copy of the points, the read-back header) lives in one file-scope device
-// array of fixed size that every GPU holds from the moment the library is
-// loaded until the process exits.
+// Who needs it: code that may not call cudaMalloc at the moment it needs a
+// list. A host application that handed all device memory to its own pool at
+// start-up has none left for the driver to give out; a simulation loop with a
+// hard bound on the latency of a step cannot afford a call that may block on
+// the whole device; a plugin running inside a framework that forbids
+// allocations outside its allocator is simply not allowed to. vesin_neighbors
+// grows its workspace and its output arrays with cudaMalloc whenever a system
+// is larger than the last one; this entry point never does: the caller brings
+// the output arrays, and the scratch the kernels need (cell histogram, cell
+// offsets, the cell-sorted copy of the points, the read-back header) lives in
+// one file-scope device array of fixed size that every GPU holds from the
+// moment the library is loaded until the process exits.
+//
+// How it runs: every kernel is launched on the legacy default stream, and the
+// host reads a small header back twice with a blocking cudaMemcpy (after the
+// pass over the points that finds their extent, and at the end for the number
+// of pairs). The call therefore behaves like any synchronous default-stream
+// work of the caller.
 //
 // Consequences of the fixed array, all documented in include/vesin_b200.h:
 //   * systems larger than VESIN_B200_NO_ALLOC_MAX_POINTS are refused;
@@ -159,7 +165,7 @@ size_t build(
 
     // the header (cursor, status, bounds) is re-initialised by a kernel
     launch_header_init(d_header, RealView{box, 0}, periodic, stream);
-    launch_bounds(RealView{points, 0}, n_points, d_header, stream);
+    launch_bounds(flat_source(RealView{points, 0}, n_points), d_header, stream);
     check(cudaGetLastError(), "launch");
     DeviceHeader header;
     check(cudaMemcpy(&header, d_header, sizeof(header), cudaMemcpyDeviceToHost), "cudaMemcpy(header)");
@@ -183,10 +189,13 @@ size_t build(
 
     // the histogram is the one array that has to start at zero
     check(cudaMemsetAsync(cell_count, 0, static_cast<size_t>(plan.n_cells_total) * sizeof(int32_t), stream), "cudaMemsetAsync");
-    launch_bin(RealView{points, 0}, n_points, plan, cell_of, rank, shift, cell_count, d_header, false, stream);
+    launch_bin(flat_source(RealView{points, 0}, n_points), 0, n_points, plan, cell_of, rank, shift, cell_count, d_header, false, true, stream);
     launch_scan_cells(cell_count, cell_start, static_cast<size_t>(plan.n_cells_total), scan_tmp, stream);
-    launch_scatter(RealView{points, 0}, n_points, cell_of, rank, shift, cell_start, sorted, d_header, stream);
-    launch_pairs(plan, cell_start, sorted, out, capacity, d_header, nullptr, stream);
+    launch_scatter(
+        flat_source(RealView{points, 0}, n_points), cell_of, rank, shift, cell_start, static_cast<size_t>(plan.n_cells_total), sorted, nullptr,
+        d_header, stream
+    );
+    launch_pairs(plan, cell_start, sorted, out, capacity, d_header, stream);
     check(cudaGetLastError(), "launch");
     check(cudaMemcpy(&header, d_header, sizeof(header), cudaMemcpyDeviceToHost), "cudaMemcpy(header)");
     return static_cast<size_t>(header.pair_cursor);
