@@ -49,6 +49,7 @@ WORKLOADS = {
     "diamond512k_half": (lambda: workloads.diamond(40), 5.0, False, False, "diamond 40x40x40 (512000 atoms), cutoff 5.0, half list, fp64, ijSdD"),
     "diamond512k_f32": (lambda: workloads.diamond(40), 5.0, True, False, "diamond 40x40x40 (512000 atoms), cutoff 5.0, full list, fp32 in / fp32 d and D out (decisions in fp64), ijSdD"),
     "diamond512k_sorted": (lambda: workloads.diamond(40), 5.0, True, True, "diamond 40x40x40 (512000 atoms), cutoff 5.0, full list sorted by first index, fp64, ijSdD"),
+    "diamond512k_canonical": (lambda: workloads.diamond(40), 5.0, True, "canonical", "diamond 40x40x40 (512000 atoms), cutoff 5.0, full list in canonical (i, j, S) order (sorted on the device), fp64, ijSdD"),
     "diamond110k": (lambda: workloads.diamond(24), 5.0, True, False, "diamond 24x24x24 (110592 atoms), cutoff 5.0, full list, fp64, ijSdD"),
     "diamond1000": (lambda: workloads.diamond(5), 5.0, True, False, "diamond 5x5x5 (1000 atoms), cutoff 5.0, full list, fp64, ijSdD"),
     "triclinic64": (lambda: workloads.small_triclinic(), 9.0, True, False, "64 atoms in a small triclinic cell, cutoff 9.0, full list, fp64, ijSdD"),
@@ -69,7 +70,7 @@ SHARDED_WORKLOADS = {
 }
 
 # what the default run reports besides the headline
-EXTRA_WORKLOADS = ("diamond512k_half", "diamond512k_f32", "diamond512k_sorted", "diamond1000", "triclinic64", "liquid2m", "liquid2m_f32")
+EXTRA_WORKLOADS = ("diamond512k_half", "diamond512k_f32", "diamond512k_sorted", "diamond512k_canonical", "diamond1000", "triclinic64", "liquid2m", "liquid2m_f32")
 EXTRA_STEPS = 10
 
 
@@ -192,6 +193,7 @@ def measured_traffic(kernel, n_pairs):
 
 
 def time_reference_cpu(system, cutoff, full, steps, warmup, budget_s, sorted=False):
+    sorted = bool(sorted)
     """Reference CPU path on all host cores; returns (pairs, seconds per build,
     builds timed, threads). The thread count is passed explicitly: launchers
     such as torch.distributed.run export OMP_NUM_THREADS=1, which the
@@ -421,10 +423,12 @@ class PlainBuild:
         self.d_box = torch.from_numpy(np.ascontiguousarray(box, dtype=dtype)).to(harness.device)
         self.d_periodic = torch.from_numpy(np.ascontiguousarray(periodic, dtype=np.bool_)).to(harness.device)
         self.entry_point = harness.lib.vesin_b200_neighbors_f32 if float_io else harness.lib.vesin_neighbors
+        if sorted_list == "canonical":
+            self.entry_point = harness.lib.vesin_b200_neighbors_canonical
         options = VesinOptions()
         options.cutoff = cutoff
         options.full = full
-        options.sorted = sorted_list
+        options.sorted = bool(sorted_list)
         options.algorithm = 0
         options.n_threads = 0
         options.return_shifts = True

@@ -61,6 +61,28 @@ VESIN_API int vesin_b200_neighbors_f32(
 );
 
 /*
+ * No counterpart in the reference, whose `sorted` option orders a list by the
+ * first index only and leaves the order of second indices and shifts open
+ * (vesin/include/vesin.h:55-58; device sort keyed on pairs[.][0],
+ * vesin/src/cuda/sort_pairs.cu:3-12): this entry point returns THE canonical
+ * list, sorted by (i, j, Sx, Sy, Sz), so that two lists of the same system can
+ * be compared element by element without sorting them on the host.
+ * `options.sorted` is taken as set. Rows are sorted on the device after the
+ * build, into a second set of output arrays (the list then owns twice the
+ * memory of an unsorted one). Everything else as vesin_neighbors.
+ */
+VESIN_API int vesin_b200_neighbors_canonical(
+    const double (*points)[3],
+    size_t n_points,
+    const double box[3][3],
+    const bool periodic[3],
+    struct VesinDevice device,
+    struct VesinOptions options,
+    struct VesinNeighborList* neighbors,
+    const char** error_message
+);
+
+/*
  * No counterpart in the reference (its callers loop over systems, e.g.
  * python/vesin/vesin/metatomic/_neighbors.py:197-199): the lists of a batch of
  * independent small systems in ONE call.

@@ -69,6 +69,7 @@ EXPORTED_SYMBOLS = (
     "vesin_b200_neighbors_slab",
     "vesin_b200_pack_halo",
     "vesin_b200_neighbors_f32",
+    "vesin_b200_neighbors_canonical",
     "vesin_b200_neighbors_slab_f32",
     "vesin_b200_slab_geometry",
     "vesin_b200_sharded_unique_id",
@@ -174,6 +175,8 @@ def get_library():
     ]
     lib.vesin_b200_neighbors_f32.restype = ctypes.c_int
     lib.vesin_b200_neighbors_f32.argtypes = lib.vesin_neighbors.argtypes
+    lib.vesin_b200_neighbors_canonical.restype = ctypes.c_int
+    lib.vesin_b200_neighbors_canonical.argtypes = lib.vesin_neighbors.argtypes
     lib.vesin_b200_neighbors_slab_f32.restype = ctypes.c_int
     lib.vesin_b200_neighbors_slab_f32.argtypes = lib.vesin_b200_neighbors_slab.argtypes
     lib.vesin_b200_slab_geometry.restype = ctypes.c_int

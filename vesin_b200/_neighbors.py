@@ -51,8 +51,11 @@ def _view(ptr, shape, typestr, device, owner):
 class NeighborList:
     """A neighbor list calculator (CUDA engine)."""
 
-    def __init__(self, cutoff, full_list, sorted=False, algorithm="auto", skin=0.0, n_threads=0):
+    def __init__(self, cutoff, full_list, sorted=False, algorithm="auto", skin=0.0, n_threads=0, canonical=False):
+        """Arguments as the reference's calculator; `canonical` (an addition)
+        asks for the list sorted by (i, j, Sx, Sy, Sz) instead of by i only."""
         self._lib = get_library()
+        self.canonical = bool(canonical)
         self.cutoff = float(cutoff)
         self.full_list = bool(full_list)
         self.sorted = bool(sorted)
@@ -127,7 +130,7 @@ class NeighborList:
         if from_torch:
             floating = initial_dtype.is_floating_point
             out_dtype = initial_dtype if floating else torch.float64
-            float_io = initial_dtype == torch.float32
+            float_io = initial_dtype == torch.float32 and not self.canonical  # the canonical entry point is fp64
             work_dtype = torch.float32 if float_io else torch.float64
             d_points = points.to(work_dtype).contiguous()
             d_box = box.to(work_dtype).contiguous()
@@ -135,7 +138,7 @@ class NeighborList:
         else:
             floating = np.issubdtype(initial_dtype, np.floating)
             out_dtype = initial_dtype if floating else np.float64
-            float_io = initial_dtype == np.float32
+            float_io = initial_dtype == np.float32 and not self.canonical
             work_dtype = np.float32 if float_io else np.float64
             d_points = torch.from_numpy(np.ascontiguousarray(points, dtype=work_dtype)).to(device, non_blocking=False)
             d_box = torch.from_numpy(np.ascontiguousarray(box, dtype=work_dtype)).to(device)
@@ -169,6 +172,8 @@ class NeighborList:
         torch.cuda.current_stream(device).synchronize()
         error_message = ctypes.c_char_p()
         entry_point = self._lib.vesin_b200_neighbors_f32 if float_io else self._lib.vesin_neighbors
+        if self.canonical:
+            entry_point = self._lib.vesin_b200_neighbors_canonical
         status = entry_point(
             d_points.data_ptr(),
             d_points.shape[0],

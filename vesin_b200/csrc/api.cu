@@ -59,7 +59,8 @@ static int neighbors_entry(
     VesinOptions options,
     VesinNeighborList* neighbors,
     const char** error_message,
-    bool float_io
+    bool float_io,
+    bool canonical = false
 ) {
     // Order and wording of the checks: vesin/src/vesin.cpp:51-105
     if (error_message == nullptr) {
@@ -107,7 +108,7 @@ static int neighbors_entry(
 
     try {
         if (device.type == VesinCUDA) {
-            vb200::neighbors(points, n_points, box, periodic, options, *neighbors, float_io);
+            vb200::neighbors(points, n_points, box, periodic, options, *neighbors, float_io, canonical);
         } else if (device.type == VesinCPU) {
             throw std::runtime_error(
                 "this build of vesin is the CUDA (sm_100a) engine only: data on VesinCPU is not supported, "
@@ -155,6 +156,19 @@ extern "C" int vesin_b200_neighbors_f32(
     const char** error_message
 ) {
     return neighbors_entry(points, n_points, box, periodic, device, options, neighbors, error_message, /*float_io=*/true);
+}
+
+extern "C" int vesin_b200_neighbors_canonical(
+    const double (*points)[3],
+    size_t n_points,
+    const double box[3][3],
+    const bool periodic[3],
+    VesinDevice device,
+    VesinOptions options,
+    VesinNeighborList* neighbors,
+    const char** error_message
+) {
+    return neighbors_entry(points, n_points, box, periodic, device, options, neighbors, error_message, /*float_io=*/false, /*canonical=*/true);
 }
 
 extern "C" void vesin_free(VesinNeighborList* neighbors) {

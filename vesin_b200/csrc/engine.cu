@@ -8,6 +8,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <utility>
 #include <stdexcept>
 #include <string>
 
@@ -114,6 +115,8 @@ struct Workspace {
 
     // output arrays (capacity in pairs); kept allocated when not requested
     DeviceBuffer out_pairs, out_shifts, out_distances, out_vectors;
+    // second set of output arrays: where a canonical list is sorted into (the sets swap roles)
+    DeviceBuffer alt_pairs, alt_shifts, alt_distances, alt_vectors;
 
     // What the last build on this list saw, and the plan made from it: the
     // next build starts from this plan without waiting for a read-back.
@@ -137,7 +140,7 @@ struct Workspace {
         for (DeviceBuffer* buffer :
              {&cell_of, &rank, &shift, &cell_count, &cell_start, &sorted_pos, &sorted_index, &sorted_shift, &masks, &unit_mask_base,
               &unit_words, &unit_count, &unit_start, &row_count, &row_start, &row_fill, &scan_tmp, &batch_offsets, &sorted_global, &checksum, &out_pairs,
-              &out_shifts, &out_distances, &out_vectors}) {
+              &out_shifts, &out_distances, &out_vectors, &alt_pairs, &alt_shifts, &alt_distances, &alt_vectors}) {
             buffer->release();
         }
         if (d_header != nullptr) {
@@ -356,8 +359,12 @@ void neighbors(
     const bool periodic[3],
     VesinOptions options,
     VesinNeighborList& list,
-    bool float_io
+    bool float_io,
+    bool canonical
 ) {
+    if (canonical) {
+        options.sorted = true; // rows in index order first, then every row is sorted
+    }
     int device_count = 0;
     if (cudaGetDeviceCount(&device_count) != cudaSuccess || device_count == 0) {
         cudaGetLastError();
@@ -620,8 +627,6 @@ void neighbors(
         // ---- sorted list: rows in index order need a scan between two passes ----
         ws.unit_mask_base.reserve(n_units * sizeof(unsigned long long));
         ws.unit_words.reserve(n_units * sizeof(uint32_t));
-        ws.unit_count.reserve(n_units * sizeof(unsigned long long));
-        ws.unit_start.reserve((n_units + 1) * sizeof(unsigned long long));
         ws.row_count.reserve(n_points * sizeof(uint32_t));
         ws.row_start.reserve((n_points + 1) * sizeof(unsigned long long));
         ws.row_fill.reserve(n_points * sizeof(uint32_t));
@@ -639,12 +644,10 @@ void neighbors(
         bool refused = false;
         for (int attempt = 0;; attempt++) {
             timer.begin(VesinB200StageCount);
-            VB200_CUDA(cudaMemsetAsync(ws.unit_count.ptr, 0, n_units * sizeof(unsigned long long), stream));
             VB200_CUDA(cudaMemsetAsync(ws.row_count.ptr, 0, n_points * sizeof(uint32_t), stream));
             launch_count(
                 plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.masks.bytes / sizeof(uint32_t),
-                ws.unit_mask_base.as<unsigned long long>(), ws.unit_words.as<uint32_t>(), ws.unit_count.as<unsigned long long>(),
-                ws.row_count.as<uint32_t>(), ws.d_header, stream
+                ws.unit_mask_base.as<unsigned long long>(), ws.unit_words.as<uint32_t>(), ws.row_count.as<uint32_t>(), ws.d_header, stream
             );
             timer.end(VesinB200StageCount);
             timer.begin(VesinB200StageScanRows);
@@ -701,9 +704,40 @@ void neighbors(
             VB200_CUDA(cudaMemsetAsync(ws.row_fill.ptr, 0, n_points * sizeof(uint32_t), stream));
             launch_emit(
                 plan, ws.cell_start.as<int32_t>(), sorted, ws.masks.as<uint32_t>(), ws.unit_mask_base.as<unsigned long long>(),
-                ws.unit_words.as<uint32_t>(), ws.unit_start.as<unsigned long long>(), ws.row_start.as<unsigned long long>(),
-                ws.row_fill.as<uint32_t>(), out, stream
+                ws.unit_words.as<uint32_t>(), ws.row_start.as<unsigned long long>(), ws.row_fill.as<uint32_t>(), out, stream
             );
+            if (canonical) {
+                // every row sorted by (second index, shift) into a second set of arrays, which then become the list's
+                ws.alt_pairs.reserve(ws.out_pairs.bytes);
+                PairOutput sorted_out{ws.alt_pairs.as<unsigned long long>(), nullptr, nullptr, nullptr, float_io ? 1 : 0};
+                if (options.return_shifts) {
+                    ws.alt_shifts.reserve(ws.out_shifts.bytes);
+                    sorted_out.shifts = ws.alt_shifts.as<int32_t>();
+                }
+                if (options.return_distances) {
+                    ws.alt_distances.reserve(ws.out_distances.bytes);
+                    sorted_out.distances = ws.alt_distances.as<double>();
+                }
+                if (options.return_vectors) {
+                    ws.alt_vectors.reserve(ws.out_vectors.bytes);
+                    sorted_out.vectors = ws.alt_vectors.as<double>();
+                }
+                launch_sort_rows(ws.row_start.as<unsigned long long>(), n_points, out, sorted_out, stream);
+                std::swap(ws.out_pairs, ws.alt_pairs);
+                list.pairs = reinterpret_cast<size_t(*)[2]>(ws.out_pairs.ptr);
+                if (options.return_shifts) {
+                    std::swap(ws.out_shifts, ws.alt_shifts);
+                    list.shifts = reinterpret_cast<int32_t(*)[3]>(ws.out_shifts.ptr);
+                }
+                if (options.return_distances) {
+                    std::swap(ws.out_distances, ws.alt_distances);
+                    list.distances = ws.out_distances.as<double>();
+                }
+                if (options.return_vectors) {
+                    std::swap(ws.out_vectors, ws.alt_vectors);
+                    list.vectors = reinterpret_cast<double(*)[3]>(ws.out_vectors.ptr);
+                }
+            }
             timer.end(VesinB200StageEmit);
             VB200_CUDA(cudaGetLastError());
             VB200_CUDA(cudaStreamSynchronize(stream));
@@ -1033,7 +1067,8 @@ void neighbors_slab_core(
                 set_outputs(list, ws, options, total + total / 16 + 256);
                 capacity = common_capacity(ws, options);
             }
-            VB200_CUDA(cudaMemsetAsync(&ws.d_header->pair_cursor, 0, 2 * sizeof(unsigned long long), stream)); // and run_cursor
+            // mask_cursor (the second run counter of a slab build), pair_cursor and run_cursor
+            VB200_CUDA(cudaMemsetAsync(&ws.d_header->mask_cursor, 0, 3 * sizeof(unsigned long long), stream));
         }
         if (refused) {
             continue;

@@ -17,6 +17,7 @@ namespace vb200 {
 /// error strings.
 /// With `float_io`, `points` and `box` are float arrays and the distances /
 /// vectors of the list are float arrays too (the decisions stay fp64).
+/// With `canonical`, the list comes out sorted by (i, j, Sx, Sy, Sz).
 void neighbors(
     const void* points,
     size_t n_points,
@@ -24,7 +25,8 @@ void neighbors(
     const bool periodic[3],
     VesinOptions options,
     VesinNeighborList& list,
-    bool float_io
+    bool float_io,
+    bool canonical = false
 );
 
 /// Lists of a batch of independent small systems in one call (no counterpart

@@ -1001,491 +1001,6 @@ __device__ __forceinline__ double exact_pair(
     return __dadd_rn(__dadd_rn(__dmul_rn(vx, vx), __dmul_rn(vy, vy)), __dmul_rn(vz, vz));
 }
 
-/// Mask words one home point needs: the sum over segment groups of the
-/// group's slots rounded up to whole words. Leaves the table of the LAST
-/// group in place and its slot count in `last_total`.
-__device__ __forceinline__ int words_of_unit(const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int n_groups, SegmentTable& table, int& last_total) {
-    int words = 0;
-    for (int g = 0; g < n_groups; g++) {
-        last_total = setup_segments(plan, cell_start, unit, g, table);
-        words += (last_total + 31) >> 5;
-    }
-    return words;
-}
-
-// ---------------------------------------------------------------------------
-// count pass
-// Replaces the distance test of find_neighbors_cell_list
-// (vesin/src/cuda/cell_list.cu:594-641) and the CPU callback
-// (vesin/src/cpu_cell_list.cpp:100-163).
-//
-// Lanes hold home points, candidates are broadcast from shared memory: every
-// lane builds the 32-bit hit word of its own point in a register, so the
-// inner loop has no votes and no shuffles. Warps split the words of a batch.
-// Hit words are stored as [tile][word][lane]: 128-byte coalesced.
-// ---------------------------------------------------------------------------
-
-constexpr int COUNT_BATCH = 1024; // candidate slots staged at once
-#define FAR_AWAY __int_as_float(0x7f800000) // +inf: never inside any cutoff
-
-__global__ void __launch_bounds__(CTA_THREADS, 4) count_kernel(
-    const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, uint32_t* __restrict__ masks,
-    unsigned long long mask_capacity, unsigned long long* __restrict__ unit_mask_base, uint32_t* __restrict__ unit_words,
-    unsigned long long* __restrict__ unit_count, uint32_t* __restrict__ row_count, DeviceHeader* header
-) {
-    __shared__ SegmentTable table;
-    __shared__ float4 stage[COUNT_BATCH];
-    __shared__ unsigned long long s_base;
-    __shared__ unsigned long long s_total;
-
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    if (header->status & STATUS_ABORT_MASK) {
-        return;
-    }
-
-    for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
-        const Unit unit = unit_of(plan, cell_start, u);
-        if (unit.n_home == 0) {
-            continue;
-        }
-        const int n_groups = (unit.n_stencil + SEG_MAX - 1) / SEG_MAX;
-        const int n_tiles = (unit.n_home + TILE_POINTS - 1) / TILE_POINTS;
-
-        // centre of the pencil: origin of the fp32 local frame
-        double centre[3];
-#pragma unroll
-        for (int c = 0; c < 3; c++) {
-            centre[c] = plan.origin[c] + (unit.c0 + 0.5 * unit.cells) * plan.cell_vec[0][c] + (unit.c1 + 0.5) * plan.cell_vec[1][c] +
-                        (unit.c2 + 0.5) * plan.cell_vec[2][c];
-        }
-
-        int group_total = 0;
-        const int words = words_of_unit(plan, cell_start, unit, n_groups, table, group_total);
-
-        // claim mask storage: n_tiles blocks of `words` x 32 lanes
-        if (threadIdx.x == 0) {
-            unsigned long long need = static_cast<unsigned long long>(n_tiles) * words * TILE_POINTS;
-            unsigned long long base = atomicAdd(&header->mask_cursor, need);
-            if (base + need > mask_capacity) {
-                atomicOr(&header->status, STATUS_MASK_OVERFLOW);
-                base = ~0ull;
-            } else {
-                unit_mask_base[u] = base;
-                unit_words[u] = static_cast<uint32_t>(words);
-            }
-            s_base = base;
-            s_total = 0;
-        }
-        __syncthreads();
-        const unsigned long long base = s_base;
-        if (base == ~0ull) {
-            __syncthreads();
-            continue; // the host grows the storage and runs the pass again
-        }
-
-        unsigned long long warp_hits = 0;
-        int word_base = 0;
-        for (int g = 0; g < n_groups; g++) {
-            if (n_groups > 1) {
-                group_total = setup_segments(plan, cell_start, unit, g, table);
-            }
-            for (int batch0 = 0; batch0 < group_total; batch0 += COUNT_BATCH) {
-                const int batch_slots = min(COUNT_BATCH, group_total - batch0);
-                const int batch_words = (batch_slots + 31) >> 5;
-
-                // ---- stage this batch as fp32 coordinates relative to the centre:
-                //      warps take segments, lanes take the points of a segment ----
-                for (int t = warp; t < SEG_MAX; t += CTA_WARPS) {
-                    const int seg_slot0 = table.slot0[t];
-                    const int seg_len = table.slot0[t + 1] - seg_slot0;
-                    const int first = max(seg_slot0, batch0) - seg_slot0;
-                    const int last = min(seg_slot0 + seg_len, batch0 + batch_slots) - seg_slot0;
-                    if (first >= last) {
-                        continue;
-                    }
-                    const double q0 = table.q[0][t], q1 = table.q[1][t], q2 = table.q[2][t];
-                    const unsigned self_ok = static_cast<unsigned>(table.self_ok[t]);
-                    for (int o = first + lane; o < last; o += 32) {
-                        const size_t p = static_cast<size_t>(table.start[t]) + o;
-                        const double rel0 = q0 - sorted.shift[3 * p + 0];
-                        const double rel1 = q1 - sorted.shift[3 * p + 1];
-                        const double rel2 = q2 - sorted.shift[3 * p + 2];
-                        const double x = sorted.pos[3 * p + 0] + (rel0 * plan.H[0][0] + rel1 * plan.H[1][0] + rel2 * plan.H[2][0]) - centre[0];
-                        const double y = sorted.pos[3 * p + 1] + (rel0 * plan.H[0][1] + rel1 * plan.H[1][1] + rel2 * plan.H[2][1]) - centre[1];
-                        const double z = sorted.pos[3 * p + 2] + (rel0 * plan.H[0][2] + rel1 * plan.H[1][2] + rel2 * plan.H[2][2]) - centre[2];
-                        const unsigned tag = (static_cast<unsigned>(sorted.index[p]) << 1) | self_ok;
-                        stage[seg_slot0 + o - batch0] =
-                            make_float4(static_cast<float>(x), static_cast<float>(y), static_cast<float>(z), __uint_as_float(tag));
-                    }
-                }
-                for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
-                    stage[s] = make_float4(FAR_AWAY, FAR_AWAY, FAR_AWAY, 0.0f);
-                }
-                __syncthreads();
-
-                // ---- tiles of 32 home points; warps split the words of the batch ----
-                for (int tile = 0; tile < n_tiles; tile++) {
-                    const int il = tile * TILE_POINTS + lane;
-                    const bool valid = il < unit.n_home;
-                    const size_t pi = static_cast<size_t>(unit.begin) + (valid ? il : 0);
-                    const int si0 = sorted.shift[3 * pi + 0];
-                    const int si1 = sorted.shift[3 * pi + 1];
-                    const int si2 = sorted.shift[3 * pi + 2];
-                    const int index_i = sorted.index[pi];
-                    const unsigned tag_i = static_cast<unsigned>(index_i) << 1;
-                    // lanes without a point carry NaN: every comparison fails
-                    const float nan = __int_as_float(0x7fc00000);
-                    const float xi = valid ? static_cast<float>(sorted.pos[3 * pi + 0] - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - centre[0]) : nan;
-                    const float yi = valid ? static_cast<float>(sorted.pos[3 * pi + 1] - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - centre[1]) : nan;
-                    const float zi = valid ? static_cast<float>(sorted.pos[3 * pi + 2] - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - centre[2]) : nan;
-
-                    uint32_t* mask_tile = masks + base + (static_cast<unsigned long long>(tile) * words + word_base + (batch0 >> 5)) * TILE_POINTS;
-                    unsigned row_hits = 0;
-                    for (int w = warp; w < batch_words; w += CTA_WARPS) {
-                        unsigned inside = 0; // surely inside the cutoff
-                        unsigned band = 0;   // too close to the cutoff for fp32
-                        const float4* candidates = stage + w * 32;
-#pragma unroll
-                        for (int b = 0; b < 32; b++) {
-                            const float4 cand = candidates[b]; // broadcast
-                            const float dx = cand.x - xi;
-                            const float dy = cand.y - yi;
-                            const float dz = cand.z - zi;
-                            const float d2 = dx * dx + dy * dy + dz * dz;
-                            const unsigned tag = __float_as_uint(cand.w);
-                            const bool keep = plan.full ? (tag != tag_i) : (tag > tag_i);
-                            if (keep && d2 <= plan.cutoff2_hi) {
-                                if (d2 < plan.cutoff2_lo) {
-                                    inside |= 1u << b;
-                                } else {
-                                    band |= 1u << b;
-                                }
-                            }
-                        }
-                        while (band != 0) {
-                            // the exact fp64 predicate of the reference decides
-                            const int b = __ffs(band) - 1;
-                            band &= band - 1;
-                            const int slot = batch0 + w * 32 + b;
-                            const int t = find_segment(table, slot);
-                            const size_t pj = static_cast<size_t>(table.start[t]) + (slot - table.slot0[t]);
-                            double vx, vy, vz;
-                            const double d2_exact = exact_pair(
-                                plan, sorted.pos[3 * pi + 0], sorted.pos[3 * pi + 1], sorted.pos[3 * pi + 2], sorted.pos[3 * pj + 0],
-                                sorted.pos[3 * pj + 1], sorted.pos[3 * pj + 2], table.q[0][t] + si0 - sorted.shift[3 * pj + 0],
-                                table.q[1][t] + si1 - sorted.shift[3 * pj + 1], table.q[2][t] + si2 - sorted.shift[3 * pj + 2], vx, vy, vz
-                            );
-                            if (d2_exact < plan.cutoff2) {
-                                inside |= 1u << b;
-                            }
-                        }
-                        mask_tile[w * TILE_POINTS + lane] = inside;
-                        row_hits += __popc(inside);
-                    }
-                    if (plan.by_index && row_hits != 0) {
-                        atomicAdd(&row_count[index_i], row_hits);
-                    }
-                    warp_hits += row_hits;
-                }
-                __syncthreads();
-            }
-            word_base += (group_total + 31) >> 5;
-        }
-
-#pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            warp_hits += __shfl_xor_sync(FULL_MASK, warp_hits, offset);
-        }
-        if (lane == 0 && warp_hits != 0) {
-            atomicAdd(&s_total, warp_hits);
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unit_count[u] = s_total;
-        }
-        __syncthreads();
-    }
-}
-
-// ---------------------------------------------------------------------------
-// emit pass
-// Replaces the append path of find_neighbors_cell_list
-// (vesin/src/cuda/cell_list.cu:643-703, one global counter) and
-// GrowableNeighborList (vesin/src/cpu_cell_list.cpp:465-632).
-//
-// Per (unit, batch, tile of 32 home points) the CTA expands the hit words into
-// a compact list of (home point, slot) in shared memory; warps then take 32
-// consecutive list entries at a time. Without `by_index` the output of a unit
-// is one contiguous block in list order, so every store instruction of a warp
-// covers one contiguous span (12- and 24-byte elements are transposed through
-// shared memory). With `by_index` (sorted output) every point owns a row at
-// the position given by the scan over original indices.
-// ---------------------------------------------------------------------------
-
-constexpr int EMIT_BATCH = 768;
-constexpr int EMIT_BATCH_WORDS = EMIT_BATCH / 32;
-constexpr int LIST_CAPACITY = 3072;
-constexpr int TASKS_PER_THREAD = (TILE_POINTS * EMIT_BATCH_WORDS + CTA_THREADS - 1) / CTA_THREADS;
-
-struct EmitShared {
-    SegmentTable table;
-    double x[EMIT_BATCH];
-    double y[EMIT_BATCH];
-    double z[EMIT_BATCH];
-    int j[EMIT_BATCH];
-    int s[3][EMIT_BATCH];                     // q - wrap shift of the candidate
-    double home_pos[3][TILE_POINTS];
-    int home_shift[3][TILE_POINTS];
-    int home_index[TILE_POINTS];
-    unsigned long long home_row[TILE_POINTS]; // by_index: where the row continues
-    int row_offset[TILE_POINTS + 1];          // list position where each home point starts
-    unsigned mask[EMIT_BATCH_WORDS * TILE_POINTS];
-    unsigned list[LIST_CAPACITY];             // (home point << 16) | slot
-    int shift_out[CTA_WARPS][96];             // per-warp transposition buffers
-    double vector_out[CTA_WARPS][96];
-};
-
-template <bool BY_INDEX>
-__global__ void __launch_bounds__(CTA_THREADS) emit_kernel(
-    const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, const uint32_t* __restrict__ masks,
-    const unsigned long long* __restrict__ unit_mask_base, const uint32_t* __restrict__ unit_words,
-    const unsigned long long* __restrict__ unit_start, const unsigned long long* __restrict__ row_start, uint32_t* __restrict__ row_fill,
-    PairOutput out
-) {
-    extern __shared__ __align__(16) unsigned char emit_smem[];
-    EmitShared& sh = *reinterpret_cast<EmitShared*>(emit_smem);
-
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-
-    for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
-        const Unit unit = unit_of(plan, cell_start, u);
-        if (unit.n_home == 0) {
-            continue;
-        }
-        const int n_groups = (unit.n_stencil + SEG_MAX - 1) / SEG_MAX;
-        const int n_tiles = (unit.n_home + TILE_POINTS - 1) / TILE_POINTS;
-        const unsigned long long base = unit_mask_base[u];
-        const int words = static_cast<int>(unit_words[u]);
-        unsigned long long cursor = BY_INDEX ? 0ull : unit_start[u]; // next free output element of the unit
-
-        int word_base = 0;
-        for (int g = 0; g < n_groups; g++) {
-            const int group_total = setup_segments(plan, cell_start, unit, g, sh.table);
-            for (int batch0 = 0; batch0 < group_total; batch0 += EMIT_BATCH) {
-                const int batch_slots = min(EMIT_BATCH, group_total - batch0);
-                const int batch_words = (batch_slots + 31) >> 5;
-
-                // ---- stage original positions, indices and shift parts ----
-                for (int t = warp; t < SEG_MAX; t += CTA_WARPS) {
-                    const int seg_slot0 = sh.table.slot0[t];
-                    const int seg_len = sh.table.slot0[t + 1] - seg_slot0;
-                    const int first = max(seg_slot0, batch0) - seg_slot0;
-                    const int last = min(seg_slot0 + seg_len, batch0 + batch_slots) - seg_slot0;
-                    if (first >= last) {
-                        continue;
-                    }
-                    const int q0 = sh.table.q[0][t], q1 = sh.table.q[1][t], q2 = sh.table.q[2][t];
-                    for (int o = first + lane; o < last; o += 32) {
-                        const size_t p = static_cast<size_t>(sh.table.start[t]) + o;
-                        const int s = seg_slot0 + o - batch0;
-                        sh.x[s] = sorted.pos[3 * p + 0];
-                        sh.y[s] = sorted.pos[3 * p + 1];
-                        sh.z[s] = sorted.pos[3 * p + 2];
-                        sh.j[s] = sorted.index[p];
-                        sh.s[0][s] = q0 - sorted.shift[3 * p + 0];
-                        sh.s[1][s] = q1 - sorted.shift[3 * p + 1];
-                        sh.s[2][s] = q2 - sorted.shift[3 * p + 2];
-                    }
-                }
-
-                for (int tile = 0; tile < n_tiles; tile++) {
-                    __syncthreads(); // staging done / previous tile done with the shared arrays
-                    // ---- the tile's home points and hit words ----
-                    if (threadIdx.x < TILE_POINTS) {
-                        const int il = tile * TILE_POINTS + threadIdx.x;
-                        if (il < unit.n_home) {
-                            const size_t pi = static_cast<size_t>(unit.begin) + il;
-                            const int index_i = sorted.index[pi];
-                            sh.home_index[threadIdx.x] = index_i;
-#pragma unroll
-                            for (int c = 0; c < 3; c++) {
-                                sh.home_pos[c][threadIdx.x] = sorted.pos[3 * pi + c];
-                                sh.home_shift[c][threadIdx.x] = sorted.shift[3 * pi + c];
-                            }
-                            if (BY_INDEX) {
-                                sh.home_row[threadIdx.x] = row_start[index_i] + row_fill[index_i];
-                            }
-                        }
-                    }
-                    const uint32_t* mask_tile = masks + base + (static_cast<unsigned long long>(tile) * words + word_base + (batch0 >> 5)) * TILE_POINTS;
-                    for (int k = threadIdx.x; k < batch_words * TILE_POINTS; k += CTA_THREADS) {
-                        sh.mask[k] = mask_tile[k];
-                    }
-                    __syncthreads();
-
-                    // ---- tasks = (home point, word), home point major; each thread
-                    //      owns TASKS_PER_THREAD consecutive tasks ----
-                    const int n_tasks = TILE_POINTS * batch_words;
-                    const int task0 = threadIdx.x * TASKS_PER_THREAD;
-                    unsigned task_word[TASKS_PER_THREAD];
-                    int my_hits = 0;
-#pragma unroll
-                    for (int k = 0; k < TASKS_PER_THREAD; k++) {
-                        const int task = task0 + k;
-                        unsigned word = 0;
-                        if (task < n_tasks) {
-                            word = sh.mask[(task % batch_words) * TILE_POINTS + (task / batch_words)];
-                        }
-                        task_word[k] = word;
-                        my_hits += __popc(word);
-                    }
-                    const int my_first = block_exclusive_scan(my_hits, sh.table.scan_tmp);
-                    const int total_hits = sh.table.scan_tmp[CTA_WARPS];
-                    {
-                        int position = my_first;
-#pragma unroll
-                        for (int k = 0; k < TASKS_PER_THREAD; k++) {
-                            const int task = task0 + k;
-                            if (task < n_tasks && task % batch_words == 0) {
-                                sh.row_offset[task / batch_words] = position;
-                            }
-                            position += __popc(task_word[k]);
-                        }
-                        if (threadIdx.x == 0) {
-                            sh.row_offset[TILE_POINTS] = total_hits;
-                        }
-                    }
-
-                    for (int round0 = 0; round0 < total_hits; round0 += LIST_CAPACITY) {
-                        __syncthreads(); // previous round consumed / row_offset visible
-                        {
-                            int position = my_first - round0;
-#pragma unroll
-                            for (int k = 0; k < TASKS_PER_THREAD; k++) {
-                                const int task = task0 + k;
-                                unsigned word = task_word[k];
-                                const unsigned code = (static_cast<unsigned>(task / batch_words) << 16) | (static_cast<unsigned>(task % batch_words) << 5);
-                                while (word != 0) {
-                                    const int b = __ffs(word) - 1;
-                                    word &= word - 1;
-                                    if (position >= 0 && position < LIST_CAPACITY) {
-                                        sh.list[position] = code | b;
-                                    }
-                                    position++;
-                                }
-                            }
-                        }
-                        __syncthreads();
-
-                        const int in_round = min(LIST_CAPACITY, total_hits - round0);
-                        for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
-                            const int n_valid = min(32, in_round - chunk0);
-                            const bool valid = lane < n_valid;
-                            double vx = 0, vy = 0, vz = 0;
-                            int s0 = 0, s1 = 0, s2 = 0;
-                            unsigned long long dest = 0;
-                            if (valid) {
-                                const unsigned entry = sh.list[chunk0 + lane];
-                                const int h = entry >> 16;
-                                const int slot = entry & 0xffff;
-                                s0 = sh.s[0][slot] + sh.home_shift[0][h];
-                                s1 = sh.s[1][slot] + sh.home_shift[1][h];
-                                s2 = sh.s[2][slot] + sh.home_shift[2][h];
-                                const double d2 = exact_pair(
-                                    plan, sh.home_pos[0][h], sh.home_pos[1][h], sh.home_pos[2][h], sh.x[slot], sh.y[slot], sh.z[slot], s0, s1, s2, vx,
-                                    vy, vz
-                                );
-                                if (BY_INDEX) {
-                                    dest = sh.home_row[h] + (round0 + chunk0 + lane - sh.row_offset[h]);
-                                } else {
-                                    dest = cursor + round0 + chunk0 + lane;
-                                }
-                                reinterpret_cast<ulonglong2*>(out.pairs)[dest] = make_ulonglong2(
-                                    static_cast<unsigned long long>(sh.home_index[h]), static_cast<unsigned long long>(sh.j[slot])
-                                );
-                                if (out.distances != nullptr) {
-                                    if (out.values_float) {
-                                        reinterpret_cast<float*>(out.distances)[dest] = static_cast<float>(__dsqrt_rn(d2));
-                                    } else {
-                                        out.distances[dest] = __dsqrt_rn(d2);
-                                    }
-                                }
-                            }
-                            if (BY_INDEX) {
-                                if (valid && out.shifts != nullptr) {
-                                    out.shifts[3 * dest + 0] = s0;
-                                    out.shifts[3 * dest + 1] = s1;
-                                    out.shifts[3 * dest + 2] = s2;
-                                }
-                                if (valid && out.vectors != nullptr) {
-                                    if (out.values_float) {
-                                        float* vectors = reinterpret_cast<float*>(out.vectors);
-                                        vectors[3 * dest + 0] = static_cast<float>(vx);
-                                        vectors[3 * dest + 1] = static_cast<float>(vy);
-                                        vectors[3 * dest + 2] = static_cast<float>(vz);
-                                    } else {
-                                        out.vectors[3 * dest + 0] = vx;
-                                        out.vectors[3 * dest + 1] = vy;
-                                        out.vectors[3 * dest + 2] = vz;
-                                    }
-                                }
-                            } else {
-                                const unsigned long long first = cursor + round0 + chunk0;
-                                if (out.shifts != nullptr) {
-                                    int* buffer = sh.shift_out[warp];
-                                    buffer[3 * lane + 0] = s0;
-                                    buffer[3 * lane + 1] = s1;
-                                    buffer[3 * lane + 2] = s2;
-                                    __syncwarp();
-                                    int32_t* dst = out.shifts + 3 * first;
-#pragma unroll
-                                    for (int k = 0; k < 3; k++) {
-                                        const int w = k * 32 + lane;
-                                        if (w < 3 * n_valid) {
-                                            dst[w] = buffer[w];
-                                        }
-                                    }
-                                }
-                                if (out.vectors != nullptr) {
-                                    double* buffer = sh.vector_out[warp];
-                                    buffer[3 * lane + 0] = vx;
-                                    buffer[3 * lane + 1] = vy;
-                                    buffer[3 * lane + 2] = vz;
-                                    __syncwarp();
-                                    double* dst = out.vectors + 3 * first;
-#pragma unroll
-                                    for (int k = 0; k < 3; k++) {
-                                        const int w = k * 32 + lane;
-                                        if (w < 3 * n_valid) {
-                                            dst[w] = buffer[w];
-                                        }
-                                    }
-                                }
-                                __syncwarp();
-                            }
-                        }
-                    }
-                    if (BY_INDEX) {
-                        __syncthreads();
-                        if (threadIdx.x < TILE_POINTS && tile * TILE_POINTS + threadIdx.x < unit.n_home) {
-                            const int hits = sh.row_offset[threadIdx.x + 1] - sh.row_offset[threadIdx.x];
-                            if (hits != 0) {
-                                row_fill[sh.home_index[threadIdx.x]] += static_cast<uint32_t>(hits);
-                            }
-                        }
-                    } else {
-                        cursor += total_hits;
-                    }
-                }
-                __syncthreads();
-            }
-            word_base += (group_total + 31) >> 5;
-        }
-    }
-}
-
 // ---------------------------------------------------------------------------
 // fused pass (unsorted lists): decide and emit in one traversal
 //
@@ -1557,6 +1072,7 @@ struct FusedShared {
     int stencil_cached;          // are the packed offsets below usable?
     int stencil_offset[SEG_MAX]; // first SEG_MAX entries of the stencil of a full-length unit, 10 bits per direction
     int next_run[2];  // run of units this CTA takes next (two slots: one is read while the other is written)
+    int slab_mode;    // slab decomposition: bit 0 = the unit's points are owned, bit 1 = so are all candidates of the group
 };
 static_assert(
     offsetof(FusedShared, near_x) % 16 == 0 && offsetof(FusedShared, near_y) % 16 == 0 && offsetof(FusedShared, near_z) % 16 == 0 &&
@@ -1806,12 +1322,20 @@ __device__ __forceinline__ void store_pairs(
 /// of distances at once, and the 24 + 48 bytes of shifts and vectors leave as
 /// 8- and 16-byte pieces of one contiguous span after a pass through shared
 /// memory.
+///
+/// A claim that starts on an odd element (slab-decomposed lists, where some
+/// blocks hold one orientation only) is written one element further on, which
+/// is even again; the reversed pair of its LAST hit then does not fit behind
+/// the block and goes to the block's first element instead. `tail_lane` is the
+/// lane that holds that hit in this chunk (-1: none), `tail_to` the element.
 __device__ __forceinline__ void store_both(
     FusedShared& sh, const PairOutput& out, int warp, int lane, unsigned long long first, int n_valid, unsigned long long a,
-    unsigned long long b, int s0, int s1, int s2, double d, double vx, double vy, double vz
+    unsigned long long b, int s0, int s1, int s2, double d, double vx, double vy, double vz, int tail_lane = -1,
+    unsigned long long tail_to = 0
 ) {
     const unsigned long long mine = first + 2 * lane;
-    if (lane < n_valid) {
+    const bool is_tail = lane == tail_lane;
+    if (lane < n_valid && !is_tail) {
         unsigned long long* dst = out.pairs + 2 * mine;
         asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(dst), "l"(a), "l"(b), "l"(b), "l"(a) : "memory");
         if (out.distances != nullptr) {
@@ -1823,7 +1347,41 @@ __device__ __forceinline__ void store_both(
             }
         }
     }
-    const bool whole = n_valid == 32; // the usual case: no bounds to check on the way out
+    if (is_tail) {
+        // forward pair in place, reversed pair at the head of the block, element by element
+        reinterpret_cast<ulonglong2*>(out.pairs)[mine] = make_ulonglong2(a, b);
+        reinterpret_cast<ulonglong2*>(out.pairs)[tail_to] = make_ulonglong2(b, a);
+        if (out.distances != nullptr) {
+            if (out.values_float) {
+                reinterpret_cast<float*>(out.distances)[mine] = static_cast<float>(d);
+                reinterpret_cast<float*>(out.distances)[tail_to] = static_cast<float>(d);
+            } else {
+                out.distances[mine] = d;
+                out.distances[tail_to] = d;
+            }
+        }
+        if (out.shifts != nullptr) {
+            out.shifts[3 * tail_to + 0] = -s0;
+            out.shifts[3 * tail_to + 1] = -s1;
+            out.shifts[3 * tail_to + 2] = -s2;
+        }
+        if (out.vectors != nullptr) {
+            if (out.values_float) {
+                float* vectors = reinterpret_cast<float*>(out.vectors);
+                vectors[3 * tail_to + 0] = -static_cast<float>(vx);
+                vectors[3 * tail_to + 1] = -static_cast<float>(vy);
+                vectors[3 * tail_to + 2] = -static_cast<float>(vz);
+            } else {
+                out.vectors[3 * tail_to + 0] = -vx;
+                out.vectors[3 * tail_to + 1] = -vy;
+                out.vectors[3 * tail_to + 2] = -vz;
+            }
+        }
+    }
+    const bool whole = n_valid == 32 && tail_lane < 0; // the usual case: no bounds to check on the way out
+    // pieces of the transposed buffers: 3 per lane; of the tail lane's, the second is half
+    // forward pair (its first word is written alone) and the third is not written at all
+    const int tail_half = (tail_lane >= 0) ? 3 * tail_lane + 1 : -1;
     if (out.shifts != nullptr) {
         int2* buffer = reinterpret_cast<int2*>(sh.transpose[warp]);
         buffer[3 * lane + 0] = make_int2(s0, s1);
@@ -1838,8 +1396,11 @@ __device__ __forceinline__ void store_both(
         } else {
 #pragma unroll
             for (int k = 0; k < 3; k++) {
-                if (k * 32 + lane < 3 * n_valid) {
-                    dst[k * 32] = buffer[k * 32 + lane];
+                const int piece = k * 32 + lane;
+                if (piece < 3 * n_valid && (tail_half < 0 || piece < tail_half)) {
+                    dst[k * 32] = buffer[piece];
+                } else if (piece == tail_half) {
+                    reinterpret_cast<int*>(dst + k * 32)[0] = buffer[piece].x;
                 }
             }
         }
@@ -1862,8 +1423,11 @@ __device__ __forceinline__ void store_both(
         } else {
 #pragma unroll
             for (int k = 0; k < 3; k++) {
-                if (k * 32 + lane < 3 * n_valid) {
-                    dst[k * 32] = buffer[k * 32 + lane];
+                const int piece = k * 32 + lane;
+                if (piece < 3 * n_valid && (tail_half < 0 || piece < tail_half)) {
+                    dst[k * 32] = buffer[piece];
+                } else if (piece == tail_half) {
+                    reinterpret_cast<float*>(dst + k * 32)[0] = buffer[piece].x;
                 }
             }
         }
@@ -1882,8 +1446,11 @@ __device__ __forceinline__ void store_both(
         } else {
 #pragma unroll
             for (int k = 0; k < 3; k++) {
-                if (k * 32 + lane < 3 * n_valid) {
-                    dst[k * 32] = buffer[k * 32 + lane];
+                const int piece = k * 32 + lane;
+                if (piece < 3 * n_valid && (tail_half < 0 || piece < tail_half)) {
+                    dst[k * 32] = buffer[piece];
+                } else if (piece == tail_half) {
+                    reinterpret_cast<double*>(dst + k * 32)[0] = buffer[piece].x;
                 }
             }
         }
@@ -1891,10 +1458,15 @@ __device__ __forceinline__ void store_both(
     }
 }
 
+/// Units a launch of the fused pass covers: [begin0, end0) and [begin1, end1).
+struct UnitRanges {
+    int begin0, end0, begin1, end1;
+};
+
 template <bool FULL, bool SLAB>
 __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, const int UNIT_RUN
+    DeviceHeader* header, const int UNIT_RUN, const UnitRanges ranges, unsigned long long* run_cursor
 ) {
     extern __shared__ __align__(16) unsigned char fused_smem[];
     FusedShared& sh = *reinterpret_cast<FusedShared*>(fused_smem);
@@ -1925,17 +1497,20 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     // UNIT_RUN neighbouring units so that most of its loads hit in L1.
     // Runs are handed out dynamically (the first one is the block index): the run after
     // the current one is fetched while the current one is processed.
-    const int n_runs = (plan.n_units + UNIT_RUN - 1) / UNIT_RUN;
+    // (the launch covers one or two ranges of units; a run lies inside one range)
+    const int n_runs0 = (ranges.end0 - ranges.begin0 + UNIT_RUN - 1) / UNIT_RUN;
+    const int n_runs = n_runs0 + (ranges.end1 - ranges.begin1 + UNIT_RUN - 1) / UNIT_RUN;
     int run = blockIdx.x;
     int run_parity = 0;
     while (run < n_runs) {
     if (threadIdx.x == 0) {
-        sh.next_run[run_parity] = static_cast<int>(gridDim.x + atomicAdd(&header->run_cursor, 1ull));
+        sh.next_run[run_parity] = static_cast<int>(gridDim.x + atomicAdd(run_cursor, 1ull));
     }
-    const int run_end = min(plan.n_units, (run + 1) * UNIT_RUN);
-    Unit unit = unit_of(plan, cell_start, run * UNIT_RUN);
-    for (int u = run * UNIT_RUN; u < run_end; u++) {
-        if (u != run * UNIT_RUN) {
+    const int run_first = (run < n_runs0) ? ranges.begin0 + run * UNIT_RUN : ranges.begin1 + (run - n_runs0) * UNIT_RUN;
+    const int run_end = min((run < n_runs0) ? ranges.end0 : ranges.end1, run_first + UNIT_RUN);
+    Unit unit = unit_of(plan, cell_start, run_first);
+    for (int u = run_first; u < run_end; u++) {
+        if (u != run_first) {
             next_unit(plan, cell_start, unit);
         }
         if (unit.n_home == 0) {
@@ -1958,16 +1533,17 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
         // upper halo layer sees nothing above it. Half lists: every unordered
         // pair is evaluated on exactly one rank with an owned home point, and
         // that rank writes it.
-        bool home_owned = true;
         if (SLAB) {
             const int layer = (plan.window_axis == 0) ? unit.c0 : ((plan.window_axis == 1) ? unit.c1 : unit.c2);
             const int last = plan.n_cells[plan.window_axis] - 1;
             if (layer == last) {
                 continue;
             }
-            home_owned = layer >= 1;
-            if (!FULL && !home_owned) {
+            if (!FULL && layer < 1) {
                 continue;
+            }
+            if (threadIdx.x == 0) {
+                sh.slab_mode = (layer >= 1) ? 1 : 0; // read after the barriers of the segment setup
             }
         }
 
@@ -1984,24 +1560,39 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
             int home_row_slots;
             const int group_total = setup_half_segments(plan, cell_start, unit, g, sh, home_row_slots);
             PHASE_MARK(1); // segments
-            bool all_owned = true;
             if (SLAB) {
                 int segment_ok = 1;
                 if (threadIdx.x < SEG_MAX) {
                     const int length = sh.table.slot0[threadIdx.x + 1] - sh.table.slot0[threadIdx.x];
                     segment_ok = (length == 0) || sh.table.self_ok[threadIdx.x];
                 }
-                all_owned = __syncthreads_and(segment_ok) && home_owned;
+                const int all_candidates_owned = __syncthreads_and(segment_ok);
+                if (threadIdx.x == 0) {
+                    sh.slab_mode = (sh.slab_mode & 1) | ((all_candidates_owned && (sh.slab_mode & 1)) ? 2 : 0);
+                }
+                // visible after the barrier that ends the staging of the first batch
             }
             for (int batch0 = 0; batch0 < group_total; batch0 += FUSED_BATCH) {
                 const int batch_slots = min(FUSED_BATCH, group_total - batch0);
                 const int batch_words = (batch_slots + 31) >> 5;
 
-                if (SLAB) {
+                if (SLAB && FULL) {
+                    // which slots of the batch hold owned points: every owned segment marks its range
                     if (threadIdx.x < FUSED_WORDS) {
                         sh.owned_word[threadIdx.x] = 0;
                     }
                     __syncthreads();
+                    if (threadIdx.x < SEG_MAX && sh.table.self_ok[threadIdx.x]) {
+                        const int a = max(sh.table.slot0[threadIdx.x], batch0) - batch0;
+                        const int b = min(sh.table.slot0[threadIdx.x + 1], batch0 + batch_slots) - batch0;
+                        for (int w = a >> 5; a < b && w <= ((b - 1) >> 5); w++) {
+                            const int lo = max(a, 32 * w) - 32 * w;
+                            const int hi = min(b, 32 * w + 32) - 32 * w;
+                            const unsigned mask = (hi - lo == 32) ? 0xffffffffu : (((1u << (hi - lo)) - 1u) << lo);
+                            atomicOr(&sh.owned_word[w], mask);
+                        }
+                    }
+                    // read after the barriers of the first tile
                 }
                 // ---- stage the candidates: one slot per thread (the segment of a slot is
                 //      found by bisection), so all loads of a batch are in flight at once ----
@@ -2018,9 +1609,6 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     sh.x[s] = px;
                     sh.y[s] = py;
                     sh.z[s] = pz;
-                    if (SLAB && sh.table.self_ok[t]) {
-                        atomicOr(&sh.owned_word[s >> 5], 1u << (s & 31));
-                    }
                     sh.sj[s] = make_int4(r0, r1, r2, sorted.index[p]);
                     // image of the candidate seen from this unit (most candidates of a large box have none)
                     double ix = px;
@@ -2130,18 +1718,15 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     // order. One pass writes both orientations (full) or the kept one
                     // (half); a unit of a slab-decomposed full list that touches halo
                     // points takes two passes, forward pairs then reversed pairs ----
-                    const int n_passes = (SLAB && FULL && !all_owned) ? 2 : 1;
+                    // (split: the unit or some of its candidates are halo points)
+                    const bool split = SLAB && FULL && (sh.slab_mode & 2) == 0;
+                    const int n_passes = split ? 2 : 1;
                     for (int pass = 0; pass < n_passes; pass++) {
-                        bool write_forward = true;
-                        bool write_reverse = FULL;
-                        bool only_owned_candidates = false;
-                        if (SLAB && FULL && !all_owned) {
-                            write_forward = (pass == 0);
-                            write_reverse = (pass == 1);
-                            only_owned_candidates = (pass == 1);
-                            if (pass == 0 && !home_owned) {
-                                continue;
-                            }
+                        const bool write_forward = !split || pass == 0;
+                        const bool write_reverse = FULL && (!split || pass == 1);
+                        const bool only_owned_candidates = split && pass == 1;
+                        if (split && pass == 0 && (sh.slab_mode & 1) == 0) {
+                            continue; // a unit of halo points: only the reversed pairs belong to this rank
                         }
                         if (pass != 0) {
                             __syncthreads(); // list, claim and scan scratch of the first pass are free again
@@ -2276,7 +1861,10 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                             }
 
                             // both orientations side by side when the claim and the arrays allow it
-                            const bool interleave = FULL && write_forward && write_reverse && out.interleave_ok && (claim & 1ull) == 0;
+                            // (a claim on an odd element is moved on by one, see store_both; plain full
+                            // lists only ever claim even blocks)
+                            const bool interleave = FULL && write_forward && write_reverse && out.interleave_ok && (SLAB || (claim & 1ull) == 0);
+                            const unsigned long long moved_on = SLAB ? (claim & 1ull) : 0ull;
                             for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
                                 const int n_valid = min(32, in_round - chunk0);
                                 double vx = 0, vy = 0, vz = 0, d = 0;
@@ -2309,8 +1897,13 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                 unsigned long long index_i = static_cast<unsigned long long>(home.w);
                                 unsigned long long index_j = static_cast<unsigned long long>(cand.w);
                                 if (interleave) {
+                                    int tail_lane = -1;
+                                    if (SLAB && moved_on != 0 && round0 + chunk0 + n_valid == total_hits) {
+                                        tail_lane = n_valid - 1; // the last hit of the block is in this chunk
+                                    }
                                     store_both(
-                                        sh, out, warp, lane, claim + 2ull * (round0 + chunk0), n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz
+                                        sh, out, warp, lane, claim + moved_on + 2ull * (round0 + chunk0), n_valid, index_i, index_j, s0, s1, s2, d,
+                                        vx, vy, vz, tail_lane, claim
                                     );
                                     continue;
                                 }
@@ -2354,6 +1947,552 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     __syncthreads(); // next_run is visible; nobody reads the other slot any more
     run = sh.next_run[run_parity];
     run_parity ^= 1;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// sorted lists: one row per point, rows in index order
+// Replaces find_neighbors_cell_list + sort_pairs (vesin/src/vesin_cuda.cpp:188-291,
+// vesin/src/cuda/sort_pairs.cu:63-202: a bitonic network over all pairs in
+// global memory) and GrowableNeighborList::sort (vesin/src/cpu_cell_list.cpp:634-730).
+//
+// A row can only be written by one CTA if that CTA sees every pair of the
+// point, so the two passes walk the FULL stencil of a unit (every pair of a
+// full list is decided twice, once from each end). Pass 1 decides with the
+// machinery of the fused pass (packed fp32 screen, exact fp64 band) and leaves
+// one hit word per (point, 32 candidates) in global memory plus the number of
+// pairs of every point; a scan turns the counts into row starts; pass 2 walks
+// the hit words, so both passes agree by construction, and writes every row
+// in the order the candidates were staged.
+// ---------------------------------------------------------------------------
+
+struct RowShared {
+    FusedShared staged;
+    unsigned long long home_row[TILE_POINTS]; // where the row of a home point continues
+    int row_offset[TILE_POINTS + 1];          // list position where the hits of each home point start
+    unsigned long long mask_base;
+};
+
+/// Does the pair (home point, candidate) belong to the list, as far as indices
+/// and shifts decide? Full lists: everything but the point itself. Half lists:
+/// the rule of the reference (vesin/src/cpu_cell_list.cpp:101-133).
+template <bool FULL>
+__device__ __forceinline__ bool row_keeps(const int4& home, const int4& candidate) {
+    const int s0 = candidate.x + home.x;
+    const int s1 = candidate.y + home.y;
+    const int s2 = candidate.z + home.z;
+    if (candidate.w != home.w) {
+        return FULL || candidate.w > home.w;
+    }
+    if ((s0 | s1 | s2) == 0) {
+        return false; // the point itself
+    }
+    return FULL || half_rule(s0, s1, s2);
+}
+
+/// Words of hit bits one home point of the unit needs: every segment group
+/// starts on a fresh word. Leaves the table of the LAST group in place.
+__device__ __forceinline__ int row_words_of_unit(
+    const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int n_groups, SegmentTable& table, int& last_total
+) {
+    int words = 0;
+    for (int g = 0; g < n_groups; g++) {
+        last_total = setup_segments(plan, cell_start, unit, g, table);
+        words += (last_total + 31) >> 5;
+    }
+    return words;
+}
+
+/// Stage `batch_slots` candidates starting at slot `batch0` of the current
+/// segment group: original positions and (shift part, index) for the exact
+/// arithmetic and the output, and, with NEAR, fp32 coordinates relative to the
+/// unit centre for the screen.
+template <bool NEAR>
+__device__ __forceinline__ void stage_row_batch(
+    FusedShared& sh, const GridPlan& plan, const SortedPoints& sorted, int n_stencil, int batch0, int batch_slots
+) {
+    for (int s = threadIdx.x; s < batch_slots; s += CTA_THREADS) {
+        const int slot = batch0 + s;
+        const int t = (n_stencil <= 32) ? find_segment<5>(sh.table, slot) : find_segment<7>(sh.table, slot);
+        const size_t p = static_cast<size_t>(sh.table.start[t]) + (slot - sh.table.slot0[t]);
+        const double px = sorted.pos[3 * p + 0];
+        const double py = sorted.pos[3 * p + 1];
+        const double pz = sorted.pos[3 * p + 2];
+        const int r0 = sh.table.q[0][t] - sorted.shift[3 * p + 0];
+        const int r1 = sh.table.q[1][t] - sorted.shift[3 * p + 1];
+        const int r2 = sh.table.q[2][t] - sorted.shift[3 * p + 2];
+        sh.x[s] = px;
+        sh.y[s] = py;
+        sh.z[s] = pz;
+        sh.sj[s] = make_int4(r0, r1, r2, sorted.index[p]);
+        if (NEAR) {
+            double ix = px;
+            double iy = py;
+            double iz = pz;
+            if ((r0 | r1 | r2) != 0) {
+                ix += r0 * plan.H[0][0] + r1 * plan.H[1][0] + r2 * plan.H[2][0];
+                iy += r0 * plan.H[0][1] + r1 * plan.H[1][1] + r2 * plan.H[2][1];
+                iz += r0 * plan.H[0][2] + r1 * plan.H[1][2] + r2 * plan.H[2][2];
+            }
+            const float fx = static_cast<float>(ix - sh.centre[0]);
+            const float fy = static_cast<float>(iy - sh.centre[1]);
+            const float fz = static_cast<float>(iz - sh.centre[2]);
+            sh.near_x[s] = fx;
+            sh.near_y[s] = fy;
+            sh.near_z[s] = fz;
+            sh.near_n[s] = fx * fx + fy * fy + fz * fz;
+        }
+    }
+    if (NEAR) {
+        const int batch_words = (batch_slots + 31) >> 5;
+        for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
+            sh.near_x[s] = 0.0f;
+            sh.near_y[s] = 0.0f;
+            sh.near_z[s] = 0.0f;
+            sh.near_n[s] = __int_as_float(0x7f800000); // never a hit
+        }
+    }
+}
+
+template <bool FULL>
+__global__ void __launch_bounds__(CTA_THREADS, 4) row_count_kernel(
+    const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, uint32_t* __restrict__ masks,
+    unsigned long long mask_capacity, unsigned long long* __restrict__ unit_mask_base, uint32_t* __restrict__ unit_words,
+    uint32_t* __restrict__ row_count, DeviceHeader* header
+) {
+    extern __shared__ __align__(16) unsigned char row_smem[];
+    RowShared& rows = *reinterpret_cast<RowShared*>(row_smem);
+    FusedShared& sh = rows.staged;
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const float cutoff2_lo = plan.cutoff2_lo;
+    const float cutoff2_hi = plan.cutoff2_hi;
+    if (header->status & STATUS_ABORT_MASK) {
+        return;
+    }
+
+    for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
+        const Unit unit = unit_of(plan, cell_start, u);
+        if (unit.n_home == 0) {
+            continue;
+        }
+        const int n_groups = (unit.n_stencil + SEG_MAX - 1) / SEG_MAX;
+        const int n_tiles = (unit.n_home + TILE_POINTS - 1) / TILE_POINTS;
+        if (threadIdx.x < 3) {
+            const int c = threadIdx.x;
+            sh.centre[c] = plan.origin[c] + (unit.c0 + 0.5 * unit.cells) * plan.cell_vec[0][c] + (unit.c1 + 0.5) * plan.cell_vec[1][c] +
+                           (unit.c2 + 0.5) * plan.cell_vec[2][c];
+        }
+
+        int group_total = 0;
+        const int words = row_words_of_unit(plan, cell_start, unit, n_groups, sh.table, group_total);
+        // claim the storage of the hit words: n_tiles blocks of `words` x 32 lanes
+        if (threadIdx.x == 0) {
+            const unsigned long long need = static_cast<unsigned long long>(n_tiles) * words * TILE_POINTS;
+            unsigned long long base = atomicAdd(&header->mask_cursor, need);
+            if (base + need > mask_capacity) {
+                atomicOr(&header->status, STATUS_MASK_OVERFLOW);
+                base = ~0ull;
+            } else {
+                unit_mask_base[u] = base;
+                unit_words[u] = static_cast<uint32_t>(words);
+            }
+            rows.mask_base = base;
+        }
+        __syncthreads();
+        const unsigned long long base = rows.mask_base;
+        if (base == ~0ull) {
+            __syncthreads();
+            continue; // the host grows the storage and runs the pass again
+        }
+
+        int word_base = 0;
+        for (int g = 0; g < n_groups; g++) {
+            if (n_groups > 1) {
+                group_total = setup_segments(plan, cell_start, unit, g, sh.table);
+            }
+            for (int batch0 = 0; batch0 < group_total; batch0 += FUSED_BATCH) {
+                const int batch_slots = min(FUSED_BATCH, group_total - batch0);
+                const int batch_words = (batch_slots + 31) >> 5;
+                stage_row_batch<true>(sh, plan, sorted, unit.n_stencil, batch0, batch_slots);
+
+                for (int tile = 0; tile < n_tiles; tile++) {
+                    __syncthreads(); // staging done; previous tile done with the hit words and the home points
+                    const int il = tile * TILE_POINTS + lane;
+                    const bool valid = il < unit.n_home;
+                    const size_t pi = static_cast<size_t>(unit.begin) + (valid ? il : 0);
+                    const double rix = sorted.pos[3 * pi + 0];
+                    const double riy = sorted.pos[3 * pi + 1];
+                    const double riz = sorted.pos[3 * pi + 2];
+                    const int si0 = sorted.shift[3 * pi + 0];
+                    const int si1 = sorted.shift[3 * pi + 1];
+                    const int si2 = sorted.shift[3 * pi + 2];
+                    // lanes without a point carry NaN: every comparison fails
+                    const float nan = __int_as_float(0x7fc00000);
+                    const float xi = valid ? static_cast<float>(rix - (si0 * plan.H[0][0] + si1 * plan.H[1][0] + si2 * plan.H[2][0]) - sh.centre[0]) : nan;
+                    const float yi = valid ? static_cast<float>(riy - (si0 * plan.H[0][1] + si1 * plan.H[1][1] + si2 * plan.H[2][1]) - sh.centre[1]) : nan;
+                    const float zi = valid ? static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - sh.centre[2]) : nan;
+                    const float an = xi * xi + yi * yi + zi * zi;
+                    if (warp == 0) {
+                        sh.home_sj[lane] = make_int4(si0, si1, si2, sorted.index[pi]);
+                    }
+                    const float ax = -2.0f * xi;
+                    const float ay = -2.0f * yi;
+                    const float az = -2.0f * zi;
+                    const unsigned long long ax2 = pack_f32x2(ax, ax);
+                    const unsigned long long ay2 = pack_f32x2(ay, ay);
+                    const unsigned long long az2 = pack_f32x2(az, az);
+                    const unsigned long long an2 = pack_f32x2(an, an);
+                    // (no half shell here: home_row_slots = 0 keeps every candidate)
+                    if (batch_words <= CTA_WARPS) {
+                        if (warp < batch_words) {
+                            sh.mask[warp * TILE_POINTS + lane] =
+                                decide_piece<32>(sh, plan, warp, 0, batch0, 0, il, ax2, ay2, az2, an2, cutoff2_lo, cutoff2_hi, rix, riy, riz, si0, si1, si2);
+                        }
+                    } else {
+                        unsigned short* halves = reinterpret_cast<unsigned short*>(sh.mask);
+                        for (int piece = warp; piece < 2 * batch_words; piece += CTA_WARPS) {
+                            const int half = (piece >= batch_words) ? 1 : 0;
+                            const int w = piece - half * batch_words;
+                            halves[2 * (w * TILE_POINTS + lane) + half] = static_cast<unsigned short>(decide_piece<16>(
+                                sh, plan, w, 16 * half, batch0, 0, il, ax2, ay2, az2, an2, cutoff2_lo, cutoff2_hi, rix, riy, riz, si0, si1, si2
+                            ));
+                        }
+                    }
+                    __syncthreads();
+                    // ---- indices and shifts have their say on the hits; the words go to global
+                    //      memory as [tile][word][lane], the counts to the rows ----
+                    uint32_t* mask_tile = masks + base + (static_cast<unsigned long long>(tile) * words + word_base + (batch0 >> 5)) * TILE_POINTS;
+                    for (int task = threadIdx.x; task < batch_words * TILE_POINTS; task += CTA_THREADS) {
+                        const int4 home = sh.home_sj[task & 31];
+                        unsigned word = sh.mask[task];
+                        unsigned kept = 0;
+                        const int slot0 = (task >> 5) << 5;
+                        while (word != 0) {
+                            const int b = __ffs(word) - 1;
+                            word &= word - 1;
+                            if (row_keeps<FULL>(home, sh.sj[slot0 + b])) {
+                                kept |= 1u << b;
+                            }
+                        }
+                        mask_tile[task] = kept;
+                        if (kept != 0) {
+                            atomicAdd(&row_count[home.w], static_cast<uint32_t>(__popc(kept)));
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+            word_base += (group_total + 31) >> 5;
+        }
+    }
+}
+
+/// 12-byte element at a 4-byte aligned address: one 8-byte and one 4-byte store.
+template <typename T>
+__device__ __forceinline__ void store_triple_32(T* base, unsigned long long element, T a, T b, T c) {
+    static_assert(sizeof(T) == 4, "int32 shifts or float vectors");
+    T* dst = base + 3 * element;
+    struct alignas(8) Two {
+        T x, y;
+    };
+    if ((element & 1ull) == 0) {
+        *reinterpret_cast<Two*>(dst) = Two{a, b};
+        dst[2] = c;
+    } else {
+        dst[0] = a;
+        *reinterpret_cast<Two*>(dst + 1) = Two{b, c};
+    }
+}
+
+/// 24-byte element at an 8-byte aligned address: one 16-byte and one 8-byte store.
+__device__ __forceinline__ void store_triple_64(double* base, unsigned long long element, double a, double b, double c) {
+    double* dst = base + 3 * element;
+    if ((element & 1ull) == 0) {
+        *reinterpret_cast<double2*>(dst) = make_double2(a, b);
+        dst[2] = c;
+    } else {
+        dst[0] = a;
+        *reinterpret_cast<double2*>(dst + 1) = make_double2(b, c);
+    }
+}
+
+__global__ void __launch_bounds__(CTA_THREADS, 4) row_emit_kernel(
+    const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, const uint32_t* __restrict__ masks,
+    const unsigned long long* __restrict__ unit_mask_base, const uint32_t* __restrict__ unit_words,
+    const unsigned long long* __restrict__ row_start, uint32_t* __restrict__ row_fill, PairOutput out
+) {
+    extern __shared__ __align__(16) unsigned char row_smem[];
+    RowShared& rows = *reinterpret_cast<RowShared*>(row_smem);
+    FusedShared& sh = rows.staged;
+    static_assert(FUSED_WORDS == 16 && FUSED_TASKS == 2, "tasks are (home point, word) pairs: home = task >> 4");
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+
+    for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
+        const Unit unit = unit_of(plan, cell_start, u);
+        if (unit.n_home == 0) {
+            continue;
+        }
+        const int n_groups = (unit.n_stencil + SEG_MAX - 1) / SEG_MAX;
+        const int n_tiles = (unit.n_home + TILE_POINTS - 1) / TILE_POINTS;
+        const unsigned long long base = unit_mask_base[u];
+        const int words = static_cast<int>(unit_words[u]);
+
+        int word_base = 0;
+        for (int g = 0; g < n_groups; g++) {
+            const int group_total = setup_segments(plan, cell_start, unit, g, sh.table);
+            for (int batch0 = 0; batch0 < group_total; batch0 += FUSED_BATCH) {
+                const int batch_slots = min(FUSED_BATCH, group_total - batch0);
+                const int batch_words = (batch_slots + 31) >> 5;
+                stage_row_batch<false>(sh, plan, sorted, unit.n_stencil, batch0, batch_slots);
+
+                for (int tile = 0; tile < n_tiles; tile++) {
+                    __syncthreads(); // staging done; previous tile done with the shared arrays
+                    if (threadIdx.x < TILE_POINTS) {
+                        const int il = tile * TILE_POINTS + threadIdx.x;
+                        if (il < unit.n_home) {
+                            const size_t pi = static_cast<size_t>(unit.begin) + il;
+                            const int index_i = sorted.index[pi];
+                            sh.home_pos[0][threadIdx.x] = sorted.pos[3 * pi + 0];
+                            sh.home_pos[1][threadIdx.x] = sorted.pos[3 * pi + 1];
+                            sh.home_pos[2][threadIdx.x] = sorted.pos[3 * pi + 2];
+                            sh.home_sj[threadIdx.x] = make_int4(sorted.shift[3 * pi + 0], sorted.shift[3 * pi + 1], sorted.shift[3 * pi + 2], index_i);
+                            rows.home_row[threadIdx.x] = row_start[index_i] + row_fill[index_i];
+                        }
+                    }
+                    // hit words of the tile, transposed to [home point][word] so that the hits of a
+                    // point are consecutive tasks; words past the batch hold nothing
+                    const uint32_t* mask_tile = masks + base + (static_cast<unsigned long long>(tile) * words + word_base + (batch0 >> 5)) * TILE_POINTS;
+                    for (int k = threadIdx.x; k < FUSED_WORDS * TILE_POINTS; k += CTA_THREADS) {
+                        const int w = k >> 5;
+                        sh.mask[(k & 31) * FUSED_WORDS + w] = (w < batch_words) ? mask_tile[k] : 0u;
+                    }
+                    __syncthreads();
+
+                    // ---- scan of the hit counts of the tasks (two consecutive tasks per thread) ----
+                    const unsigned word_a = sh.mask[2 * threadIdx.x];
+                    const unsigned word_b = sh.mask[2 * threadIdx.x + 1];
+                    const int my_hits = __popc(word_a) + __popc(word_b);
+                    int inclusive = my_hits;
+#pragma unroll
+                    for (int offset = 1; offset < 32; offset <<= 1) {
+                        const int up = __shfl_up_sync(FULL_MASK, inclusive, offset);
+                        if (lane >= offset) {
+                            inclusive += up;
+                        }
+                    }
+                    sh.prefix[threadIdx.x] = static_cast<unsigned short>(inclusive - my_hits);
+                    if (lane == 31) {
+                        sh.table.scan_tmp[warp] = inclusive;
+                    }
+                    __syncthreads();
+                    int total_hits = 0;
+                    int before_warp = 0;
+#pragma unroll
+                    for (int w = 0; w < CTA_WARPS; w++) {
+                        const int sum = sh.table.scan_tmp[w];
+                        if (w < warp) {
+                            before_warp += sum;
+                        }
+                        total_hits += sum;
+                    }
+                    // the thread that owns the first task of a home point knows where its hits start
+                    if ((threadIdx.x & 7) == 0) {
+                        rows.row_offset[threadIdx.x >> 3] = before_warp + inclusive - my_hits;
+                    }
+                    if (threadIdx.x == 0) {
+                        rows.row_offset[TILE_POINTS] = total_hits;
+                    }
+
+                    for (int round0 = 0; round0 < total_hits; round0 += FUSED_LIST) {
+                        if (round0 != 0) {
+                            __syncthreads(); // previous round consumed
+                        }
+                        const int in_round = min(FUSED_LIST, total_hits - round0);
+                        {
+                            // every thread writes the same number of consecutive list entries (see the fused pass)
+                            const int quota = (in_round + CTA_THREADS - 1) / CTA_THREADS;
+                            int position = round0 + threadIdx.x * quota;
+                            const int stop = min(position + quota, round0 + in_round);
+                            if (position < stop) {
+                                int owner_warp = 0;
+                                int before = 0;
+                                {
+                                    int running = 0;
+#pragma unroll
+                                    for (int w = 0; w < CTA_WARPS - 1; w++) {
+                                        running += sh.table.scan_tmp[w];
+                                        if (running <= position) {
+                                            owner_warp = w + 1;
+                                            before = running;
+                                        }
+                                    }
+                                }
+                                const int target = position - before;
+                                const unsigned short* local = sh.prefix + owner_warp * 32;
+                                int lo = 0;
+                                int hi = 32;
+#pragma unroll
+                                for (int step = 0; step < 5; step++) {
+                                    const int mid = (lo + hi) >> 1;
+                                    if (static_cast<int>(local[mid]) <= target) {
+                                        lo = mid;
+                                    } else {
+                                        hi = mid;
+                                    }
+                                }
+                                int skip = target - static_cast<int>(local[lo]);
+                                lo += owner_warp * 32;
+                                int task = lo * 2;
+                                unsigned word = sh.mask[task];
+                                {
+                                    const int count = __popc(word);
+                                    if (skip >= count) {
+                                        skip -= count;
+                                        task++;
+                                        word = sh.mask[task];
+                                    }
+                                }
+                                word &= 0xffffffffu << select_bit(word, skip);
+                                for (; position < stop; position++) {
+                                    while (word == 0 && task + 1 < FUSED_WORDS * TILE_POINTS) {
+                                        task++;
+                                        word = sh.mask[task];
+                                    }
+                                    const int bit = __ffs(word) - 1;
+                                    word &= word - 1;
+                                    // (home point << 9) | slot in the batch
+                                    sh.list[position - round0] = static_cast<unsigned short>(((task >> 4) << 9) | ((task & 15) << 5) | (bit & 31));
+                                }
+                            }
+                        }
+                        __syncthreads();
+
+                        for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
+                            if (chunk0 + lane >= in_round) {
+                                continue;
+                            }
+                            const unsigned entry = sh.list[chunk0 + lane];
+                            const int h = entry >> 9;
+                            const int s = entry & 511;
+                            const int4 cand = sh.sj[s];
+                            const int4 home = sh.home_sj[h];
+                            const int s0 = cand.x + home.x;
+                            const int s1 = cand.y + home.y;
+                            const int s2 = cand.z + home.z;
+                            double vx, vy, vz;
+                            const double d2 = exact_pair(
+                                plan, sh.home_pos[0][h], sh.home_pos[1][h], sh.home_pos[2][h], sh.x[s], sh.y[s], sh.z[s], s0, s1, s2, vx, vy, vz
+                            );
+                            const unsigned long long dest = rows.home_row[h] + static_cast<unsigned long long>(round0 + chunk0 + lane - rows.row_offset[h]);
+                            reinterpret_cast<ulonglong2*>(out.pairs)[dest] =
+                                make_ulonglong2(static_cast<unsigned long long>(home.w), static_cast<unsigned long long>(cand.w));
+                            if (out.shifts != nullptr) {
+                                store_triple_32(out.shifts, dest, s0, s1, s2);
+                            }
+                            if (out.values_float) {
+                                if (out.distances != nullptr) {
+                                    reinterpret_cast<float*>(out.distances)[dest] = static_cast<float>(__dsqrt_rn(d2));
+                                }
+                                if (out.vectors != nullptr) {
+                                    store_triple_32(
+                                        reinterpret_cast<float*>(out.vectors), dest, static_cast<float>(vx), static_cast<float>(vy), static_cast<float>(vz)
+                                    );
+                                }
+                            } else {
+                                if (out.distances != nullptr) {
+                                    out.distances[dest] = __dsqrt_rn(d2);
+                                }
+                                if (out.vectors != nullptr) {
+                                    store_triple_64(out.vectors, dest, vx, vy, vz);
+                                }
+                            }
+                        }
+                    }
+                    __syncthreads();
+                    if (threadIdx.x < TILE_POINTS && tile * TILE_POINTS + threadIdx.x < unit.n_home) {
+                        const int hits = rows.row_offset[threadIdx.x + 1] - rows.row_offset[threadIdx.x];
+                        if (hits != 0) {
+                            row_fill[sh.home_sj[threadIdx.x].w] += static_cast<uint32_t>(hits);
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+            word_base += (group_total + 31) >> 5;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// canonical order inside the rows
+// A list sorted by the first index becomes THE canonical list (rows ordered by
+// second index, then by shift) when every row is sorted. Rows are short (tens
+// to hundreds of pairs), so a warp ranks the pairs of a row against each other
+// (the rank of a pair is the number of pairs of the row that come before it)
+// and copies every pair to its place in a second set of arrays. No counterpart
+// in the reference, whose device sort stops at the first index
+// (vesin/src/cuda/sort_pairs.cu:3-12).
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ bool shift_before(const int32_t* __restrict__ shifts, unsigned long long a, unsigned long long b) {
+    if (shifts == nullptr) {
+        return false;
+    }
+#pragma unroll
+    for (int c = 0; c < 3; c++) {
+        const int sa = shifts[3 * a + c];
+        const int sb = shifts[3 * b + c];
+        if (sa != sb) {
+            return sa < sb;
+        }
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(CTA_THREADS, 4) row_sort_kernel(
+    const unsigned long long* __restrict__ row_start, size_t n_rows, PairOutput in, PairOutput out
+) {
+    const int lane = threadIdx.x & 31;
+    const size_t warps = (static_cast<size_t>(gridDim.x) * blockDim.x) >> 5;
+    for (size_t row = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < n_rows; row += warps) {
+        const unsigned long long begin = row_start[row];
+        const unsigned long long length = row_start[row + 1] - begin;
+        for (unsigned long long e = lane; e < length; e += 32) {
+            const unsigned long long mine = begin + e;
+            const unsigned long long j = in.pairs[2 * mine + 1];
+            unsigned long long rank = 0;
+            for (unsigned long long k = 0; k < length; k++) {
+                const unsigned long long other = in.pairs[2 * (begin + k) + 1]; // the same address for every lane
+                if (other < j || (other == j && (shift_before(in.shifts, begin + k, mine) || (k < e && !shift_before(in.shifts, mine, begin + k))))) {
+                    rank++;
+                }
+            }
+            const unsigned long long dest = begin + rank;
+            reinterpret_cast<ulonglong2*>(out.pairs)[dest] = reinterpret_cast<const ulonglong2*>(in.pairs)[mine];
+            if (in.shifts != nullptr) {
+                store_triple_32(out.shifts, dest, in.shifts[3 * mine + 0], in.shifts[3 * mine + 1], in.shifts[3 * mine + 2]);
+            }
+            if (in.values_float) {
+                if (in.distances != nullptr) {
+                    reinterpret_cast<float*>(out.distances)[dest] = reinterpret_cast<const float*>(in.distances)[mine];
+                }
+                if (in.vectors != nullptr) {
+                    const float* v = reinterpret_cast<const float*>(in.vectors) + 3 * mine;
+                    store_triple_32(reinterpret_cast<float*>(out.vectors), dest, v[0], v[1], v[2]);
+                }
+            } else {
+                if (in.distances != nullptr) {
+                    out.distances[dest] = in.distances[mine];
+                }
+                if (in.vectors != nullptr) {
+                    store_triple_64(out.vectors, dest, in.vectors[3 * mine + 0], in.vectors[3 * mine + 1], in.vectors[3 * mine + 2]);
+                }
+            }
+        }
     }
 }
 
@@ -2401,8 +2540,9 @@ int pair_grid(int n_units, int per_sm) {
 // ---------------------------------------------------------------------------
 
 void configure_kernels() {
-    cudaFuncSetAttribute(emit_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
-    cudaFuncSetAttribute(emit_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(EmitShared)));
+    cudaFuncSetAttribute(row_count_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
+    cudaFuncSetAttribute(row_count_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
+    cudaFuncSetAttribute(row_emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
     cudaFuncSetAttribute(pairs_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
     cudaFuncSetAttribute(pairs_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
     cudaFuncSetAttribute(pairs_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
@@ -2528,30 +2668,37 @@ void launch_scatter(
 
 void launch_count(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, uint32_t* masks, unsigned long long mask_capacity,
-    unsigned long long* unit_mask_base, uint32_t* unit_words, unsigned long long* unit_count, uint32_t* row_count,
-    DeviceHeader* header, cudaStream_t stream
+    unsigned long long* unit_mask_base, uint32_t* unit_words, uint32_t* row_count, DeviceHeader* header, cudaStream_t stream
 ) {
-    int grid = pair_grid(plan.n_units, 32);
-    count_kernel<<<grid, CTA_THREADS, 0, stream>>>(
-        plan, cell_start, sorted, masks, mask_capacity, unit_mask_base, unit_words, unit_count, row_count, header
-    );
+    const int grid = pair_grid(plan.n_units, 4);
+    if (plan.full) {
+        row_count_kernel<true><<<grid, CTA_THREADS, sizeof(RowShared), stream>>>(
+            plan, cell_start, sorted, masks, mask_capacity, unit_mask_base, unit_words, row_count, header
+        );
+    } else {
+        row_count_kernel<false><<<grid, CTA_THREADS, sizeof(RowShared), stream>>>(
+            plan, cell_start, sorted, masks, mask_capacity, unit_mask_base, unit_words, row_count, header
+        );
+    }
 }
 
 void launch_emit(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks, const unsigned long long* unit_mask_base,
-    const uint32_t* unit_words, const unsigned long long* unit_start, const unsigned long long* row_start, uint32_t* row_fill,
-    PairOutput out, cudaStream_t stream
+    const uint32_t* unit_words, const unsigned long long* row_start, uint32_t* row_fill, PairOutput out, cudaStream_t stream
 ) {
-    int grid = pair_grid(plan.n_units, 16);
-    if (plan.by_index) {
-        emit_kernel<true><<<grid, CTA_THREADS, sizeof(EmitShared), stream>>>(
-            plan, cell_start, sorted, masks, unit_mask_base, unit_words, unit_start, row_start, row_fill, out
-        );
-    } else {
-        emit_kernel<false><<<grid, CTA_THREADS, sizeof(EmitShared), stream>>>(
-            plan, cell_start, sorted, masks, unit_mask_base, unit_words, unit_start, row_start, row_fill, out
-        );
+    const int grid = pair_grid(plan.n_units, 4);
+    row_emit_kernel<<<grid, CTA_THREADS, sizeof(RowShared), stream>>>(
+        plan, cell_start, sorted, masks, unit_mask_base, unit_words, row_start, row_fill, out
+    );
+}
+
+void launch_sort_rows(const unsigned long long* row_start, size_t n_rows, PairOutput in, PairOutput out, cudaStream_t stream) {
+    if (n_rows == 0) {
+        return;
     }
+    // a warp per row, eight rows per CTA
+    const size_t blocks = std::min<size_t>((n_rows + CTA_WARPS - 1) / CTA_WARPS, 148 * 64);
+    row_sort_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(row_start, n_rows, in, out);
 }
 
 void launch_pairs(
@@ -2569,25 +2716,54 @@ void launch_pairs(
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         }
     }
-    // at least 8 runs per CTA, so that the last runs do not leave most of the GPU idle
-    const int unit_run = std::max(1, std::min(DEFAULT_UNIT_RUN, plan.n_units / (sms * 4 * 8)));
-    int grid = pair_grid((plan.n_units + unit_run - 1) / unit_run, per_sm);
     const size_t smem = sizeof(FusedShared);
     // paired stores of full lists: 32 bytes of indices, 16 of distances / vectors, 8 of shifts
     // (half of that for float values); null arrays are not written
     const auto aligned = [](const void* pointer, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(pointer) % bytes == 0; };
     const uintptr_t value_bytes = out.values_float ? 8 : 16;
     out.interleave_ok = aligned(out.pairs, 32) && aligned(out.shifts, 8) && aligned(out.distances, value_bytes) && aligned(out.vectors, value_bytes);
-    if (plan.window_axis >= 0) {
+
+    const auto launch = [&](auto kernel, UnitRanges ranges, unsigned long long* run_cursor) {
+        const int n_units = (ranges.end0 - ranges.begin0) + (ranges.end1 - ranges.begin1);
+        if (n_units <= 0) {
+            return;
+        }
+        // at least 8 runs per CTA, so that the last runs do not leave most of the GPU idle
+        const int unit_run = std::max(1, std::min(DEFAULT_UNIT_RUN, n_units / (sms * 4 * 8)));
+        const int runs = (ranges.end0 - ranges.begin0 + unit_run - 1) / unit_run + (ranges.end1 - ranges.begin1 + unit_run - 1) / unit_run;
+        const int grid = pair_grid(runs, per_sm);
+        launch_chained(kernel, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run, ranges, run_cursor);
+    };
+    const UnitRanges all{0, plan.n_units, 0, 0};
+    if (plan.window_axis < 0) {
         if (plan.full) {
-            launch_chained(pairs_kernel<true, true>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run);
+            launch(pairs_kernel<true, false>, all, &header->run_cursor);
         } else {
-            launch_chained(pairs_kernel<false, true>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run);
+            launch(pairs_kernel<false, false>, all, &header->run_cursor);
+        }
+    } else if (plan.window_axis == 2) {
+        // Slab cut along the last direction: a layer of cells is a contiguous range of units.
+        // Units whose whole stencil holds owned points are ordinary units: they take the
+        // plain kernel. Half lists: every layer but the two halo layers (a unit pairs with the
+        // layer above it; the pairs with halo points above are this rank's too). Full lists:
+        // the lower halo layer and the last owned layer write one orientation of some of
+        // their pairs only: they go to the slab kernel, launched behind the plain one so that
+        // the blocks of odd length it may claim do not move the plain kernel's blocks off
+        // their alignment.
+        const int per_layer = plan.n_units / plan.n_cells[2];
+        const int layers = plan.n_cells[2];
+        if (!plan.full) {
+            launch(pairs_kernel<false, false>, UnitRanges{per_layer, per_layer * (layers - 1), 0, 0}, &header->run_cursor);
+        } else {
+            launch(pairs_kernel<true, false>, UnitRanges{per_layer, per_layer * (layers - 2), 0, 0}, &header->run_cursor);
+            launch(
+                pairs_kernel<true, true>, UnitRanges{0, per_layer, per_layer * (layers - 2), per_layer * (layers - 1)}, &header->mask_cursor
+            );
         }
     } else if (plan.full) {
-        launch_chained(pairs_kernel<true, false>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run);
+        launch(pairs_kernel<true, true>, all, &header->run_cursor);
     } else {
-        launch_chained(pairs_kernel<false, false>, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run);
+        launch(pairs_kernel<false, true>, all, &header->run_cursor);
     }
 }
 

@@ -159,22 +159,25 @@ void launch_scan_units(
     const unsigned long long* counts, unsigned long long* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream
 );
 
-/// Pass 1: fp32 screen + fp64 decision for every (point, candidate); writes
-/// one hit bit per candidate, the number of pairs of every work unit and,
-/// when plan.by_index is set, the number of pairs of every point.
+/// Sorted lists, pass 1: fp32 screen + fp64 decision for every (point,
+/// candidate) of the full stencil; writes one hit bit per candidate and adds
+/// the pairs of every point to row_count (which must start at zero).
 void launch_count(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, uint32_t* masks, unsigned long long mask_capacity,
-    unsigned long long* unit_mask_base, uint32_t* unit_words, unsigned long long* unit_count, uint32_t* row_count,
-    DeviceHeader* header, cudaStream_t stream
+    unsigned long long* unit_mask_base, uint32_t* unit_words, uint32_t* row_count, DeviceHeader* header, cudaStream_t stream
 );
 
-/// Pass 2: walks the hit bits and writes i, j, S, d, D with coalesced stores:
-/// unit after unit (plan.by_index == 0) or one row per point in index order.
+/// Sorted lists, pass 2: walks the hit bits and writes i, j, S, d, D, one row
+/// per point in index order (row_start from the scan of row_count; row_fill
+/// must start at zero).
 void launch_emit(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, const uint32_t* masks, const unsigned long long* unit_mask_base,
-    const uint32_t* unit_words, const unsigned long long* unit_start, const unsigned long long* row_start, uint32_t* row_fill,
-    PairOutput out, cudaStream_t stream
+    const uint32_t* unit_words, const unsigned long long* row_start, uint32_t* row_fill, PairOutput out, cudaStream_t stream
 );
+
+/// Sorts the pairs inside every row by (second index, shift): `in` holds rows
+/// [row_start[r], row_start[r + 1]), `out` receives the sorted rows.
+void launch_sort_rows(const unsigned long long* row_start, size_t n_rows, PairOutput in, PairOutput out, cudaStream_t stream);
 
 /// Fused pass for unsorted lists: decides every candidate of the half-shell
 /// stencil once and writes the pairs into ranges claimed from
