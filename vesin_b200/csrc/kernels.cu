@@ -1970,6 +1970,7 @@ struct RowShared {
     FusedShared staged;
     unsigned long long home_row[TILE_POINTS]; // where the row of a home point continues
     int row_offset[TILE_POINTS + 1];          // list position where the hits of each home point start
+    int tile_hits[TILE_POINTS];               // pass 1: hits of the home points of the tile in the current batch
     unsigned long long mask_base;
 };
 
@@ -2071,6 +2072,9 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) row_count_kernel(
     if (header->status & STATUS_ABORT_MASK) {
         return;
     }
+    if (threadIdx.x < TILE_POINTS) {
+        rows.tile_hits[threadIdx.x] = 0;
+    }
 
     for (int u = blockIdx.x; u < plan.n_units; u += gridDim.x) {
         const Unit unit = unit_of(plan, cell_start, u);
@@ -2107,11 +2111,17 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) row_count_kernel(
             continue; // the host grows the storage and runs the pass again
         }
 
+        // the unit's own cells open the entries own_entry ... of the stencil: the slot of a home
+        // point among the candidates is the slot of its first cell plus its number in the unit
+        const int own_entry = plan.n_search[0] + (unit.cells + 2 * plan.n_search[0]) * (plan.n_search[1] + (2 * plan.n_search[1] + 1) * plan.n_search[2]);
+        const int own_group = own_entry / SEG_MAX;
+        const bool own_straddles = (own_entry % SEG_MAX) + unit.cells > SEG_MAX;
         int word_base = 0;
         for (int g = 0; g < n_groups; g++) {
             if (n_groups > 1) {
                 group_total = setup_segments(plan, cell_start, unit, g, sh.table);
             }
+            const int own_slot0 = (g == own_group) ? sh.table.slot0[own_entry % SEG_MAX] : 0;
             for (int batch0 = 0; batch0 < group_total; batch0 += FUSED_BATCH) {
                 const int batch_slots = min(FUSED_BATCH, group_total - batch0);
                 const int batch_words = (batch_slots + 31) >> 5;
@@ -2162,23 +2172,43 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) row_count_kernel(
                     }
                     __syncthreads();
                     // ---- indices and shifts have their say on the hits; the words go to global
-                    //      memory as [tile][word][lane], the counts to the rows ----
+                    //      memory as [tile][word][lane], the counts to the rows. A thread meets the
+                    //      same home point in all of its tasks (256 is a multiple of 32). ----
                     uint32_t* mask_tile = masks + base + (static_cast<unsigned long long>(tile) * words + word_base + (batch0 >> 5)) * TILE_POINTS;
+                    const int4 home = sh.home_sj[lane];
+                    // full lists: the only candidate to drop is the point itself, whose slot is known
+                    const int self_bit = (g == own_group) ? own_slot0 + tile * TILE_POINTS + lane - batch0 : -1;
+                    int my_hits = 0;
                     for (int task = threadIdx.x; task < batch_words * TILE_POINTS; task += CTA_THREADS) {
-                        const int4 home = sh.home_sj[task & 31];
                         unsigned word = sh.mask[task];
-                        unsigned kept = 0;
+                        unsigned kept = word;
                         const int slot0 = (task >> 5) << 5;
-                        while (word != 0) {
-                            const int b = __ffs(word) - 1;
-                            word &= word - 1;
-                            if (row_keeps<FULL>(home, sh.sj[slot0 + b])) {
-                                kept |= 1u << b;
+                        if (FULL && !own_straddles) {
+                            if (self_bit >= slot0 && self_bit < slot0 + 32) {
+                                kept &= ~(1u << (self_bit - slot0));
+                            }
+                        } else {
+                            kept = 0;
+                            while (word != 0) {
+                                const int b = __ffs(word) - 1;
+                                word &= word - 1;
+                                if (row_keeps<FULL>(home, sh.sj[slot0 + b])) {
+                                    kept |= 1u << b;
+                                }
                             }
                         }
                         mask_tile[task] = kept;
-                        if (kept != 0) {
-                            atomicAdd(&row_count[home.w], static_cast<uint32_t>(__popc(kept)));
+                        my_hits += __popc(kept);
+                    }
+                    if (my_hits != 0) {
+                        atomicAdd(&rows.tile_hits[lane], my_hits);
+                    }
+                    __syncthreads();
+                    if (threadIdx.x < TILE_POINTS) {
+                        const int hits = rows.tile_hits[threadIdx.x];
+                        if (hits != 0) {
+                            atomicAdd(&row_count[sh.home_sj[threadIdx.x].w], static_cast<uint32_t>(hits));
+                            rows.tile_hits[threadIdx.x] = 0;
                         }
                     }
                 }
@@ -2453,22 +2483,58 @@ __device__ __forceinline__ bool shift_before(const int32_t* __restrict__ shifts,
     return false;
 }
 
+constexpr int ROW_SORT_STAGED = 512; // second indices of a row a warp keeps in shared memory
+
 __global__ void __launch_bounds__(CTA_THREADS, 4) row_sort_kernel(
     const unsigned long long* __restrict__ row_start, size_t n_rows, PairOutput in, PairOutput out
 ) {
+    __shared__ __align__(16) unsigned row_keys[CTA_WARPS][ROW_SORT_STAGED];
     const int lane = threadIdx.x & 31;
+    unsigned* keys = row_keys[threadIdx.x >> 5];
     const size_t warps = (static_cast<size_t>(gridDim.x) * blockDim.x) >> 5;
     for (size_t row = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < n_rows; row += warps) {
         const unsigned long long begin = row_start[row];
         const unsigned long long length = row_start[row + 1] - begin;
+        // indices fit 31 bits: the low words of the second indices of the row, padded with the
+        // largest key to a multiple of four
+        const bool staged = length <= ROW_SORT_STAGED;
+        if (staged) {
+            __syncwarp();
+            for (unsigned long long e = lane; e < ((length + 3) & ~3ull); e += 32) {
+                keys[e] = (e < length) ? static_cast<unsigned>(in.pairs[2 * (begin + e) + 1]) : 0xffffffffu;
+            }
+            __syncwarp();
+        }
         for (unsigned long long e = lane; e < length; e += 32) {
             const unsigned long long mine = begin + e;
             const unsigned long long j = in.pairs[2 * mine + 1];
             unsigned long long rank = 0;
-            for (unsigned long long k = 0; k < length; k++) {
-                const unsigned long long other = in.pairs[2 * (begin + k) + 1]; // the same address for every lane
-                if (other < j || (other == j && (shift_before(in.shifts, begin + k, mine) || (k < e && !shift_before(in.shifts, mine, begin + k))))) {
-                    rank++;
+            if (staged) {
+                const unsigned key = static_cast<unsigned>(j);
+                int smaller = 0;
+                int equal = 0;
+                const uint4* four = reinterpret_cast<const uint4*>(keys);
+                for (int k = 0; k < static_cast<int>((length + 3) >> 2); k++) {
+                    const uint4 others = four[k]; // the same address for every lane
+                    smaller += (others.x < key) + (others.y < key) + (others.z < key) + (others.w < key);
+                    equal += (others.x == key) + (others.y == key) + (others.z == key) + (others.w == key);
+                }
+                rank = static_cast<unsigned long long>(smaller);
+                if (equal > 1) {
+                    // the same second index several times in the row (periodic images): shifts decide
+                    for (unsigned long long k = 0; k < length; k++) {
+                        if (keys[k] == key && k != e &&
+                            (shift_before(in.shifts, begin + k, mine) || (k < e && !shift_before(in.shifts, mine, begin + k)))) {
+                            rank++;
+                        }
+                    }
+                }
+            } else {
+                for (unsigned long long k = 0; k < length; k++) {
+                    const unsigned long long other = in.pairs[2 * (begin + k) + 1]; // the same address for every lane
+                    if (other < j || (other == j && (shift_before(in.shifts, begin + k, mine) || (k < e && !shift_before(in.shifts, mine, begin + k))))) {
+                        rank++;
+                    }
                 }
             }
             const unsigned long long dest = begin + rank;
