@@ -21,7 +21,8 @@ enum VesinB200Stage {
     VesinB200StageCount = 4,   /* pass 1: hit masks + pairs per point */
     VesinB200StageScanRows = 5,
     VesinB200StageEmit = 6,    /* pass 2: writes i, j, S, d, D */
-    VesinB200StageCount_ = 7,
+    VesinB200StageHalo = 7,    /* sharded lists: wait for the halo messages, then bin / scan / scatter of the halo */
+    VesinB200StageCount_ = 8,
 };
 
 /* No counterpart in the reference. Switches per-stage device timing (CUDA

@@ -19,8 +19,8 @@ VesinAutoAlgorithm = 0
 VesinBruteForce = 1
 VesinCellList = 2
 
-N_STAGES = 7
-STAGE_NAMES = ("bounds", "bin", "scan_cells", "scatter", "count", "scan_rows", "emit")
+N_STAGES = 8
+STAGE_NAMES = ("bounds", "bin", "scan_cells", "scatter", "count", "scan_rows", "emit", "halo")
 
 
 class VesinDevice(ctypes.Structure):

@@ -977,6 +977,12 @@ void neighbors_slab_core(
         // the pair pass writes global indices: it reads them where a plain build keeps local ones
         SortedPoints sorted_for_pairs{sorted.pos, ws.sorted_global.as<int32_t>(), sorted.shift};
 
+        // Cut along the last direction: the cells of the owned layers come first in the cell
+        // order (see window_storage_layer), so the owned points are sorted on their own, while
+        // the messages are on their way; the halo is sorted behind them. Other directions:
+        // everything is sorted together once the messages are there.
+        const bool owned_first = with_messages && axis == 2 && n_owned == n_array;
+        const size_t owned_cells = owned_first ? n_cells / static_cast<size_t>(plan.n_cells[2]) * static_cast<size_t>(plan.n_cells[2] - 2) : n_cells;
         timer.begin(VesinB200StageBin);
         launch_header_reset(ws.d_header, ws.cell_count.as<int32_t>(), n_cells, stream);
         // points of the caller's array first: their binning runs while the messages are on their way
@@ -984,23 +990,53 @@ void neighbors_slab_core(
             source, 0, n_array, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_count.as<int32_t>(),
             ws.d_header, true, true, stream
         );
-        if (with_messages) {
+        timer.end(VesinB200StageBin);
+        if (owned_first) {
+            timer.begin(VesinB200StageScanCells);
+            launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), owned_cells, ws.scan_tmp.ptr, stream);
+            timer.end(VesinB200StageScanCells);
+            timer.begin(VesinB200StageScatter);
+            launch_scatter(
+                source, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, sorted,
+                ws.sorted_global.as<int32_t>(), ws.d_header, stream, 0, n_array
+            );
+            timer.end(VesinB200StageScatter);
+            // the halo: binned, scanned behind the owned cells, scattered behind the owned records
+            timer.begin(VesinB200StageHalo);
             await_messages();
             launch_bin(
                 source, n_array, n_index, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
                 ws.cell_count.as<int32_t>(), ws.d_header, true, false, stream
             );
+            launch_scan_cells(
+                ws.cell_count.as<int32_t>() + owned_cells, ws.cell_start.as<int32_t>() + owned_cells, n_cells - owned_cells, ws.scan_tmp.ptr,
+                stream, ws.cell_start.as<int32_t>() + owned_cells
+            );
+            launch_scatter(
+                source, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, sorted,
+                ws.sorted_global.as<int32_t>(), ws.d_header, stream, n_array, n_index
+            );
+            timer.end(VesinB200StageHalo);
+        } else {
+            if (with_messages) {
+                timer.begin(VesinB200StageHalo);
+                await_messages();
+                launch_bin(
+                    source, n_array, n_index, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
+                    ws.cell_count.as<int32_t>(), ws.d_header, true, false, stream
+                );
+                timer.end(VesinB200StageHalo);
+            }
+            timer.begin(VesinB200StageScanCells);
+            launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
+            timer.end(VesinB200StageScanCells);
+            timer.begin(VesinB200StageScatter);
+            launch_scatter(
+                source, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, sorted,
+                ws.sorted_global.as<int32_t>(), ws.d_header, stream
+            );
+            timer.end(VesinB200StageScatter);
         }
-        timer.end(VesinB200StageBin);
-        timer.begin(VesinB200StageScanCells);
-        launch_scan_cells(ws.cell_count.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, ws.scan_tmp.ptr, stream);
-        timer.end(VesinB200StageScanCells);
-        timer.begin(VesinB200StageScatter);
-        launch_scatter(
-            source, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, sorted,
-            ws.sorted_global.as<int32_t>(), ws.d_header, stream
-        );
-        timer.end(VesinB200StageScatter);
 
         set_outputs(list, ws, options, std::max<size_t>(common_capacity(ws, options), 256));
         size_t capacity = common_capacity(ws, options);
@@ -1025,6 +1061,9 @@ void neighbors_slab_core(
                 timer.collect(VesinB200StageBin);
                 timer.collect(VesinB200StageScanCells);
                 timer.collect(VesinB200StageScatter);
+                if (with_messages) {
+                    timer.collect(VesinB200StageHalo);
+                }
                 if (header.status & STATUS_BAD_POINT) {
                     throw std::runtime_error("local point " + std::to_string(header.first_bad) + " has a non-finite coordinate");
                 }

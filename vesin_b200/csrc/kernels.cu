@@ -378,6 +378,19 @@ __global__ void __launch_bounds__(CTA_THREADS) bounds_kernel(const PointSource s
 // (vesin/src/cpu_cell_list.cpp:353-374).
 // ---------------------------------------------------------------------------
 
+// Slab decomposition. Along the cut direction a rank's cells are layers 0 ...
+// n - 1 in space: 0 and n - 1 hold halo points, the layers between hold owned
+// points. They are STORED in the order owned layers, upper halo layer, lower
+// halo layer, so that the cell-sorted records of the owned points come first
+// and do not depend on the halo: the owned points can be sorted while the
+// halo is still on its way.
+__device__ __forceinline__ int window_storage_layer(int layer, int n) {
+    return (layer == 0) ? n - 1 : layer - 1;
+}
+__device__ __forceinline__ int window_space_layer(int stored, int n) {
+    return (stored == n - 1) ? 0 : stored + 1;
+}
+
 /// Cell (linear index) and wrap shift of point i. `check`: the plan is
 /// speculative; a point with a non-finite coordinate or outside the cells of a
 /// non-periodic direction refuses it.
@@ -410,7 +423,7 @@ __device__ __forceinline__ int locate_point(
             } else {
                 layer = (2 * layer < last) ? 0 : last;
             }
-            cell[k] = layer;
+            cell[k] = window_storage_layer(layer, last + 1);
         } else if (plan.periodic[k]) {
             int q = floor_div(gi, plan.n_cells[k]);
             wrap[k] = q;
@@ -567,7 +580,7 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_spine_kernel(unsigned long l
 template <typename TIn, typename TOut, bool SPINE>
 __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
     const TIn* __restrict__ in, TOut* __restrict__ out, size_t n, const unsigned long long* __restrict__ tile_offsets,
-    unsigned long long* __restrict__ total_out
+    unsigned long long* __restrict__ total_out, const TOut* __restrict__ first_value
 ) {
     let_next_kernel_start();
     wait_for_previous_kernel();
@@ -621,6 +634,9 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
         }
     }
     unsigned long long prefix = tile_offset + inclusive - local;
+    if (first_value != nullptr) {
+        prefix += static_cast<unsigned long long>(*first_value); // the scan continues an earlier one
+    }
     for (int w = 0; w < warp; w++) {
         prefix += s_warp[w];
     }
@@ -650,13 +666,13 @@ __global__ void __launch_bounds__(CTA_THREADS) scan_apply_kernel(
 /// Step 1: where does point i go? Only its index is scattered (4 bytes per point).
 template <bool HALO>
 __global__ void __launch_bounds__(CTA_THREADS) scatter_index_kernel(
-    const PointSource source, size_t n, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank,
+    const PointSource source, size_t first, size_t last, const int32_t* __restrict__ cell_of, const int32_t* __restrict__ rank,
     const int32_t* __restrict__ cell_start, int32_t* __restrict__ sorted_index, const DeviceHeader* __restrict__ header
 ) {
     let_next_kernel_start();
     wait_for_previous_kernel();
-    size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n || (header->status & STATUS_ABORT_MASK)) {
+    size_t i = first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= last || (header->status & STATUS_ABORT_MASK)) {
         return;
     }
     if (HALO && i >= source.n0) {
@@ -674,22 +690,23 @@ __global__ void __launch_bounds__(CTA_THREADS) scatter_index_kernel(
 /// store instruction writes one contiguous span whatever the order of the
 /// input (a scatter of whole records writes partial sectors all over the
 /// arrays when neighbouring points are far apart in the input).
-/// `n_records` (device): number of records, i.e. cell_start[n_cells]; the
-/// grid covers the whole local index space, which may hold empty slots.
+/// Records [first, last). `n_records` (device): number of records, i.e.
+/// cell_start[n_cells]; the range may reach past it when the local index space
+/// holds empty slots.
 template <bool HALO>
 __global__ void __launch_bounds__(CTA_THREADS) gather_records_kernel(
-    const PointSource source, size_t n, const int32_t* __restrict__ n_records, const int32_t* __restrict__ shift, SortedPoints sorted,
-    int32_t* __restrict__ sorted_global, DeviceHeader* __restrict__ header
+    const PointSource source, size_t first, size_t last, const int32_t* __restrict__ n_records, const int32_t* __restrict__ shift,
+    SortedPoints sorted, int32_t* __restrict__ sorted_global, DeviceHeader* __restrict__ header
 ) {
     let_next_kernel_start();
     wait_for_previous_kernel();
-    size_t f = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (f >= 3 * n || (header->status & STATUS_ABORT_MASK)) {
+    size_t f = 3 * first + static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (f >= 3 * last || (header->status & STATUS_ABORT_MASK)) {
         return;
     }
     size_t p = f / 3;
     size_t c = f - 3 * p;
-    if (HALO && p >= static_cast<size_t>(*n_records)) {
+    if (HALO && n_records != nullptr && p >= static_cast<size_t>(*n_records)) {
         return;
     }
     size_t i = static_cast<size_t>(sorted.index[p]);
@@ -1138,6 +1155,13 @@ __device__ __forceinline__ int setup_half_segments(
             int nb[3] = {unit.c0 + ox, unit.c1 + oy, unit.c2 + oz};
             int q[3] = {0, 0, 0};
             bool valid = true;
+            if (plan.window_axis >= 0) {
+                // the offset counts layers in space
+                const int k = plan.window_axis;
+                const int offset = (k == 0) ? ox : ((k == 1) ? oy : oz);
+                const int home = (k == 0) ? unit.c0 : ((k == 1) ? unit.c1 : unit.c2);
+                nb[k] = window_space_layer(home, plan.n_cells[k]) + offset;
+            }
 #pragma unroll
             for (int k = 0; k < 3; k++) {
                 const bool outside = nb[k] < 0 || nb[k] >= plan.n_cells[k];
@@ -1151,16 +1175,17 @@ __device__ __forceinline__ int setup_half_segments(
                 }
             }
             if (valid) {
+                if (plan.window_axis >= 0) {
+                    const int k = plan.window_axis;
+                    owned = (nb[k] >= 1 && nb[k] <= plan.n_cells[k] - 2) ? 1 : 0;
+                    nb[k] = window_storage_layer(nb[k], plan.n_cells[k]);
+                }
                 const int linear = (nb[2] * plan.n_cells[1] + nb[1]) * plan.n_cells[0] + nb[0];
                 start = cell_start[linear];
                 length = cell_start[linear + 1] - start;
                 q0 = q[0];
                 q1 = q[1];
                 q2 = q[2];
-                if (plan.window_axis >= 0) {
-                    const int layer = nb[plan.window_axis];
-                    owned = (layer >= 1 && layer <= plan.n_cells[plan.window_axis] - 2) ? 1 : 0;
-                }
             }
         }
         table.start[t] = start;
@@ -1534,7 +1559,8 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
         // pair is evaluated on exactly one rank with an owned home point, and
         // that rank writes it.
         if (SLAB) {
-            const int layer = (plan.window_axis == 0) ? unit.c0 : ((plan.window_axis == 1) ? unit.c1 : unit.c2);
+            const int stored = (plan.window_axis == 0) ? unit.c0 : ((plan.window_axis == 1) ? unit.c1 : unit.c2);
+            const int layer = window_space_layer(stored, plan.n_cells[plan.window_axis]);
             const int last = plan.n_cells[plan.window_axis] - 1;
             if (layer == last) {
                 continue;
@@ -1551,8 +1577,12 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
         // the barriers of the segment setup, and not held in registers across the unit)
         if (threadIdx.x < 3) {
             const int c = threadIdx.x;
-            sh.centre[c] = plan.origin[c] + (unit.c0 + 0.5 * unit.cells) * plan.cell_vec[0][c] + (unit.c1 + 0.5) * plan.cell_vec[1][c] +
-                           (unit.c2 + 0.5) * plan.cell_vec[2][c];
+            // (along the cut direction of a slab the geometry follows the layer in space)
+            const int g0 = (plan.window_axis == 0) ? window_space_layer(unit.c0, plan.n_cells[0]) : unit.c0;
+            const int g1 = (plan.window_axis == 1) ? window_space_layer(unit.c1, plan.n_cells[1]) : unit.c1;
+            const int g2 = (plan.window_axis == 2) ? window_space_layer(unit.c2, plan.n_cells[2]) : unit.c2;
+            sh.centre[c] = plan.origin[c] + (g0 + 0.5 * unit.cells) * plan.cell_vec[0][c] + (g1 + 0.5) * plan.cell_vec[1][c] +
+                           (g2 + 0.5) * plan.cell_vec[2][c];
         }
 
         PHASE_MARK(0); // unit setup
@@ -2691,21 +2721,25 @@ size_t scan_tmp_bytes(size_t n) {
 }
 
 template <typename TIn, typename TOut>
-static void launch_scan(const TIn* counts, TOut* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream) {
+static void launch_scan(
+    const TIn* counts, TOut* starts, size_t n, void* tmp, unsigned long long* total, cudaStream_t stream, const TOut* first_value = nullptr
+) {
     auto* tile_sums = static_cast<unsigned long long*>(tmp);
     size_t tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
     launch_chained(scan_tile_sums_kernel<TIn>, static_cast<unsigned>(tiles), CTA_THREADS, 0, stream, counts, n, tile_sums);
     if (tiles <= 2048) {
         // short spine: every block of the second kernel adds up the tile sums before it
-        launch_chained(scan_apply_kernel<TIn, TOut, true>, static_cast<unsigned>(tiles), CTA_THREADS, 0, stream, counts, starts, n, tile_sums, total);
+        launch_chained(
+            scan_apply_kernel<TIn, TOut, true>, static_cast<unsigned>(tiles), CTA_THREADS, 0, stream, counts, starts, n, tile_sums, total, first_value
+        );
     } else {
         scan_spine_kernel<<<1, CTA_THREADS, 0, stream>>>(tile_sums, tiles, total);
-        scan_apply_kernel<TIn, TOut, false><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, starts, n, tile_sums, nullptr);
+        scan_apply_kernel<TIn, TOut, false><<<static_cast<unsigned>(tiles), CTA_THREADS, 0, stream>>>(counts, starts, n, tile_sums, nullptr, first_value);
     }
 }
 
-void launch_scan_cells(const int32_t* counts, int32_t* starts, size_t n, void* tmp, cudaStream_t stream) {
-    launch_scan<int32_t, int32_t>(counts, starts, n, tmp, nullptr, stream);
+void launch_scan_cells(const int32_t* counts, int32_t* starts, size_t n, void* tmp, cudaStream_t stream, const int32_t* first_value) {
+    launch_scan<int32_t, int32_t>(counts, starts, n, tmp, nullptr, stream, first_value);
 }
 
 void launch_scan_rows(
@@ -2716,19 +2750,30 @@ void launch_scan_rows(
 
 void launch_scatter(
     const PointSource& source, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
-    size_t n_cells, SortedPoints sorted, int32_t* sorted_global, DeviceHeader* header, cudaStream_t stream
+    size_t n_cells, SortedPoints sorted, int32_t* sorted_global, DeviceHeader* header, cudaStream_t stream, size_t first, size_t last
 ) {
-    const size_t n = source.n_index();
+    if (last == static_cast<size_t>(-1)) {
+        last = source.n_index();
+    }
+    if (last <= first) {
+        return;
+    }
+    // local indices [first, last) go to records [first, last) at most: cells are filled in the order
+    // of the local indices' segments (see the slab build), or the range is everything
+    const size_t n = last - first;
     const unsigned index_blocks = static_cast<unsigned>((n + CTA_THREADS - 1) / CTA_THREADS);
     const unsigned record_blocks = static_cast<unsigned>((3 * n + CTA_THREADS - 1) / CTA_THREADS);
-    const int32_t* n_records = cell_start + n_cells;
+    // records below source.n0 are the points of the caller's array: all there; further on the
+    // local index space may hold empty slots and the number of records (known once every cell
+    // has its start) bounds the range
+    const int32_t* n_records = (last <= source.n0) ? nullptr : cell_start + n_cells;
     const DeviceHeader* read_header = header;
     if (source.message[0] != nullptr && source.capacity > 0) {
-        launch_chained(scatter_index_kernel<true>, index_blocks, CTA_THREADS, 0, stream, source, n, cell_of, rank, cell_start, sorted.index, read_header);
-        launch_chained(gather_records_kernel<true>, record_blocks, CTA_THREADS, 0, stream, source, n, n_records, shift, sorted, sorted_global, header);
+        launch_chained(scatter_index_kernel<true>, index_blocks, CTA_THREADS, 0, stream, source, first, last, cell_of, rank, cell_start, sorted.index, read_header);
+        launch_chained(gather_records_kernel<true>, record_blocks, CTA_THREADS, 0, stream, source, first, last, n_records, shift, sorted, sorted_global, header);
     } else {
-        launch_chained(scatter_index_kernel<false>, index_blocks, CTA_THREADS, 0, stream, source, n, cell_of, rank, cell_start, sorted.index, read_header);
-        launch_chained(gather_records_kernel<false>, record_blocks, CTA_THREADS, 0, stream, source, n, n_records, shift, sorted, sorted_global, header);
+        launch_chained(scatter_index_kernel<false>, index_blocks, CTA_THREADS, 0, stream, source, first, last, cell_of, rank, cell_start, sorted.index, read_header);
+        launch_chained(gather_records_kernel<false>, record_blocks, CTA_THREADS, 0, stream, source, first, last, n_records, shift, sorted, sorted_global, header);
     }
 }
 
@@ -2810,20 +2855,23 @@ void launch_pairs(
     } else if (plan.window_axis == 2) {
         // Slab cut along the last direction: a layer of cells is a contiguous range of units.
         // Units whose whole stencil holds owned points are ordinary units: they take the
-        // plain kernel. Half lists: every layer but the two halo layers (a unit pairs with the
-        // layer above it; the pairs with halo points above are this rank's too). Full lists:
-        // the lower halo layer and the last owned layer write one orientation of some of
+        // plain kernel. Half lists: every owned layer (a unit pairs with the layer above it;
+        // the pairs with halo points above are this rank's too). Full lists: the lower halo
+        // layer and the last owned layer write one orientation of some of
         // their pairs only: they go to the slab kernel, launched behind the plain one so that
         // the blocks of odd length it may claim do not move the plain kernel's blocks off
         // their alignment.
+        // (layers are stored as: owned layers, upper halo layer, lower halo layer)
         const int per_layer = plan.n_units / plan.n_cells[2];
-        const int layers = plan.n_cells[2];
+        const int owned_layers = plan.n_cells[2] - 2;
         if (!plan.full) {
-            launch(pairs_kernel<false, false>, UnitRanges{per_layer, per_layer * (layers - 1), 0, 0}, &header->run_cursor);
+            launch(pairs_kernel<false, false>, UnitRanges{0, per_layer * owned_layers, 0, 0}, &header->run_cursor);
         } else {
-            launch(pairs_kernel<true, false>, UnitRanges{per_layer, per_layer * (layers - 2), 0, 0}, &header->run_cursor);
+            launch(pairs_kernel<true, false>, UnitRanges{0, per_layer * (owned_layers - 1), 0, 0}, &header->run_cursor);
             launch(
-                pairs_kernel<true, true>, UnitRanges{0, per_layer, per_layer * (layers - 2), per_layer * (layers - 1)}, &header->mask_cursor
+                pairs_kernel<true, true>,
+                UnitRanges{per_layer * (owned_layers - 1), per_layer * owned_layers, per_layer * (owned_layers + 1), per_layer * (owned_layers + 2)},
+                &header->mask_cursor
             );
         }
     } else if (plan.full) {

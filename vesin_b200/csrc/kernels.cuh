@@ -123,7 +123,10 @@ void launch_bin(
 );
 
 /// Exclusive scan of int32 counts into int32 starts (n + 1 entries).
-void launch_scan_cells(const int32_t* counts, int32_t* starts, size_t n, void* tmp, cudaStream_t stream);
+/// `first_value` (device, may be null): what the first start is; lets a scan continue an earlier one.
+void launch_scan_cells(
+    const int32_t* counts, int32_t* starts, size_t n, void* tmp, cudaStream_t stream, const int32_t* first_value = nullptr
+);
 /// Exclusive scan of uint32 counts into uint64 starts (n + 1 entries); the
 /// grand total also goes to *total.
 void launch_scan_rows(
@@ -135,10 +138,13 @@ size_t scan_tmp_bytes(size_t n);
 /// Counting-sort scatter into the cell-sorted records. `n_cells`: cells of the
 /// plan (cell_start[n_cells] is the number of records). `sorted_global`, when
 /// not null, receives the global index of every record (31 bits; a larger one
-/// sets STATUS_INDEX_RANGE).
+/// sets STATUS_INDEX_RANGE). With [first, last): only these local indices are
+/// scattered and only these records gathered (a slab build sorts its owned
+/// points, whose records come first, before the halo has arrived).
 void launch_scatter(
     const PointSource& source, const int32_t* cell_of, const int32_t* rank, const int32_t* shift, const int32_t* cell_start,
-    size_t n_cells, SortedPoints sorted, int32_t* sorted_global, DeviceHeader* header, cudaStream_t stream
+    size_t n_cells, SortedPoints sorted, int32_t* sorted_global, DeviceHeader* header, cudaStream_t stream, size_t first = 0,
+    size_t last = static_cast<size_t>(-1)
 );
 
 /// Small systems: header reset and plan check (when `speculative`), binning,
