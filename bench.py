@@ -640,16 +640,16 @@ class ShardedBuild:
         self.d_points = self.h_points.to(harness.device)
         self.d_index = self.h_index.to(harness.device)
         self.calculator = vesin_b200.ShardedNeighborList(cutoff=cutoff, full_list=full)
-        self.last = None
 
     def build(self, points_tensor=None, index_tensor=None):
+        """The C call (vesin_b200_sharded_neighbors), like PlainBuild.build."""
         points_tensor = self.d_points if points_tensor is None else points_tensor
         index_tensor = self.d_index if index_tensor is None else index_tensor
-        self.last = self.calculator.compute(points_tensor, index_tensor, self.box, self.periodic, "PSdD", copy=False)
-        return int(self.last[0].shape[0])
+        return self.calculator.build(points_tensor, index_tensor, self.box, self.periodic, "PSdD")
 
     def outputs(self):
-        return list(self.last)
+        torch = self.harness.torch
+        return list(self.calculator.outputs(self.harness.device, "PSdD", torch.float32 if self.float_io else torch.float64))
 
     def checksum(self):
         return self.calculator.checksum()
@@ -668,7 +668,6 @@ class ShardedBuild:
         return {key: value / steps for key, value in total.items()}
 
     def free(self):
-        self.last = None
         self.calculator.close()
 
 

@@ -369,11 +369,20 @@ class ShardedNeighborList:
         float_io = points.dtype == torch.float32
         points = points.to(torch.float32 if float_io else torch.float64).contiguous()
         global_index = global_index.to(torch.int64).contiguous()
-        self._ensure_handle(device)
-        h_box = np.ascontiguousarray(box, dtype=np.float32 if float_io else np.float64)
-        h_periodic = np.ascontiguousarray(periodic, dtype=np.bool_)
         # inputs produced on another stream of the caller must be complete: the library works on its own streams
         torch.cuda.current_stream(device).synchronize()
+        self.build(points, global_index, box, periodic, quantities)
+        return self._outputs(device, quantities, copy, points.dtype)
+
+    def build(self, points, global_index, box, periodic, quantities="ij"):
+        """The C call alone (``vesin_b200_sharded_neighbors`` or its float32
+        twin): `points` float64 or float32 and `global_index` int64, contiguous
+        CUDA tensors whose contents are complete. The result stays in the
+        list; returns the number of pairs of this rank."""
+        float_io = points.dtype == torch.float32
+        self._ensure_handle(points.device)
+        h_box = np.ascontiguousarray(box, dtype=np.float32 if float_io else np.float64)
+        h_periodic = np.ascontiguousarray(periodic, dtype=np.bool_)
         error = ctypes.c_char_p()
         entry_point = self._lib.vesin_b200_sharded_neighbors_f32 if float_io else self._lib.vesin_b200_sharded_neighbors
         status = entry_point(
@@ -389,7 +398,11 @@ class ShardedNeighborList:
         )
         if status != 0:
             raise RuntimeError(error.value.decode("utf8"))
-        return self._outputs(device, quantities, copy, points.dtype)
+        return self._neighbors.length
+
+    def outputs(self, device, quantities, value_dtype=torch.float64):
+        """Zero-copy views of the arrays the last build left in the list."""
+        return self._outputs(device, quantities, False, value_dtype)
 
     def checksum(self):
         """Checksum of this rank's part of the list (add the ranks' words mod 2^64)."""
