@@ -116,6 +116,23 @@ VESIN_API int vesin_b200_neighbors_batch(
     const char** error_message
 );
 
+/* The same for float32 points and boxes: float distances and vectors come out,
+ * every decision is taken in fp64 on the exactly converted values (see
+ * vesin_b200_neighbors_f32). */
+VESIN_API int vesin_b200_neighbors_batch_f32(
+    const float (*points)[3],
+    const size_t* system_offsets,
+    size_t n_systems,
+    const float (*boxes)[3][3],
+    const bool (*periodic)[3],
+    struct VesinDevice device,
+    struct VesinOptions options,
+    bool global_indices,
+    struct VesinNeighborList* neighbors,
+    const size_t** pair_offsets,
+    const char** error_message
+);
+
 /* The slab of one rank: the box is cut along direction `axis` (which must be
  * periodic); the rank owns the points whose fractional coordinate along that
  * direction, wrapped into [0, 1), lies in [lower, upper). */

@@ -91,3 +91,50 @@ def test_empty_systems_and_errors():
     bad[4, 0] = float("inf")
     with pytest.raises(RuntimeError, match="point 4 of the batch has a non-finite coordinate"):
         calculator.compute(bad, [0, 10])
+
+
+def test_molecules_float32_and_mixed_sizes():
+    """The fp32 batch entry point (float points in, float d and D out, decisions
+    in fp64 on the upcast values), on a batch that mixes molecules small enough
+    for the warp-per-system kernel with larger ones."""
+    import torch
+
+    import vesin_b200
+
+    device = torch.device("cuda", 0)
+    rng = np.random.default_rng(77)
+    sizes = [1, 2, 0, 96, 97, 130, 33, 64, 5]
+    systems = [rng.uniform(-4.0, 4.0, (n, 3)).astype(np.float32) for n in sizes]
+    points = np.concatenate(systems)
+    offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+    for full in (True, False):
+        calculator = vesin_b200.BatchNeighborList(cutoff=3.0, full_list=full)
+        (i, j, S, d, D), pair_offsets = calculator.compute(torch.tensor(points, device=device), offsets, None, None, "ijSdD")
+        assert d.dtype == torch.float32 and D.dtype == torch.float32
+        i, j, S, d, D = (t.cpu().numpy() for t in (i, j, S, d, D))
+        pair_offsets = pair_offsets.cpu().numpy()
+        for k, system in enumerate(systems):
+            lo, hi = pair_offsets[k], pair_offsets[k + 1]
+            expected = O.canonical(O.restated_neighbors(system.astype(np.float64), np.zeros((3, 3)), [False] * 3, 3.0, full, "ijSdD"))
+            got = O.canonical({"i": i[lo:hi], "j": j[lo:hi], "S": S[lo:hi], "d": d[lo:hi], "D": D[lo:hi]})
+            assert np.array_equal(got["i"], expected["i"]) and np.array_equal(got["j"], expected["j"]), f"system {k}"
+            assert np.array_equal(got["S"], expected["S"])
+            assert np.array_equal(got["d"], expected["d"].astype(np.float32)), "d is the fp64 value rounded once"
+            assert np.array_equal(got["D"], expected["D"].astype(np.float32))
+
+
+def test_molecules_on_the_edge_of_the_cutoff():
+    """Pairs within rounding distance of the cutoff: the fp32 screen must hand
+    them to the exact predicate."""
+    rng = np.random.default_rng(5)
+    systems = []
+    for _ in range(50):
+        n = int(rng.integers(2, 40))
+        base = rng.uniform(-5.0, 5.0, 3) + 1000.0 * rng.standard_normal(3)
+        directions = rng.standard_normal((n, 3))
+        directions /= np.linalg.norm(directions, axis=1)[:, None]
+        radii = 2.0 * (1.0 + rng.integers(-3, 4, n) * 2.0 ** -52)
+        systems.append(base + directions * radii[:, None] * 0.5 + np.where(rng.random((n, 1)) < 0.5, 0.0, 1e-16))
+    points = np.concatenate(systems)
+    offsets = np.concatenate([[0], np.cumsum([len(s) for s in systems])]).astype(np.int64)
+    _check_batch(points, offsets, None, None, 2.0, True)

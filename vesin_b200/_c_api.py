@@ -66,6 +66,7 @@ EXPORTED_SYMBOLS = (
     "vesin_b200_version",
     "vesin_b200_neighbors_no_alloc",
     "vesin_b200_neighbors_batch",
+    "vesin_b200_neighbors_batch_f32",
     "vesin_b200_neighbors_slab",
     "vesin_b200_pack_halo",
     "vesin_b200_neighbors_f32",
@@ -159,6 +160,8 @@ def get_library():
         ctypes.POINTER(ctypes.c_void_p),  # pair_offsets (out, device)
         ctypes.POINTER(ctypes.c_char_p),
     ]
+    lib.vesin_b200_neighbors_batch_f32.restype = ctypes.c_int
+    lib.vesin_b200_neighbors_batch_f32.argtypes = lib.vesin_b200_neighbors_batch.argtypes
     lib.vesin_b200_neighbors_slab.restype = ctypes.c_int
     lib.vesin_b200_neighbors_slab.argtypes = [
         ctypes.c_void_p,  # points (device): owned first, then halo

@@ -228,11 +228,12 @@ extern "C" int vesin_b200_stage_times(const VesinNeighborList* neighbors, double
     return vb200::stage_times(*neighbors, stage_ms) ? 0 : 1;
 }
 
-extern "C" int vesin_b200_neighbors_batch(
-    const double (*points)[3],
+static int batch_entry(
+    const void* points,
+    bool float_io,
     const size_t* system_offsets,
     size_t n_systems,
-    const double (*boxes)[3][3],
+    const void* boxes,
     const bool (*periodic)[3],
     VesinDevice device,
     VesinOptions options,
@@ -275,7 +276,7 @@ extern "C" int vesin_b200_neighbors_batch(
     }
     neighbors->device = device;
     try {
-        vb200::neighbors_batch(points, system_offsets, n_systems, boxes, periodic, options, global_indices, *neighbors, pair_offsets);
+        vb200::neighbors_batch(points, float_io, system_offsets, n_systems, boxes, periodic, options, global_indices, *neighbors, pair_offsets);
     } catch (const std::bad_alloc&) {
         LAST_ERROR = "failed to allocate memory";
         *error_message = LAST_ERROR.c_str();
@@ -286,6 +287,38 @@ extern "C" int vesin_b200_neighbors_batch(
         return EXIT_FAILURE;
     }
     return EXIT_SUCCESS;
+}
+
+extern "C" int vesin_b200_neighbors_batch(
+    const double (*points)[3],
+    const size_t* system_offsets,
+    size_t n_systems,
+    const double (*boxes)[3][3],
+    const bool (*periodic)[3],
+    VesinDevice device,
+    VesinOptions options,
+    bool global_indices,
+    VesinNeighborList* neighbors,
+    const size_t** pair_offsets,
+    const char** error_message
+) {
+    return batch_entry(points, false, system_offsets, n_systems, boxes, periodic, device, options, global_indices, neighbors, pair_offsets, error_message);
+}
+
+extern "C" int vesin_b200_neighbors_batch_f32(
+    const float (*points)[3],
+    const size_t* system_offsets,
+    size_t n_systems,
+    const float (*boxes)[3][3],
+    const bool (*periodic)[3],
+    VesinDevice device,
+    VesinOptions options,
+    bool global_indices,
+    VesinNeighborList* neighbors,
+    const size_t** pair_offsets,
+    const char** error_message
+) {
+    return batch_entry(points, true, system_offsets, n_systems, boxes, periodic, device, options, global_indices, neighbors, pair_offsets, error_message);
 }
 
 static int slab_entry(

@@ -750,10 +750,11 @@ void neighbors(
 }
 
 void neighbors_batch(
-    const double (*points)[3],
+    const void* points,
+    bool float_io,
     const size_t* system_offsets,
     size_t n_systems,
-    const double (*boxes)[3][3],
+    const void* boxes,
     const bool (*periodic)[3],
     VesinOptions options,
     bool global_indices,
@@ -796,7 +797,7 @@ void neighbors_batch(
     DeviceGuard guard(list.device.device_id);
     Workspace& ws = workspace_of(list);
     ws.cache.valid = false; // the list was used for something else than a single system
-    ws.values_float = false;
+    ws.values_float = float_io;
     const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
     cudaStream_t stream = ws.stream;
     const DeviceHeader& header = *ws.h_header;
@@ -812,9 +813,10 @@ void neighbors_batch(
     VB200_CUDA(cudaMemsetAsync(&ws.d_header->mask_cursor, 0xff, sizeof(unsigned long long), stream)); // first singular system
 
     BatchInput in{};
-    in.points = reinterpret_cast<const double*>(points);
+    in.points = points;
+    in.is_float = float_io ? 1 : 0;
     in.offsets = ws.batch_offsets.as<unsigned long long>();
-    in.boxes = reinterpret_cast<const double*>(boxes);
+    in.boxes = boxes;
     in.periodic = reinterpret_cast<const bool*>(periodic);
     in.n_systems = static_cast<unsigned>(n_systems);
     in.cutoff = options.cutoff;
@@ -822,9 +824,11 @@ void neighbors_batch(
     in.full = options.full ? 1 : 0;
     in.global_indices = global_indices ? 1 : 0;
 
+    // systems with a periodic direction or many points take the CTA-per-system kernel
+    const bool any_for_cta_kernel = periodic != nullptr || largest > molecules_max_points();
     size_t total = 0;
     if (n_systems > 0) {
-        launch_small_count(in, largest, ws.unit_count.as<unsigned long long>(), ws.d_header, stream);
+        launch_small_count(in, largest, any_for_cta_kernel, ws.unit_count.as<unsigned long long>(), ws.d_header, stream);
         launch_scan_units(
             ws.unit_count.as<unsigned long long>(), ws.unit_start.as<unsigned long long>(), n_systems, ws.scan_tmp.ptr,
             &ws.d_header->total_pairs, stream
@@ -861,8 +865,9 @@ void neighbors_batch(
             reinterpret_cast<int32_t*>(list.shifts),
             list.distances,
             reinterpret_cast<double*>(list.vectors),
+            float_io ? 1 : 0,
         };
-        launch_small_emit(in, largest, ws.unit_start.as<unsigned long long>(), out, ws.d_header, stream);
+        launch_small_emit(in, largest, any_for_cta_kernel, ws.unit_start.as<unsigned long long>(), out, ws.d_header, stream);
         VB200_CUDA(cudaGetLastError());
     }
     VB200_CUDA(cudaStreamSynchronize(stream));

@@ -32,10 +32,11 @@ void neighbors(
 /// Lists of a batch of independent small systems in one call (no counterpart
 /// in the reference, whose callers loop over systems). Throws like neighbors().
 void neighbors_batch(
-    const double (*points)[3],
+    const void* points,
+    bool float_io,
     const size_t* system_offsets,
     size_t n_systems,
-    const double (*boxes)[3][3],
+    const void* boxes,
     const bool (*periodic)[3],
     VesinOptions options,
     bool global_indices,

@@ -12,6 +12,8 @@
 // only walks the stored hit bits, so the passes can not disagree.
 #include "kernels.cuh"
 
+#include "emit.cuh"
+
 #include <algorithm>
 #include <cfloat>
 
@@ -1274,215 +1276,6 @@ __device__ __forceinline__ unsigned decide_piece(
     return inside;
 }
 
-/// Write `n_valid` consecutive pairs starting at output element `first`:
-/// lane l holds pair l. 12- and 24-byte elements are transposed through
-/// shared memory so that every store instruction covers one contiguous span.
-__device__ __forceinline__ void store_pairs(
-    FusedShared& sh, const PairOutput& out, int warp, int lane, unsigned long long first, int n_valid, unsigned long long a,
-    unsigned long long b, int s0, int s1, int s2, double d, double vx, double vy, double vz
-) {
-    if (lane < n_valid) {
-        reinterpret_cast<ulonglong2*>(out.pairs)[first + lane] = make_ulonglong2(a, b);
-        if (out.distances != nullptr) {
-            if (out.values_float) {
-                reinterpret_cast<float*>(out.distances)[first + lane] = static_cast<float>(d);
-            } else {
-                out.distances[first + lane] = d;
-            }
-        }
-    }
-    if (out.shifts != nullptr) {
-        int* buffer = reinterpret_cast<int*>(sh.transpose[warp]);
-        buffer[3 * lane + 0] = s0;
-        buffer[3 * lane + 1] = s1;
-        buffer[3 * lane + 2] = s2;
-        __syncwarp();
-        int32_t* dst = out.shifts + 3 * first;
-#pragma unroll
-        for (int k = 0; k < 3; k++) {
-            const int w = k * 32 + lane;
-            if (w < 3 * n_valid) {
-                dst[w] = buffer[w];
-            }
-        }
-        __syncwarp();
-    }
-    if (out.vectors != nullptr && out.values_float) {
-        // fp32 output: rounded once from the fp64 result
-        float* buffer = reinterpret_cast<float*>(sh.transpose[warp]);
-        buffer[3 * lane + 0] = static_cast<float>(vx);
-        buffer[3 * lane + 1] = static_cast<float>(vy);
-        buffer[3 * lane + 2] = static_cast<float>(vz);
-        __syncwarp();
-        float* dst = reinterpret_cast<float*>(out.vectors) + 3 * first;
-#pragma unroll
-        for (int k = 0; k < 3; k++) {
-            const int w = k * 32 + lane;
-            if (w < 3 * n_valid) {
-                dst[w] = buffer[w];
-            }
-        }
-    } else if (out.vectors != nullptr) {
-        double* buffer = sh.transpose[warp];
-        buffer[3 * lane + 0] = vx;
-        buffer[3 * lane + 1] = vy;
-        buffer[3 * lane + 2] = vz;
-        __syncwarp();
-        double* dst = out.vectors + 3 * first;
-#pragma unroll
-        for (int k = 0; k < 3; k++) {
-            const int w = k * 32 + lane;
-            if (w < 3 * n_valid) {
-                dst[w] = buffer[w];
-            }
-        }
-    }
-    __syncwarp();
-}
-
-/// Full lists: lane l holds hit l and writes both orientations as the two
-/// consecutive elements first + 2 l (i, j, S, d, v) and first + 2 l + 1
-/// (j, i, -S, d, -v). `first` is even and the arrays are aligned (checked by
-/// the launch wrapper), so a lane stores its 32 bytes of indices and 16 bytes
-/// of distances at once, and the 24 + 48 bytes of shifts and vectors leave as
-/// 8- and 16-byte pieces of one contiguous span after a pass through shared
-/// memory.
-///
-/// A claim that starts on an odd element (slab-decomposed lists, where some
-/// blocks hold one orientation only) is written one element further on, which
-/// is even again; the reversed pair of its LAST hit then does not fit behind
-/// the block and goes to the block's first element instead. `tail_lane` is the
-/// lane that holds that hit in this chunk (-1: none), `tail_to` the element.
-__device__ __forceinline__ void store_both(
-    FusedShared& sh, const PairOutput& out, int warp, int lane, unsigned long long first, int n_valid, unsigned long long a,
-    unsigned long long b, int s0, int s1, int s2, double d, double vx, double vy, double vz, int tail_lane = -1,
-    unsigned long long tail_to = 0
-) {
-    const unsigned long long mine = first + 2 * lane;
-    const bool is_tail = lane == tail_lane;
-    if (lane < n_valid && !is_tail) {
-        unsigned long long* dst = out.pairs + 2 * mine;
-        asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(dst), "l"(a), "l"(b), "l"(b), "l"(a) : "memory");
-        if (out.distances != nullptr) {
-            if (out.values_float) {
-                const float df = static_cast<float>(d);
-                *reinterpret_cast<float2*>(reinterpret_cast<float*>(out.distances) + mine) = make_float2(df, df);
-            } else {
-                *reinterpret_cast<double2*>(out.distances + mine) = make_double2(d, d);
-            }
-        }
-    }
-    if (is_tail) {
-        // forward pair in place, reversed pair at the head of the block, element by element
-        reinterpret_cast<ulonglong2*>(out.pairs)[mine] = make_ulonglong2(a, b);
-        reinterpret_cast<ulonglong2*>(out.pairs)[tail_to] = make_ulonglong2(b, a);
-        if (out.distances != nullptr) {
-            if (out.values_float) {
-                reinterpret_cast<float*>(out.distances)[mine] = static_cast<float>(d);
-                reinterpret_cast<float*>(out.distances)[tail_to] = static_cast<float>(d);
-            } else {
-                out.distances[mine] = d;
-                out.distances[tail_to] = d;
-            }
-        }
-        if (out.shifts != nullptr) {
-            out.shifts[3 * tail_to + 0] = -s0;
-            out.shifts[3 * tail_to + 1] = -s1;
-            out.shifts[3 * tail_to + 2] = -s2;
-        }
-        if (out.vectors != nullptr) {
-            if (out.values_float) {
-                float* vectors = reinterpret_cast<float*>(out.vectors);
-                vectors[3 * tail_to + 0] = -static_cast<float>(vx);
-                vectors[3 * tail_to + 1] = -static_cast<float>(vy);
-                vectors[3 * tail_to + 2] = -static_cast<float>(vz);
-            } else {
-                out.vectors[3 * tail_to + 0] = -vx;
-                out.vectors[3 * tail_to + 1] = -vy;
-                out.vectors[3 * tail_to + 2] = -vz;
-            }
-        }
-    }
-    const bool whole = n_valid == 32 && tail_lane < 0; // the usual case: no bounds to check on the way out
-    // pieces of the transposed buffers: 3 per lane; of the tail lane's, the second is half
-    // forward pair (its first word is written alone) and the third is not written at all
-    const int tail_half = (tail_lane >= 0) ? 3 * tail_lane + 1 : -1;
-    if (out.shifts != nullptr) {
-        int2* buffer = reinterpret_cast<int2*>(sh.transpose[warp]);
-        buffer[3 * lane + 0] = make_int2(s0, s1);
-        buffer[3 * lane + 1] = make_int2(s2, -s0);
-        buffer[3 * lane + 2] = make_int2(-s1, -s2);
-        __syncwarp();
-        int2* dst = reinterpret_cast<int2*>(out.shifts + 3 * first) + lane;
-        if (whole) {
-            dst[0] = buffer[lane];
-            dst[32] = buffer[lane + 32];
-            dst[64] = buffer[lane + 64];
-        } else {
-#pragma unroll
-            for (int k = 0; k < 3; k++) {
-                const int piece = k * 32 + lane;
-                if (piece < 3 * n_valid && (tail_half < 0 || piece < tail_half)) {
-                    dst[k * 32] = buffer[piece];
-                } else if (piece == tail_half) {
-                    reinterpret_cast<int*>(dst + k * 32)[0] = buffer[piece].x;
-                }
-            }
-        }
-        __syncwarp();
-    }
-    if (out.vectors != nullptr && out.values_float) {
-        const float fx = static_cast<float>(vx);
-        const float fy = static_cast<float>(vy);
-        const float fz = static_cast<float>(vz);
-        float2* buffer = reinterpret_cast<float2*>(sh.transpose[warp]);
-        buffer[3 * lane + 0] = make_float2(fx, fy);
-        buffer[3 * lane + 1] = make_float2(fz, -fx);
-        buffer[3 * lane + 2] = make_float2(-fy, -fz);
-        __syncwarp();
-        float2* dst = reinterpret_cast<float2*>(reinterpret_cast<float*>(out.vectors) + 3 * first) + lane;
-        if (whole) {
-            dst[0] = buffer[lane];
-            dst[32] = buffer[lane + 32];
-            dst[64] = buffer[lane + 64];
-        } else {
-#pragma unroll
-            for (int k = 0; k < 3; k++) {
-                const int piece = k * 32 + lane;
-                if (piece < 3 * n_valid && (tail_half < 0 || piece < tail_half)) {
-                    dst[k * 32] = buffer[piece];
-                } else if (piece == tail_half) {
-                    reinterpret_cast<float*>(dst + k * 32)[0] = buffer[piece].x;
-                }
-            }
-        }
-        __syncwarp();
-    } else if (out.vectors != nullptr) {
-        double2* buffer = reinterpret_cast<double2*>(sh.transpose[warp]);
-        buffer[3 * lane + 0] = make_double2(vx, vy);
-        buffer[3 * lane + 1] = make_double2(vz, -vx);
-        buffer[3 * lane + 2] = make_double2(-vy, -vz);
-        __syncwarp();
-        double2* dst = reinterpret_cast<double2*>(out.vectors + 3 * first) + lane;
-        if (whole) {
-            dst[0] = buffer[lane];
-            dst[32] = buffer[lane + 32];
-            dst[64] = buffer[lane + 64];
-        } else {
-#pragma unroll
-            for (int k = 0; k < 3; k++) {
-                const int piece = k * 32 + lane;
-                if (piece < 3 * n_valid && (tail_half < 0 || piece < tail_half)) {
-                    dst[k * 32] = buffer[piece];
-                } else if (piece == tail_half) {
-                    reinterpret_cast<double*>(dst + k * 32)[0] = buffer[piece].x;
-                }
-            }
-        }
-        __syncwarp();
-    }
-}
-
 /// Units a launch of the fused pass covers: [begin0, end0) and [begin1, end1).
 struct UnitRanges {
     int begin0, end0, begin1, end1;
@@ -1932,7 +1725,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                         tail_lane = n_valid - 1; // the last hit of the block is in this chunk
                                     }
                                     store_both(
-                                        sh, out, warp, lane, claim + moved_on + 2ull * (round0 + chunk0), n_valid, index_i, index_j, s0, s1, s2, d,
+                                        sh.transpose[warp], out, lane, claim + moved_on + 2ull * (round0 + chunk0), n_valid, index_i, index_j, s0, s1, s2, d,
                                         vx, vy, vz, tail_lane, claim
                                     );
                                     continue;
@@ -1940,11 +1733,11 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                 const unsigned long long first = claim + round0 + chunk0;
                                 if (FULL) {
                                     if (write_forward) {
-                                        store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
+                                        store_pairs(sh.transpose[warp], out, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
                                     }
                                     if (write_reverse) {
                                         store_pairs(
-                                            sh, out, warp, lane, first + (write_forward ? total_hits : 0), n_valid, index_j, index_i, -s0, -s1, -s2,
+                                            sh.transpose[warp], out, lane, first + (write_forward ? total_hits : 0), n_valid, index_j, index_i, -s0, -s1, -s2,
                                             d, -vx, -vy, -vz
                                         );
                                     }
@@ -1962,7 +1755,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                         vy = -vy;
                                         vz = -vz;
                                     }
-                                    store_pairs(sh, out, warp, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
+                                    store_pairs(sh.transpose[warp], out, lane, first, n_valid, index_i, index_j, s0, s1, s2, d, vx, vy, vz);
                                 }
                             }
                             PHASE_MARK(8); // emission

@@ -201,15 +201,16 @@ void launch_pairs(
 
 /// A batch of independent systems stored back to back.
 struct BatchInput {
-    const double* points;              // [offsets[n_systems]][3]
+    const void* points;                // [offsets[n_systems]][3], double or float (is_float)
     const unsigned long long* offsets; // [n_systems + 1], device memory
-    const double* boxes;               // [n_systems][9] or null (then nothing is periodic)
+    const void* boxes;                 // [n_systems][9], double or float, or null (then nothing is periodic)
     const bool* periodic;              // [n_systems][3] or null (then nothing is periodic)
     unsigned n_systems;
     double cutoff;
     double cutoff2;
     int full;
     int global_indices; // pair indices count from the start of the batch, not of the system
+    int is_float;       // points and boxes are float arrays (fp32 entry point); decisions stay fp64
 };
 
 /// Largest system the batch kernels accept (its points live in shared memory).
@@ -217,11 +218,17 @@ size_t small_systems_max_points();
 void configure_small_systems();
 /// Pass 1: pairs of every system -> system_count; the first non-finite point
 /// and the first singular box are reported through the header.
-void launch_small_count(const BatchInput& in, size_t max_points, unsigned long long* system_count, DeviceHeader* header, cudaStream_t stream);
+/// (`any_for_cta_kernel`: some system is periodic or has more points than
+/// molecules_max_points(), so the CTA-per-system kernel runs as well.)
+void launch_small_count(
+    const BatchInput& in, size_t max_points, bool any_for_cta_kernel, unsigned long long* system_count, DeviceHeader* header, cudaStream_t stream
+);
+/// Largest system the warp-per-system kernel takes.
+size_t molecules_max_points();
 /// Pass 2: every system writes its pairs at system_start[system].
 void launch_small_emit(
-    const BatchInput& in, size_t max_points, const unsigned long long* system_start, PairOutput out, DeviceHeader* header,
-    cudaStream_t stream
+    const BatchInput& in, size_t max_points, bool any_for_cta_kernel, const unsigned long long* system_start, PairOutput out,
+    DeviceHeader* header, cudaStream_t stream
 );
 
 /// Order-independent checksum of a list: result[0], result[1] = two sums
