@@ -51,6 +51,8 @@ WORKLOADS = {
     "diamond512k_sorted": (lambda: workloads.diamond(40), 5.0, True, True, "diamond 40x40x40 (512000 atoms), cutoff 5.0, full list sorted by first index, fp64, ijSdD"),
     "diamond512k_canonical": (lambda: workloads.diamond(40), 5.0, True, "canonical", "diamond 40x40x40 (512000 atoms), cutoff 5.0, full list in canonical (i, j, S) order (sorted on the device), fp64, ijSdD"),
     "diamond110k": (lambda: workloads.diamond(24), 5.0, True, False, "diamond 24x24x24 (110592 atoms), cutoff 5.0, full list, fp64, ijSdD"),
+    "diamond110k_sorted": (lambda: workloads.diamond(24), 5.0, True, True, "diamond 24x24x24 (110592 atoms), cutoff 5.0, full list sorted by first index, fp64, ijSdD"),
+    "diamond110k_canonical": (lambda: workloads.diamond(24), 5.0, True, "canonical", "diamond 24x24x24 (110592 atoms), cutoff 5.0, full list in canonical (i, j, S) order, fp64, ijSdD"),
     "diamond1000": (lambda: workloads.diamond(5), 5.0, True, False, "diamond 5x5x5 (1000 atoms), cutoff 5.0, full list, fp64, ijSdD"),
     "triclinic64": (lambda: workloads.small_triclinic(), 9.0, True, False, "64 atoms in a small triclinic cell, cutoff 9.0, full list, fp64, ijSdD"),
     "liquid2m": (lambda: workloads.liquid(1 << 21), 6.0, False, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, half list, fp64 ABI, ijSdD"),
