@@ -56,6 +56,8 @@ WORKLOADS = {
     "diamond1000": (lambda: workloads.diamond(5), 5.0, True, False, "diamond 5x5x5 (1000 atoms), cutoff 5.0, full list, fp64, ijSdD"),
     "triclinic64": (lambda: workloads.small_triclinic(), 9.0, True, False, "64 atoms in a small triclinic cell, cutoff 9.0, full list, fp64, ijSdD"),
     "liquid2m": (lambda: workloads.liquid(1 << 21), 6.0, False, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, half list, fp64 ABI, ijSdD"),
+    "liquid2m_skin": (lambda: workloads.liquid(1 << 21), 6.0, False, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, skin 2.0 (steady state: cached candidates re-filtered, points moved by up to 0.2 A), half list, fp64, ijSdD"),
+    "liquid262k_skin": (lambda: workloads.liquid(1 << 18), 6.0, False, False, "LJ-density liquid, 262144 atoms, cutoff 6.0, skin 2.0 (steady state), half list, fp64, ijSdD"),
     "liquid2m_f32": (lambda: workloads.liquid(1 << 21), 6.0, False, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, half list, fp32 in / fp32 d and D out, ijSdD"),
 }
 
@@ -72,7 +74,7 @@ SHARDED_WORKLOADS = {
 }
 
 # what the default run reports besides the headline
-EXTRA_WORKLOADS = ("diamond512k_half", "diamond512k_f32", "diamond512k_sorted", "diamond512k_canonical", "diamond1000", "triclinic64", "liquid2m", "liquid2m_f32")
+EXTRA_WORKLOADS = ("diamond512k_half", "diamond512k_f32", "diamond512k_sorted", "diamond512k_canonical", "diamond1000", "triclinic64", "liquid2m", "liquid2m_f32", "liquid2m_skin")
 EXTRA_STEPS = 10
 
 
@@ -411,7 +413,7 @@ class Harness:
 class PlainBuild:
     """One system on this rank's GPU through vesin_neighbors (or the fp32 entry point)."""
 
-    def __init__(self, harness, system, cutoff, full, float_io=False, sorted_list=False):
+    def __init__(self, harness, system, cutoff, full, float_io=False, sorted_list=False, skin=0.0):
         from vesin_b200._c_api import VesinCUDA, VesinDevice, VesinNeighborList, VesinOptions
 
         torch = harness.torch
@@ -436,14 +438,24 @@ class PlainBuild:
         options.return_shifts = True
         options.return_distances = True
         options.return_vectors = True
-        options.skin = 0.0
+        options.skin = skin
         self.options = options
+        # with a skin the timed builds alternate between the points the candidates were built for
+        # and a copy moved by up to 0.2 A per coordinate: every step re-filters cached candidates
+        self.moved = None
+        self.calls = 0
+        if skin > 0.0:
+            shift = np.random.default_rng(11).uniform(-0.2, 0.2, np.shape(points)).astype(dtype)
+            self.moved = torch.from_numpy(np.ascontiguousarray(points, dtype=dtype) + shift).to(harness.device)
         self.c_device = VesinDevice(VesinCUDA, harness.local_rank)
         self.neighbors = VesinNeighborList()
         self.error = ctypes.c_char_p()
 
     def build(self, points_tensor=None):
         tensor = self.d_points if points_tensor is None else points_tensor
+        if points_tensor is None and self.moved is not None:
+            self.calls += 1
+            tensor = self.moved if self.calls % 2 == 0 else self.d_points
         status = self.entry_point(
             tensor.data_ptr(), self.n_points, self.d_box.data_ptr(), self.d_periodic.data_ptr(), self.c_device, self.options,
             ctypes.byref(self.neighbors), ctypes.byref(self.error),
@@ -531,7 +543,7 @@ def measure_extra(harness, name):
         return measure_extra_batch(harness, name)
     make, cutoff, full, sorted_list, description = WORKLOADS[name]
     float_io = name.endswith("_f32")
-    build = PlainBuild(harness, make(), cutoff, full, float_io, sorted_list)
+    build = PlainBuild(harness, make(), cutoff, full, float_io, sorted_list, skin=2.0 if name.endswith("_skin") else 0.0)
     for _ in range(3):
         n_pairs = build.build()
     device_ms, n_pairs = harness.time_steps(build.build, EXTRA_STEPS)
@@ -768,7 +780,7 @@ def run_ours(args):
         launches_per_step = 9  # pack, header, bin (owned), bin (halo), 2 x scan, 2 x scatter, pairs (+ the NCCL send/recv kernel)
     else:
         system = make()
-        build = PlainBuild(harness, system, cutoff, full, float_io, sorted_list)
+        build = PlainBuild(harness, system, cutoff, full, float_io, sorted_list, skin=2.0 if name.endswith("_skin") else 0.0)
         n_points_rank = build.n_points
         per_gpu = "one independent copy of the system per GPU, no communication" if world > 1 else "the whole system on one GPU"
         launches_per_step = 7  # header (reset, zero, box check), bin (+ point checks), 2 x scan, 2 x scatter, pairs

@@ -3,6 +3,7 @@
 #include "engine.hpp"
 
 #include <atomic>
+#include <chrono>
 #include <cerrno>
 #include <cmath>
 #include <cstdlib>
@@ -131,6 +132,25 @@ struct Workspace {
         GridPlan plan{};
     } cache;
 
+    // Verlet-skin cache (options.skin > 0): candidates found at cutoff + skin, kept as records,
+    // and what they were built for. `candidates` is a list of its own, built like any other.
+    struct VerletCache {
+        bool valid = false;
+        // every call rebuilds: shifts of this system do not fit the records, or filtering the
+        // candidates of this system turned out slower than building a list (dense systems)
+        bool disabled = false;
+        double build_seconds = 0.0; // host time of the last build of candidates
+        double cutoff = 0.0;
+        double skin = 0.0;
+        bool full = false;
+        bool float_io = false;
+        size_t n_points = 0;
+        size_t n_records = 0;
+        VesinNeighborList candidates{};
+        DeviceBuffer records, reference_points, reference_box, state, rank_of, positions;
+        VerletState* h_state = nullptr; // pinned
+    } verlet;
+
     cudaEvent_t events[2 * N_STAGES] = {};
     bool events_created = false;
     bool timed = false;
@@ -142,6 +162,15 @@ struct Workspace {
               &unit_words, &unit_count, &unit_start, &row_count, &row_start, &row_fill, &scan_tmp, &batch_offsets, &sorted_global, &checksum, &out_pairs,
               &out_shifts, &out_distances, &out_vectors, &alt_pairs, &alt_shifts, &alt_distances, &alt_vectors}) {
             buffer->release();
+        }
+        for (DeviceBuffer* buffer : {&verlet.records, &verlet.reference_points, &verlet.reference_box, &verlet.state, &verlet.rank_of, &verlet.positions}) {
+            buffer->release();
+        }
+        if (verlet.h_state != nullptr) {
+            cudaFreeHost(verlet.h_state);
+        }
+        if (verlet.candidates.opaque != nullptr) {
+            free_neighbors(verlet.candidates);
         }
         if (d_header != nullptr) {
             cudaFree(d_header);
@@ -352,6 +381,196 @@ bool stage_times(const VesinNeighborList& list, double* stage_ms) {
     return true;
 }
 
+namespace {
+
+/// `skin > 0`: the list from cached candidates when they still fit the inputs,
+/// else candidates are rebuilt at cutoff + skin first. Either way the result is
+/// the exact list at the cutoff (vesin/src/verlet_cuda.cpp:307-322).
+void neighbors_with_skin(
+    const void* points, size_t n_points, const void* box, const bool periodic[3], VesinOptions options, VesinNeighborList& list,
+    bool float_io
+) {
+    DeviceGuard guard(list.device.device_id);
+    Workspace& ws = workspace_of(list);
+    auto& cache = ws.verlet;
+    ws.values_float = float_io;
+    ws.cache.valid = false; // the plain build's plan is not kept up to date by these calls
+    cudaStream_t stream = ws.stream;
+    StageTimer timer(ws, PROFILING.load());
+    const RealView flat_points{points, float_io ? 1 : 0};
+    const RealView flat_box{box, float_io ? 1 : 0};
+    const size_t pair_limit_per_point = max_pairs_per_point(options.cutoff);
+    const size_t value_bytes = float_io ? sizeof(float) : sizeof(double);
+
+    if (cache.h_state == nullptr) {
+        VB200_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&cache.h_state), sizeof(VerletState), cudaHostAllocDefault));
+        cache.state.reserve(sizeof(VerletState));
+        cache.reference_box.reserve(9 * sizeof(double) + 8);
+    }
+    auto* d_state = cache.state.as<VerletState>();
+    const auto read_state = [&]() {
+        VB200_CUDA(cudaMemcpyAsync(cache.h_state, d_state, sizeof(VerletState), cudaMemcpyDeviceToHost, stream));
+        VB200_CUDA(cudaStreamSynchronize(stream));
+    };
+
+    if (cache.disabled) {
+        options.skin = 0.0;
+        neighbors(points, n_points, box, periodic, options, list, float_io, false);
+        return;
+    }
+    bool usable = cache.valid && cache.cutoff == options.cutoff && cache.skin == options.skin && cache.full == options.full &&
+                  cache.float_io == float_io && cache.n_points == n_points;
+    std::chrono::steady_clock::time_point filter_started{};
+    for (int round = 0;; round++) {
+        if (!usable) {
+            // ---- candidates: the half list at cutoff + skin, built like any list ----
+            cache.valid = false;
+            cache.candidates.device = list.device;
+            VesinOptions wide = options;
+            wide.cutoff = options.cutoff + options.skin;
+            wide.skin = 0.0;
+            wide.full = false;
+            wide.sorted = false;
+            wide.return_shifts = true;
+            wide.return_distances = false;
+            wide.return_vectors = false;
+            const auto build_started = std::chrono::steady_clock::now();
+            neighbors(points, n_points, box, periodic, wide, cache.candidates, float_io, false);
+            cache.build_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - build_started).count();
+            cache.n_records = cache.candidates.length;
+            cache.records.reserve(std::max<size_t>(cache.n_records, 1) * 3 * sizeof(uint32_t));
+            cache.reference_points.reserve(std::max<size_t>(n_points, 1) * 3 * value_bytes);
+            VB200_CUDA(cudaMemsetAsync(d_state, 0, sizeof(VerletState), stream));
+            // records name the points by their position in the cell-sorted order of this very build
+            const auto* built = static_cast<const Workspace*>(cache.candidates.opaque);
+            cache.rank_of.reserve(std::max<size_t>(n_points, 1) * sizeof(uint32_t));
+            cache.positions.reserve(std::max<size_t>(n_points, 1) * 4 * sizeof(double));
+            launch_verlet_pack(
+                reinterpret_cast<const unsigned long long*>(cache.candidates.pairs), reinterpret_cast<const int32_t*>(cache.candidates.shifts),
+                cache.n_records, built->sorted_index.as<int32_t>(), n_points, cache.rank_of.as<uint32_t>(), cache.records.as<uint32_t>(), d_state,
+                stream
+            );
+            if (timer.enabled && built->timed) {
+                for (int k = 0; k < N_STAGES; k++) {
+                    ws.stage_ms[k] += built->stage_ms[k]; // the build of the candidates belongs to this call
+                }
+            }
+            VB200_CUDA(cudaMemcpyAsync(cache.reference_points.ptr, points, n_points * 3 * value_bytes, cudaMemcpyDeviceToDevice, stream));
+            // box as doubles and the periodicity flags behind it
+            if (float_io) {
+                float box32[9];
+                VB200_CUDA(cudaMemcpy(box32, box, sizeof(box32), cudaMemcpyDeviceToHost));
+                double box64[9];
+                for (int k = 0; k < 9; k++) {
+                    box64[k] = box32[k];
+                }
+                VB200_CUDA(cudaMemcpyAsync(cache.reference_box.ptr, box64, sizeof(box64), cudaMemcpyHostToDevice, stream));
+                VB200_CUDA(cudaStreamSynchronize(stream)); // box64 leaves scope
+            } else {
+                VB200_CUDA(cudaMemcpyAsync(cache.reference_box.ptr, box, 9 * sizeof(double), cudaMemcpyDeviceToDevice, stream));
+            }
+            VB200_CUDA(cudaMemcpyAsync(cache.reference_box.as<double>() + 9, periodic, 3, cudaMemcpyDeviceToDevice, stream));
+            cache.cutoff = options.cutoff;
+            cache.skin = options.skin;
+            cache.full = options.full;
+            cache.float_io = float_io;
+            cache.n_points = n_points;
+            cache.valid = true;
+        } else {
+            filter_started = std::chrono::steady_clock::now();
+            timer.begin(VesinB200StageBounds);
+            VB200_CUDA(cudaMemsetAsync(d_state, 0, sizeof(VerletState), stream));
+            launch_verlet_check(
+                flat_points, RealView{cache.reference_points.ptr, float_io ? 1 : 0}, n_points, flat_box, periodic, cache.reference_box.as<double>(),
+                reinterpret_cast<const unsigned char*>(cache.reference_box.as<double>() + 9), options.skin, d_state, stream
+            );
+            timer.end(VesinB200StageBounds);
+        }
+
+        // ---- filter: into the arrays of the previous call first; when the pairs do not fit they
+        // have still been counted: grow to the exact total and filter again ----
+        set_outputs(list, ws, options, std::max<size_t>(common_capacity(ws, options), 256));
+        size_t capacity = common_capacity(ws, options);
+        bool stale = false;
+        for (int attempt = 0;; attempt++) {
+            PairOutput out{
+                reinterpret_cast<unsigned long long*>(list.pairs),
+                reinterpret_cast<int32_t*>(list.shifts),
+                list.distances,
+                reinterpret_cast<double*>(list.vectors),
+                float_io ? 1 : 0,
+            };
+            const auto* built = static_cast<const Workspace*>(cache.candidates.opaque);
+            timer.begin(VesinB200StageEmit);
+            if (attempt == 0) {
+                launch_verlet_positions(flat_points, built->sorted_index.as<int32_t>(), n_points, cache.positions.as<double>(), d_state, stream);
+            }
+            launch_verlet_filter(
+                cache.records.as<uint32_t>(), cache.n_records, cache.positions.as<double>(), built->sorted_index.as<int32_t>(), flat_box,
+                options.cutoff * options.cutoff, options.full, out, capacity, d_state, stream
+            );
+            timer.end(VesinB200StageEmit);
+            VB200_CUDA(cudaGetLastError());
+            read_state();
+            if (attempt == 0 && usable) {
+                timer.collect(VesinB200StageBounds);
+            }
+            timer.collect(VesinB200StageEmit);
+            if (cache.h_state->unpackable) {
+                // shifts beyond the records' range (points very far outside the box): no cache for this list
+                cache.disabled = true;
+                cache.valid = false;
+                options.skin = 0.0;
+                neighbors(points, n_points, box, periodic, options, list, float_io, false);
+                return;
+            }
+            if (cache.h_state->stale) {
+                stale = true;
+                break;
+            }
+            const size_t total = static_cast<size_t>(cache.h_state->pair_cursor);
+            if (total > n_points * pair_limit_per_point) {
+                throw std::runtime_error(
+                    "The number of neighbor pairs exceeds the maximum capacity of " + std::to_string(n_points * pair_limit_per_point) +
+                    " (max_pairs_per_point=" + std::to_string(pair_limit_per_point) + "; n_points=" + std::to_string(n_points) + "). " +
+                    "Consider reducing the cutoff distance, or explicitly setting " +
+                    "VESIN_CUDA_MAX_PAIRS_PER_POINT as an environment variable."
+                );
+            }
+            if (total <= capacity) {
+                list.length = total;
+                ws.timed = timer.enabled;
+                if (usable && attempt == 0) {
+                    // Re-filtering pays when few candidates lie between cutoff and cutoff + skin per kept
+                    // pair and the build has many candidates to screen per pair (sparse systems); for
+                    // dense ones a build is cheaper than a pass over the candidates. Decided by the
+                    // clock: a check + filter that took longer than the build of the candidates (at
+                    // the larger cutoff, so slower than a plain build) ends the caching for this list.
+                    const double filter_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - filter_started).count();
+                    // (small systems are bound by launch latency either way: they keep their candidates)
+                    if (filter_seconds > 2.0e-4 && filter_seconds > cache.build_seconds) {
+                        cache.disabled = true;
+                        cache.valid = false;
+                    }
+                }
+                return;
+            }
+            if (attempt >= 2) {
+                throw std::runtime_error("internal error: the pair total kept changing between passes");
+            }
+            set_outputs(list, ws, options, total + total / 16 + 256);
+            capacity = common_capacity(ws, options);
+            VB200_CUDA(cudaMemsetAsync(&d_state->pair_cursor, 0, sizeof(unsigned long long), stream));
+        }
+        if (!stale || round >= 1) {
+            throw std::runtime_error("internal error: candidates built for these very inputs were refused");
+        }
+        usable = false; // some point moved too far, or the box did: new candidates
+    }
+}
+
+} // namespace
+
 void neighbors(
     const void* points,
     size_t n_points,
@@ -373,6 +592,12 @@ void neighbors(
     validate_pointers(points, box, periodic, list);
     if (n_points >= (1ull << 31) - 1) {
         throw std::runtime_error("this engine indexes points with 31 bits: too many points");
+    }
+
+    if (options.skin > 0.0 && std::isfinite(options.skin) && !options.sorted && n_points > 0 && options.algorithm != VesinBruteForce) {
+        // cached candidates at cutoff + skin, re-filtered (the result is the list at the cutoff all the same)
+        neighbors_with_skin(points, n_points, box, periodic, options, list, float_io);
+        return;
     }
 
     DeviceGuard guard(list.device.device_id);

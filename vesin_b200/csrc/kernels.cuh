@@ -240,6 +240,49 @@ void launch_checksum(
     cudaStream_t stream
 );
 
+// ---- Verlet-skin cache (verlet.cu) ----
+
+/// Device words of the cache of one list: what the check and the filter report.
+struct VerletState {
+    unsigned long long pair_cursor; // output elements claimed by the filter (= its pair total)
+    int stale;                      // the candidates do not fit the inputs of this call
+    int unpackable;                 // a candidate's shift does not fit its 10 bits
+};
+
+/// Candidates (pairs + shifts of a half list) to 12-byte records: the two
+/// points as positions in the cell-sorted order `sorted_index` (position ->
+/// index) of the build that found them, and the three shift components in 10
+/// bits each; a shift outside [-512, 511] sets state->unpackable. `rank_of`:
+/// n_points words of scratch (index -> position).
+void launch_verlet_pack(
+    const unsigned long long* pairs, const int32_t* shifts, size_t n, const int32_t* sorted_index, size_t n_points, uint32_t* rank_of,
+    uint32_t* records, VerletState* state, cudaStream_t stream
+);
+
+/// Row p of `positions` (4 doubles, 32 bytes) = x, y, z of points[sorted_index[p]]
+/// and sorted_index[p] as raw bits (nothing when state->stale is set).
+void launch_verlet_positions(
+    RealView points, const int32_t* sorted_index, size_t n_points, double* positions, const VerletState* state, cudaStream_t stream
+);
+
+/// Sets state->stale when some point moved further than (skin - corner
+/// displacement of the box) / 2 from `reference_points`, when the box corners
+/// moved by `skin` or more, or when the periodicity changed. `reference_box`
+/// (9 doubles) and `reference_periodic` (3 bytes) live in device memory.
+void launch_verlet_check(
+    RealView points, RealView reference_points, size_t n, RealView box, const bool* periodic, const double* reference_box,
+    const unsigned char* reference_periodic, double skin, VerletState* state, cudaStream_t stream
+);
+
+/// Writes the records within the cutoff (exact fp64 predicate on `positions`,
+/// the current points in cell-sorted order, and the box) into ranges claimed from state->pair_cursor; a full list
+/// gets both orientations of every kept record. Does nothing when
+/// state->stale is set. Ranges past `capacity` are counted, not written.
+void launch_verlet_filter(
+    const uint32_t* records, size_t n, const double* positions, const int32_t* sorted_index, RealView box, double cutoff2, bool full,
+    PairOutput out, unsigned long long capacity, VerletState* state, cudaStream_t stream
+);
+
 /// One-time per-device kernel attribute setup (shared-memory opt-in).
 void configure_kernels();
 
