@@ -1284,7 +1284,7 @@ struct UnitRanges {
 template <bool FULL, bool SLAB>
 __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, const int UNIT_RUN, const UnitRanges ranges, unsigned long long* run_cursor
+    DeviceHeader* header, const int UNIT_RUN, const UnitRanges ranges, unsigned long long* run_cursor, const int follows_pair_kernel
 ) {
     extern __shared__ __align__(16) unsigned char fused_smem[];
     FusedShared& sh = *reinterpret_cast<FusedShared*>(fused_smem);
@@ -1294,7 +1294,15 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     const float cutoff2_lo = plan.cutoff2_lo;
     const float cutoff2_hi = plan.cutoff2_hi;
 
-    wait_for_previous_kernel();
+    // A slab build launches two pair kernels back to back: the second one (the units next to
+    // the halo) needs nothing the first one writes, only what the kernels before both wrote.
+    // The first one lets its follower be scheduled once every one of its own blocks has seen
+    // those kernels complete (below); the follower then does not wait for it, and its blocks
+    // fill the SMs that the first kernel's last runs leave idle.
+    if (!follows_pair_kernel) {
+        wait_for_previous_kernel();
+        let_next_kernel_start();
+    }
     if (header->status & STATUS_ABORT_MASK) {
         return; // the plan was refused: the host will redo the build
     }
@@ -2627,7 +2635,7 @@ void launch_pairs(
     const uintptr_t value_bytes = out.values_float ? 8 : 16;
     out.interleave_ok = aligned(out.pairs, 32) && aligned(out.shifts, 8) && aligned(out.distances, value_bytes) && aligned(out.vectors, value_bytes);
 
-    const auto launch = [&](auto kernel, UnitRanges ranges, unsigned long long* run_cursor) {
+    const auto launch = [&](auto kernel, UnitRanges ranges, unsigned long long* run_cursor, bool follows = false) {
         const int n_units = (ranges.end0 - ranges.begin0) + (ranges.end1 - ranges.begin1);
         if (n_units <= 0) {
             return;
@@ -2636,7 +2644,9 @@ void launch_pairs(
         const int unit_run = std::max(1, std::min(DEFAULT_UNIT_RUN, n_units / (sms * 4 * 8)));
         const int runs = (ranges.end0 - ranges.begin0 + unit_run - 1) / unit_run + (ranges.end1 - ranges.begin1 + unit_run - 1) / unit_run;
         const int grid = pair_grid(runs, per_sm);
-        launch_chained(kernel, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run, ranges, run_cursor);
+        launch_chained(
+            kernel, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run, ranges, run_cursor, follows ? 1 : 0
+        );
     };
     const UnitRanges all{0, plan.n_units, 0, 0};
     if (plan.window_axis < 0) {
@@ -2651,9 +2661,9 @@ void launch_pairs(
         // plain kernel. Half lists: every owned layer (a unit pairs with the layer above it;
         // the pairs with halo points above are this rank's too). Full lists: the lower halo
         // layer and the last owned layer write one orientation of some of
-        // their pairs only: they go to the slab kernel, launched behind the plain one so that
-        // the blocks of odd length it may claim do not move the plain kernel's blocks off
-        // their alignment.
+        // their pairs only: they go to the slab kernel, launched behind the plain one (whose
+        // tail its blocks fill, see the top of the kernel) so that the blocks of odd length it
+        // may claim move few of the plain kernel's blocks off their alignment.
         // (layers are stored as: owned layers, upper halo layer, lower halo layer)
         const int per_layer = plan.n_units / plan.n_cells[2];
         const int owned_layers = plan.n_cells[2] - 2;
@@ -2664,7 +2674,7 @@ void launch_pairs(
             launch(
                 pairs_kernel<true, true>,
                 UnitRanges{per_layer * (owned_layers - 1), per_layer * owned_layers, per_layer * (owned_layers + 1), per_layer * (owned_layers + 2)},
-                &header->mask_cursor
+                &header->mask_cursor, /*follows=*/owned_layers > 1
             );
         }
     } else if (plan.full) {
