@@ -138,3 +138,18 @@ def test_molecules_on_the_edge_of_the_cutoff():
     points = np.concatenate(systems)
     offsets = np.concatenate([[0], np.cumsum([len(s) for s in systems])]).astype(np.int64)
     _check_batch(points, offsets, None, None, 2.0, True)
+
+
+def test_cutoff_far_beyond_the_box_of_a_system_is_refused():
+    import torch
+
+    import vesin_b200
+
+    device = torch.device("cuda", 0)
+    points = np.random.default_rng(1).random((6, 3))
+    offsets = np.array([0, 3, 6])
+    boxes = np.stack([np.eye(3) * 5.0, np.eye(3) * 1e-3])
+    periodic = np.ones((2, 3), dtype=bool)
+    calculator = vesin_b200.BatchNeighborList(cutoff=2.0, full_list=True)
+    with pytest.raises(RuntimeError, match="too large for the box of system 1"):
+        calculator.compute(torch.tensor(points, device=device), offsets, torch.tensor(boxes, device=device), torch.tensor(periodic, device=device), "ij")

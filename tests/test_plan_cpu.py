@@ -152,6 +152,19 @@ def test_errors_of_the_reference(planner):
     assert np.array_equal(np.array(plan.H).reshape(3, 3), np.eye(3))
 
 
+def test_cutoff_hundreds_of_times_the_box_is_refused(planner):
+    """A stencil beyond 2^20 cells (a collapsed box, a wrong unit) is an error,
+    not a kernel that walks billions of images; large but sane stencils pass."""
+    plan = planner(np.eye(3) * 0.5, [True, True, True], [0, 0, 0], [0.4, 0.4, 0.4], 3, 0.6)
+    assert plan.n_search[0] == 2
+    plan = planner(np.eye(3), [True, True, True], [0, 0, 0], [1, 1, 1], 4, 40.0)  # 81^3 = 531 441 cells
+    assert plan.n_search[0] >= 40
+    with pytest.raises(RuntimeError, match="the cutoff is too large for this box"):
+        planner(np.eye(3), [True, True, True], [0, 0, 0], [1, 1, 1], 4, 60.0)
+    # non-periodic directions have no images: the same numbers are fine
+    planner(np.eye(3), [False, False, False], [0, 0, 0], [1, 1, 1], 4, 60.0)
+
+
 def test_huge_empty_box_does_not_allocate_by_volume(planner):
     plan = planner(np.eye(3) * 1.0e6, [True, True, True], [0, 0, 0], [10, 10, 10], 64, 3.0)
     assert plan.n_cells_total <= 64

@@ -1060,6 +1060,9 @@ void neighbors_batch(
         );
         VB200_CUDA(cudaGetLastError());
         read_header(ws);
+        if (header.status & STATUS_STENCIL_TOO_LARGE) {
+            throw std::runtime_error("the cutoff is too large for the box of system " + std::to_string(header.mask_cursor) + " of the batch");
+        }
         if (header.status & STATUS_SINGULAR_BOX) {
             throw std::runtime_error("the box matrix is not invertible (system " + std::to_string(header.mask_cursor) + " of the batch)");
         }

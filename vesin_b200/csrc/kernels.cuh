@@ -36,6 +36,7 @@ constexpr unsigned int STATUS_BAD_POINT = 2u;  // a point has a non-finite coord
 constexpr unsigned int STATUS_PLAN_STALE = 4u; // box / periodicity / extent differ from what the plan was made for
 constexpr unsigned int STATUS_ABORT_MASK = STATUS_BAD_POINT | STATUS_PLAN_STALE;
 constexpr unsigned int STATUS_SINGULAR_BOX = 8u; // batches: the box of a system is not invertible
+constexpr unsigned int STATUS_STENCIL_TOO_LARGE = 64u; // batches: the cutoff is hundreds of times the box of a system
 constexpr unsigned int STATUS_HALO_OVERFLOW = 16u; // slab decomposition: a halo message holds fewer records than were selected
 constexpr unsigned int STATUS_INDEX_RANGE = 32u;   // slab decomposition: a global index does not fit 31 bits
 constexpr unsigned long long NO_BAD_POINT = ~0ull;

@@ -238,6 +238,20 @@ GridPlan make_plan(
         }
         plan.n_stencil *= 2 * plan.n_search[k] + 1;
     }
+    {
+        // a cutoff many times the box (a collapsed box, a wrong unit) would mean a stencil of
+        // billions of cells: an error, not a kernel that never ends
+        double stencil = 1.0;
+        for (int k = 0; k < 3; k++) {
+            stencil *= 2.0 * plan.n_search[k] + 1.0;
+        }
+        if (stencil > static_cast<double>(MAX_STENCIL_CELLS)) {
+            throw std::runtime_error(
+                "the cutoff is too large for this box: every point would be compared with more than " + std::to_string(MAX_STENCIL_CELLS) +
+                " periodic images of the cells around it"
+            );
+        }
+    }
     plan.n_cells_total = plan.n_cells[0] * plan.n_cells[1] * plan.n_cells[2];
     for (int c = 0; c < 3; c++) {
         plan.origin[c] = 0.0;

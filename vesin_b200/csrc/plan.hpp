@@ -62,6 +62,11 @@ struct GridPlan {
     int32_t full;     // full list (1) or half list (0)
 };
 
+/// Largest stencil (product of 2 * n_search + 1 over the directions; for a
+/// batch system: of 2 * reach + 1) a build accepts. A larger one means the
+/// cutoff is hundreds of box lengths: refused with an error.
+constexpr long long MAX_STENCIL_CELLS = 1 << 20;
+
 /// Bounds of the input points, as found by the reduction kernel
 struct PointBounds {
     double min[3];

@@ -18,6 +18,7 @@
 #include "kernels.cuh"
 
 #include "emit.cuh"
+#include "plan.hpp"
 
 #include <cfloat>
 
@@ -128,6 +129,11 @@ __device__ void make_frame(SystemFrame& frame, const BatchInput& in, unsigned sy
             double reach = floor(cutoff * inv_face * (1.0 + 1e-9) + 0.5 + 1e-9);
             frame.reach[k] = static_cast<int>(fmin(reach, 1.0e6));
         }
+    }
+    // images per pair: beyond the limit the system is refused (2: "cutoff too large for the box")
+    const double images = (2.0 * frame.reach[0] + 1.0) * (2.0 * frame.reach[1] + 1.0) * (2.0 * frame.reach[2] + 1.0);
+    if (images > static_cast<double>(MAX_STENCIL_CELLS)) {
+        frame.singular = 2;
     }
 }
 
@@ -380,7 +386,7 @@ __global__ void __launch_bounds__(SMALL_THREADS) small_systems_kernel(
             make_frame(sh.frame, in, system, in.periodic ? in.periodic + 3 * static_cast<size_t>(system) : nullptr, in.cutoff);
             sh.counter = 0;
             if (sh.frame.singular && !EMIT) {
-                atomicOr(&header->status, STATUS_SINGULAR_BOX);
+                atomicOr(&header->status, sh.frame.singular == 2 ? STATUS_STENCIL_TOO_LARGE : STATUS_SINGULAR_BOX);
                 atomicMin(&header->mask_cursor, static_cast<unsigned long long>(system)); // first offending system
             }
         }
