@@ -812,7 +812,7 @@ void neighbors(
                 };
                 const size_t pass_capacity = count_only ? 0 : capacity;
                 timer.begin(VesinB200StageEmit);
-                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, pass_capacity, ws.d_header, stream);
+                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted, out, pass_capacity, ws.d_header, stream, n_points);
                 timer.end(VesinB200StageEmit);
                 VB200_CUDA(cudaGetLastError());
                 read_header(ws);

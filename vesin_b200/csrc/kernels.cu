@@ -1063,6 +1063,7 @@ __device__ unsigned long long g_phase_clocks[16];
 
 constexpr int FUSED_BATCH = 512;
 constexpr int DEFAULT_UNIT_RUN = 4; // neighbouring units handled back to back by one CTA
+constexpr int MAX_UNIT_SPLITS = 32; // CTAs that share the candidate batches of one unit (launches of few units)
 constexpr int FUSED_WORDS = FUSED_BATCH / 32;
 constexpr int FUSED_LIST = 2048;
 constexpr int FUSED_TASKS = (TILE_POINTS * FUSED_WORDS + CTA_THREADS - 1) / CTA_THREADS;
@@ -1279,6 +1280,9 @@ __device__ __forceinline__ unsigned decide_piece(
 /// Units a launch of the fused pass covers: [begin0, end0) and [begin1, end1).
 struct UnitRanges {
     int begin0, end0, begin1, end1;
+    /// Launches with far fewer units than CTAs (one small box whose stencil holds many
+    /// images): every unit is handed to `splits` CTAs, which share out its candidate batches.
+    int splits = 1;
 };
 
 template <bool FULL, bool SLAB>
@@ -1324,14 +1328,19 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
     // Runs are handed out dynamically (the first one is the block index): the run after
     // the current one is fetched while the current one is processed.
     // (the launch covers one or two ranges of units; a run lies inside one range)
+    // (with splits > 1 a run is one unit, taken `splits` times: once per share of its batches)
+    const int splits = ranges.splits;
     const int n_runs0 = (ranges.end0 - ranges.begin0 + UNIT_RUN - 1) / UNIT_RUN;
-    const int n_runs = n_runs0 + (ranges.end1 - ranges.begin1 + UNIT_RUN - 1) / UNIT_RUN;
-    int run = blockIdx.x;
+    const int n_runs = (n_runs0 + (ranges.end1 - ranges.begin1 + UNIT_RUN - 1) / UNIT_RUN) * splits;
+    int claimed = blockIdx.x;
     int run_parity = 0;
-    while (run < n_runs) {
+    while (claimed < n_runs) {
     if (threadIdx.x == 0) {
         sh.next_run[run_parity] = static_cast<int>(gridDim.x + atomicAdd(run_cursor, 1ull));
     }
+    const int run = (splits > 1) ? claimed / splits : claimed;
+    const int share = (splits > 1) ? claimed - run * splits : 0;
+    int batch_counter = 0;
     const int run_first = (run < n_runs0) ? ranges.begin0 + run * UNIT_RUN : ranges.begin1 + (run - n_runs0) * UNIT_RUN;
     const int run_end = min((run < n_runs0) ? ranges.end0 : ranges.end1, run_first + UNIT_RUN);
     Unit unit = unit_of(plan, cell_start, run_first);
@@ -1406,6 +1415,14 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
             for (int batch0 = 0; batch0 < group_total; batch0 += FUSED_BATCH) {
                 const int batch_slots = min(FUSED_BATCH, group_total - batch0);
                 const int batch_words = (batch_slots + 31) >> 5;
+                if (splits > 1) {
+                    // the same decision in every thread of the CTA
+                    const bool mine = (batch_counter % splits) == share;
+                    batch_counter++;
+                    if (!mine) {
+                        continue;
+                    }
+                }
 
                 if (SLAB && FULL) {
                     // which slots of the batch hold owned points: every owned segment marks its range
@@ -1776,7 +1793,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
         }
     }
     __syncthreads(); // next_run is visible; nobody reads the other slot any more
-    run = sh.next_run[run_parity];
+    claimed = sh.next_run[run_parity];
     run_parity ^= 1;
     }
 }
@@ -2615,7 +2632,7 @@ void launch_sort_rows(const unsigned long long* row_start, size_t n_rows, PairOu
 
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, cudaStream_t stream
+    DeviceHeader* header, cudaStream_t stream, size_t n_records
 ) {
     // as many CTAs as are resident (4 per SM by registers and shared memory), which take
     // runs of units from a shared counter; small systems give every unit its own CTA
@@ -2642,7 +2659,19 @@ void launch_pairs(
         }
         // at least 8 runs per CTA, so that the last runs do not leave most of the GPU idle
         const int unit_run = std::max(1, std::min(DEFAULT_UNIT_RUN, n_units / (sms * 4 * 8)));
-        const int runs = (ranges.end0 - ranges.begin0 + unit_run - 1) / unit_run + (ranges.end1 - ranges.begin1 + unit_run - 1) / unit_run;
+        int runs = (ranges.end0 - ranges.begin0 + unit_run - 1) / unit_run + (ranges.end1 - ranges.begin1 + unit_run - 1) / unit_run;
+        // A handful of units whose stencils hold many batches of candidates (a small box with
+        // many images): several CTAs share the batches of a unit.
+        if (unit_run == 1 && runs * 2 <= sms * per_sm && plan.n_cells_total > 0 && n_records > 0) {
+            const int row_width = plan.pencil + 2 * plan.n_search[0];
+            const int rows_above = plan.n_search[1] + plan.n_search[2] * (2 * plan.n_search[1] + 1);
+            const double stencil_cells = static_cast<double>(plan.pencil + plan.n_search[0]) + static_cast<double>(row_width) * rows_above;
+            const double per_cell = static_cast<double>(n_records) / static_cast<double>(plan.n_cells_total);
+            const double batches = std::ceil(stencil_cells * per_cell / FUSED_BATCH);
+            const int wanted = std::min(MAX_UNIT_SPLITS, (sms * per_sm) / runs);
+            ranges.splits = std::max(1, static_cast<int>(std::min<double>(wanted, batches)));
+            runs *= ranges.splits;
+        }
         const int grid = pair_grid(runs, per_sm);
         launch_chained(
             kernel, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run, ranges, run_cursor, follows ? 1 : 0

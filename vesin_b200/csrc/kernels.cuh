@@ -195,8 +195,10 @@ void launch_sort_rows(const unsigned long long* row_start, size_t n_rows, PairOu
 /// global indices there.
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, cudaStream_t stream
+    DeviceHeader* header, cudaStream_t stream, size_t n_records = 0
 );
+// (n_records: how many sorted records there are, if the caller knows; with it a launch of few
+//  units can tell how many batches of candidates a unit holds and share them among CTAs)
 
 // ---- batches of small systems (small_systems.cu) ----
 
