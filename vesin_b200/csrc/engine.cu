@@ -544,11 +544,11 @@ void neighbors_with_skin(
                     // Re-filtering pays when few candidates lie between cutoff and cutoff + skin per kept
                     // pair and the build has many candidates to screen per pair (sparse systems); for
                     // dense ones a build is cheaper than a pass over the candidates. Decided by the
-                    // clock: a check + filter that took longer than the build of the candidates (at
+                    // clock: a check + filter that took nearly as long as the build of the candidates (at
                     // the larger cutoff, so slower than a plain build) ends the caching for this list.
                     const double filter_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - filter_started).count();
                     // (small systems are bound by launch latency either way: they keep their candidates)
-                    if (filter_seconds > 2.0e-4 && filter_seconds > cache.build_seconds) {
+                    if (filter_seconds > 2.0e-4 && filter_seconds > 0.85 * cache.build_seconds) {
                         cache.disabled = true;
                         cache.valid = false;
                     }

@@ -1068,25 +1068,39 @@ constexpr int FUSED_WORDS = FUSED_BATCH / 32;
 constexpr int FUSED_LIST = 2048;
 constexpr int FUSED_TASKS = (TILE_POINTS * FUSED_WORDS + CTA_THREADS - 1) / CTA_THREADS;
 
-struct FusedShared {
+/// Shared memory of a CTA of THREADS_ threads that stages BATCH_ candidates at a time and
+/// lists up to LIST_ hits per round.
+template <int THREADS_, int BATCH_, int LIST_>
+struct FusedSharedT {
+    static constexpr int THREADS = THREADS_;
+    static constexpr int WARPS = THREADS_ / 32;
+    static constexpr int BATCH = BATCH_;
+    static constexpr int WORDS = BATCH_ / 32;
+    static constexpr int LIST = LIST_;
+    /// (home point, word) tasks per thread when the hits of a tile are counted
+    static constexpr int TASKS = (TILE_POINTS * WORDS + THREADS_ - 1) / THREADS_;
+    static_assert(BATCH_ % 32 == 0 && (WORDS & (WORDS - 1)) == 0, "whole words, a power of two of them");
+    static_assert(TILE_POINTS * BATCH_ < 65536, "hit counts of a tile are kept in 16 bits");
+    static_assert(BATCH_ <= 512 && TILE_POINTS <= 32, "a list entry packs (lane, slot) into 14 bits");
+
     SegmentTable table;
     // fp32 coordinates of the candidates relative to the unit centre and their squared norm,
     // one array per component so that two candidates fill one packed fp32x2 operand
-    alignas(16) float near_x[FUSED_BATCH]; // read as 16-byte vectors
-    alignas(16) float near_y[FUSED_BATCH];
-    alignas(16) float near_z[FUSED_BATCH];
-    alignas(16) float near_n[FUSED_BATCH];
-    double x[FUSED_BATCH];       // original positions of the candidates
-    double y[FUSED_BATCH];
-    double z[FUSED_BATCH];
-    int4 sj[FUSED_BATCH];        // x, y, z: q - wrap shift of the candidate; w: its index
+    alignas(16) float near_x[BATCH]; // read as 16-byte vectors
+    alignas(16) float near_y[BATCH];
+    alignas(16) float near_z[BATCH];
+    alignas(16) float near_n[BATCH];
+    double x[BATCH];       // original positions of the candidates
+    double y[BATCH];
+    double z[BATCH];
+    int4 sj[BATCH];        // x, y, z: q - wrap shift of the candidate; w: its index
     double home_pos[3][TILE_POINTS];
     int4 home_sj[TILE_POINTS];   // x, y, z: wrap shift of the home point; w: its index
-    unsigned mask[FUSED_WORDS * TILE_POINTS]; // [word][lane]
-    unsigned short list[FUSED_LIST];          // (home lane << 9) | slot in batch
-    unsigned short prefix[CTA_THREADS];       // hits of the tasks of the threads before this one in its warp
-    alignas(16) double transpose[CTA_WARPS][192];         // per warp: 64 shifts, then 64 vectors, on their way to coalesced stores
-    unsigned owned_word[FUSED_WORDS]; // slab decomposition: which slots of a word hold owned points
+    unsigned mask[WORDS * TILE_POINTS]; // [word][lane]
+    unsigned short list[LIST];          // (home lane << 9) | slot in batch
+    unsigned short prefix[THREADS];       // hits of the tasks of the threads before this one in its warp
+    alignas(16) double transpose[WARPS][192];         // per warp: 64 shifts, then 64 vectors, on their way to coalesced stores
+    unsigned owned_word[WORDS]; // slab decomposition: which slots of a word hold owned points
     unsigned long long claim;
     double centre[3]; // centre of the unit: origin of the fp32 local frame
     int stencil_cached;          // are the packed offsets below usable?
@@ -1094,14 +1108,29 @@ struct FusedShared {
     int next_run[2];  // run of units this CTA takes next (two slots: one is read while the other is written)
     int slab_mode;    // slab decomposition: bit 0 = the unit's points are owned, bit 1 = so are all candidates of the group
 };
+/// The row kernels of sorted lists: 256 threads, 512 candidates per batch.
+using FusedShared = FusedSharedT<CTA_THREADS, FUSED_BATCH, FUSED_LIST>;
+/// The pair kernel of unsorted lists: CTAs of 4 warps with 256 candidates per batch, 8 of them per
+/// SM. A barrier holds up 4 warps instead of 8 and twice as many CTAs are there to issue
+/// meanwhile: sparse systems (a unit of 30 points with 400 hits) gain 17 %, dense ones 1-2 %.
+constexpr int PAIR_THREADS = 128;
+constexpr int PAIR_WARPS = PAIR_THREADS / 32;
+constexpr int PAIR_BATCH = 256;
+constexpr int PAIR_WORDS = PAIR_BATCH / 32;
+constexpr int PAIR_LIST = 1024;
+constexpr int PAIR_CTAS_PER_SM = 8;
+using PairShared = FusedSharedT<PAIR_THREADS, PAIR_BATCH, PAIR_LIST>;
+constexpr int PAIR_TASKS = PairShared::TASKS;
+static_assert(PAIR_THREADS >= SEG_MAX, "one thread per stencil segment of a group");
 static_assert(
+    offsetof(PairShared, near_x) % 16 == 0 && offsetof(PairShared, near_y) % 16 == 0 && offsetof(PairShared, near_z) % 16 == 0 &&
+        offsetof(PairShared, near_n) % 16 == 0 && offsetof(PairShared, transpose) % 16 == 0 && offsetof(PairShared, sj) % 16 == 0 &&
+        offsetof(PairShared, home_sj) % 16 == 0 &&
     offsetof(FusedShared, near_x) % 16 == 0 && offsetof(FusedShared, near_y) % 16 == 0 && offsetof(FusedShared, near_z) % 16 == 0 &&
         offsetof(FusedShared, near_n) % 16 == 0 && offsetof(FusedShared, transpose) % 16 == 0 && offsetof(FusedShared, sj) % 16 == 0 &&
         offsetof(FusedShared, home_sj) % 16 == 0,
     "members read or written as 16-byte vectors"
 );
-static_assert(TILE_POINTS * FUSED_BATCH < 65536, "hit counts of a tile are kept in 16 bits");
-static_assert(FUSED_BATCH <= 512 && TILE_POINTS <= 32, "a list entry packs (lane, slot) into 14 bits");
 
 /// Offset (in cells, relative to the first cell of the unit) of entry `index`
 /// of the half-shell stencil of a unit of `cells` cells.
@@ -1132,8 +1161,9 @@ __device__ __forceinline__ void half_stencil_offset(const GridPlan& plan, int ce
 /// first (its own cells, then the n_search[0] cells after them), then the rows
 /// above. Returns the slots of the group and how many of them belong to the
 /// unit's own row; ends with a __syncthreads().
+template <class Shared>
 __device__ __forceinline__ int setup_half_segments(
-    const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int group, FusedShared& sh, int& home_row_slots
+    const GridPlan& plan, const int32_t* __restrict__ cell_start, const Unit& unit, int group, Shared& sh, int& home_row_slots
 ) {
     SegmentTable& table = sh.table;
     const int t = threadIdx.x;
@@ -1201,7 +1231,7 @@ __device__ __forceinline__ int setup_half_segments(
     if (t < SEG_MAX) {
         table.slot0[t] = prefix;
     }
-    const int total = table.scan_tmp[CTA_WARPS];
+    const int total = table.scan_tmp[CTA_WARPS]; // where block_exclusive_scan leaves the total
     if (t == 0) {
         table.slot0[SEG_MAX] = total;
     }
@@ -1215,9 +1245,9 @@ __device__ __forceinline__ int setup_half_segments(
 /// of the staged batch, starting at bit `first_bit`: fp32 screen of every
 /// candidate, the exact fp64 predicate for those too close to the cutoff for
 /// fp32. Returns one bit per candidate that is a pair.
-template <int BITS>
+template <int BITS, class Shared>
 __device__ __forceinline__ unsigned decide_piece(
-    const FusedShared& sh, const GridPlan& plan, int w, int first_bit, int batch0, int home_row_slots, int il, unsigned long long ax2,
+    const Shared& sh, const GridPlan& plan, int w, int first_bit, int batch0, int home_row_slots, int il, unsigned long long ax2,
     unsigned long long ay2, unsigned long long az2, unsigned long long an2, float cutoff2_lo, float cutoff2_hi, double rix, double riy,
     double riz, int si0, int si1, int si2
 ) {
@@ -1286,12 +1316,12 @@ struct UnitRanges {
 };
 
 template <bool FULL, bool SLAB>
-__global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
+__global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
     DeviceHeader* header, const int UNIT_RUN, const UnitRanges ranges, unsigned long long* run_cursor, const int follows_pair_kernel
 ) {
     extern __shared__ __align__(16) unsigned char fused_smem[];
-    FusedShared& sh = *reinterpret_cast<FusedShared*>(fused_smem);
+    PairShared& sh = *reinterpret_cast<PairShared*>(fused_smem);
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -1412,8 +1442,8 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                 }
                 // visible after the barrier that ends the staging of the first batch
             }
-            for (int batch0 = 0; batch0 < group_total; batch0 += FUSED_BATCH) {
-                const int batch_slots = min(FUSED_BATCH, group_total - batch0);
+            for (int batch0 = 0; batch0 < group_total; batch0 += PAIR_BATCH) {
+                const int batch_slots = min(PAIR_BATCH, group_total - batch0);
                 const int batch_words = (batch_slots + 31) >> 5;
                 if (splits > 1) {
                     // the same decision in every thread of the CTA
@@ -1426,7 +1456,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
 
                 if (SLAB && FULL) {
                     // which slots of the batch hold owned points: every owned segment marks its range
-                    if (threadIdx.x < FUSED_WORDS) {
+                    if (threadIdx.x < PAIR_WORDS) {
                         sh.owned_word[threadIdx.x] = 0;
                     }
                     __syncthreads();
@@ -1444,7 +1474,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                 }
                 // ---- stage the candidates: one slot per thread (the segment of a slot is
                 //      found by bisection), so all loads of a batch are in flight at once ----
-                for (int s = threadIdx.x; s < batch_slots; s += CTA_THREADS) {
+                for (int s = threadIdx.x; s < batch_slots; s += PAIR_THREADS) {
                     const int slot = batch0 + s;
                     const int t = (unit.n_stencil <= 32) ? find_segment<5>(sh.table, slot) : find_segment<7>(sh.table, slot);
                     const size_t p = static_cast<size_t>(sh.table.start[t]) + (slot - sh.table.slot0[t]);
@@ -1475,7 +1505,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     sh.near_z[s] = fz;
                     sh.near_n[s] = fx * fx + fy * fy + fz * fz;
                 }
-                for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += CTA_THREADS) {
+                for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += PAIR_THREADS) {
                     sh.near_x[s] = 0.0f;
                     sh.near_y[s] = 0.0f;
                     sh.near_z[s] = 0.0f;
@@ -1490,7 +1520,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     const bool valid = il < unit.n_home;
                     // The home points are the first candidates of a unit (its own cells open the
                     // stencil): while they sit in the staged batch they are read from there.
-                    const bool home_staged = (g == 0) && (batch0 == 0) && (tile * TILE_POINTS + TILE_POINTS <= FUSED_BATCH);
+                    const bool home_staged = (g == 0) && (batch0 == 0) && (tile * TILE_POINTS + TILE_POINTS <= PAIR_BATCH);
                     // Lanes without a point carry NaN: every comparison fails.
                     const float nan = __int_as_float(0x7fc00000);
                     double rix, riy, riz;
@@ -1539,7 +1569,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     const unsigned long long az2 = pack_f32x2(az, az);
                     const unsigned long long an2 = pack_f32x2(an, an);
 
-                    if (batch_words <= CTA_WARPS) {
+                    if (batch_words <= PAIR_WARPS) {
                         // a word of 32 candidates per warp
                         if (warp < batch_words) {
                             sh.mask[warp * TILE_POINTS + lane] = decide_piece<32>(
@@ -1549,7 +1579,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                     } else {
                         // more words than warps: halves of words, so that no warp does two words while others do one
                         unsigned short* halves = reinterpret_cast<unsigned short*>(sh.mask);
-                        for (int piece = warp; piece < 2 * batch_words; piece += CTA_WARPS) {
+                        for (int piece = warp; piece < 2 * batch_words; piece += PAIR_WARPS) {
                             const int half = (piece >= batch_words) ? 1 : 0;
                             const int w = piece - half * batch_words;
                             halves[2 * (w * TILE_POINTS + lane) + half] = static_cast<unsigned short>(decide_piece<16>(
@@ -1584,14 +1614,14 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         const auto task_word = [&](int task) -> unsigned {
                             unsigned word = (task < n_tasks) ? sh.mask[task] : 0u;
                             if (SLAB && only_owned_candidates) {
-                                word &= sh.owned_word[(task >> 5) & (FUSED_WORDS - 1)];
+                                word &= sh.owned_word[(task >> 5) & (PAIR_WORDS - 1)];
                             }
                             return word;
                         };
                         int my_hits = 0;
 #pragma unroll
-                        for (int k = 0; k < FUSED_TASKS; k++) {
-                            my_hits += __popc(task_word(threadIdx.x * FUSED_TASKS + k));
+                        for (int k = 0; k < PAIR_TASKS; k++) {
+                            my_hits += __popc(task_word(threadIdx.x * PAIR_TASKS + k));
                         }
                         // scan of the hit counts: inside the warp with shuffles, across warps by
                         // reading the eight warp totals after one barrier
@@ -1610,7 +1640,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         __syncthreads();
                         int total_hits = 0;
 #pragma unroll
-                        for (int w = 0; w < CTA_WARPS; w++) {
+                        for (int w = 0; w < PAIR_WARPS; w++) {
                             total_hits += sh.table.scan_tmp[w];
                         }
                         if (total_hits == 0) {
@@ -1629,18 +1659,18 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                         }
                         unsigned long long claim = 0;
 
-                        for (int round0 = 0; round0 < total_hits; round0 += FUSED_LIST) {
+                        for (int round0 = 0; round0 < total_hits; round0 += PAIR_LIST) {
                             if (round0 != 0) {
                                 __syncthreads(); // previous round consumed
                             }
-                            const int in_round = min(FUSED_LIST, total_hits - round0);
+                            const int in_round = min(PAIR_LIST, total_hits - round0);
                             {
                                 // List of the hits of this round, in task order. Every thread writes the
                                 // same number of consecutive entries whatever the hits of its own tasks:
                                 // it finds the task that holds its first entry in the scanned counts
                                 // (first the warp, then the thread), skips the bits before it and walks
                                 // on from there.
-                                const int quota = (in_round + CTA_THREADS - 1) / CTA_THREADS;
+                                const int quota = (in_round + PAIR_THREADS - 1) / PAIR_THREADS;
                                 int position = round0 + threadIdx.x * quota;
                                 const int stop = min(position + quota, round0 + in_round);
                                 if (position < stop) {
@@ -1649,7 +1679,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                     {
                                         int running = 0;
 #pragma unroll
-                                        for (int w = 0; w < CTA_WARPS - 1; w++) {
+                                        for (int w = 0; w < PAIR_WARPS - 1; w++) {
                                             running += sh.table.scan_tmp[w];
                                             if (running <= position) {
                                                 owner_warp = w + 1;
@@ -1672,10 +1702,10 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                                     }
                                     int skip = target - static_cast<int>(local[lo]);
                                     lo += owner_warp * 32;
-                                    int task = lo * FUSED_TASKS;
+                                    int task = lo * PAIR_TASKS;
                                     unsigned word = task_word(task);
 #pragma unroll
-                                    for (int k = 1; k < FUSED_TASKS; k++) {
+                                    for (int k = 1; k < PAIR_TASKS; k++) {
                                         const int count = __popc(word);
                                         if (skip >= count) {
                                             skip -= count;
@@ -1713,7 +1743,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) pairs_kernel(
                             // lists only ever claim even blocks)
                             const bool interleave = FULL && write_forward && write_reverse && out.interleave_ok && (SLAB || (claim & 1ull) == 0);
                             const unsigned long long moved_on = SLAB ? (claim & 1ull) : 0ull;
-                            for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += CTA_WARPS * 32) {
+                            for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += PAIR_WARPS * 32) {
                                 const int n_valid = min(32, in_round - chunk0);
                                 double vx = 0, vy = 0, vz = 0, d = 0;
                                 int h = 0, s = 0;
@@ -2457,10 +2487,10 @@ void configure_kernels() {
     cudaFuncSetAttribute(row_count_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
     cudaFuncSetAttribute(row_count_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
     cudaFuncSetAttribute(row_emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
-    cudaFuncSetAttribute(pairs_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
-    cudaFuncSetAttribute(pairs_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
-    cudaFuncSetAttribute(pairs_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
-    cudaFuncSetAttribute(pairs_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(FusedShared)));
+    cudaFuncSetAttribute(pairs_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PairShared)));
+    cudaFuncSetAttribute(pairs_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PairShared)));
+    cudaFuncSetAttribute(pairs_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PairShared)));
+    cudaFuncSetAttribute(pairs_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PairShared)));
 }
 
 static ExpectedInputs expected_inputs(const double box[9], const bool periodic[3]) {
@@ -2634,10 +2664,10 @@ void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
     DeviceHeader* header, cudaStream_t stream, size_t n_records
 ) {
-    // as many CTAs as are resident (4 per SM by registers and shared memory), which take
+    // as many CTAs as are resident (8 per SM by registers and shared memory), which take
     // runs of units from a shared counter; small systems give every unit its own CTA
     // instead of runs of neighbouring units
-    const int per_sm = 4;
+    const int per_sm = PAIR_CTAS_PER_SM;
     int sms = 148;
     {
         int device = 0;
@@ -2645,7 +2675,7 @@ void launch_pairs(
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         }
     }
-    const size_t smem = sizeof(FusedShared);
+    const size_t smem = sizeof(PairShared);
     // paired stores of full lists: 32 bytes of indices, 16 of distances / vectors, 8 of shifts
     // (half of that for float values); null arrays are not written
     const auto aligned = [](const void* pointer, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(pointer) % bytes == 0; };
@@ -2674,7 +2704,7 @@ void launch_pairs(
         }
         const int grid = pair_grid(runs, per_sm);
         launch_chained(
-            kernel, grid, CTA_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run, ranges, run_cursor, follows ? 1 : 0
+            kernel, grid, PAIR_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run, ranges, run_cursor, follows ? 1 : 0
         );
     };
     const UnitRanges all{0, plan.n_units, 0, 0};
