@@ -56,6 +56,7 @@ WORKLOADS = {
     "diamond1000": (lambda: workloads.diamond(5), 5.0, True, False, "diamond 5x5x5 (1000 atoms), cutoff 5.0, full list, fp64, ijSdD"),
     "triclinic64": (lambda: workloads.small_triclinic(), 9.0, True, False, "64 atoms in a small triclinic cell, cutoff 9.0, full list, fp64, ijSdD"),
     "liquid2m": (lambda: workloads.liquid(1 << 21), 6.0, False, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, half list, fp64 ABI, ijSdD"),
+    "liquid262k": (lambda: workloads.liquid(1 << 18), 6.0, False, False, "LJ-density liquid, 262144 atoms, cutoff 6.0, half list, fp64, ijSdD"),
     "liquid2m_skin": (lambda: workloads.liquid(1 << 21), 6.0, False, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, skin 2.0 (steady state: cached candidates re-filtered, points moved by up to 0.2 A), half list, fp64, ijSdD"),
     "liquid262k_skin": (lambda: workloads.liquid(1 << 18), 6.0, False, False, "LJ-density liquid, 262144 atoms, cutoff 6.0, skin 2.0 (steady state), half list, fp64, ijSdD"),
     "liquid2m_f32": (lambda: workloads.liquid(1 << 21), 6.0, False, False, "LJ-density liquid, 2097152 atoms, cutoff 6.0, half list, fp32 in / fp32 d and D out, ijSdD"),

@@ -140,6 +140,11 @@ struct Workspace {
         // candidates of this system turned out slower than building a list (dense systems)
         bool disabled = false;
         double build_seconds = 0.0; // host time of the last build of candidates
+        // Does re-filtering beat a plain build for this list? Settled once by the clock:
+        // 0 = time the next filter pass, 1 = a plain build to warm its workspace up,
+        // 2 = a plain build that is timed and compared, 3 = settled.
+        int trial = 0;
+        double filter_seconds = 0.0;
         double cutoff = 0.0;
         double skin = 0.0;
         bool full = false;
@@ -420,6 +425,20 @@ void neighbors_with_skin(
     }
     bool usable = cache.valid && cache.cutoff == options.cutoff && cache.skin == options.skin && cache.full == options.full &&
                   cache.float_io == float_io && cache.n_points == n_points;
+    if (usable && (cache.trial == 1 || cache.trial == 2)) {
+        // the same list by a plain build (the candidates stay as they are)
+        const auto plain_started = std::chrono::steady_clock::now();
+        VesinOptions plain = options;
+        plain.skin = 0.0;
+        neighbors(points, n_points, box, periodic, plain, list, float_io, false);
+        const double plain_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - plain_started).count();
+        if (cache.trial == 2 && plain_seconds < cache.filter_seconds) {
+            cache.disabled = true;
+            cache.valid = false;
+        }
+        cache.trial++;
+        return;
+    }
     std::chrono::steady_clock::time_point filter_started{};
     for (int round = 0;; round++) {
         if (!usable) {
@@ -542,15 +561,14 @@ void neighbors_with_skin(
                 ws.timed = timer.enabled;
                 if (usable && attempt == 0) {
                     // Re-filtering pays when few candidates lie between cutoff and cutoff + skin per kept
-                    // pair and the build has many candidates to screen per pair (sparse systems); for
-                    // dense ones a build is cheaper than a pass over the candidates. Decided by the
-                    // clock: a check + filter that took nearly as long as the build of the candidates (at
-                    // the larger cutoff, so slower than a plain build) ends the caching for this list.
-                    const double filter_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - filter_started).count();
+                    // pair and the build has many candidates to screen per pair; otherwise a build is
+                    // cheaper than a pass over the candidates. Decided by the clock: this pass is timed,
+                    // the next two calls are served by plain builds (the second one timed), and the
+                    // faster way serves the list from then on.
                     // (small systems are bound by launch latency either way: they keep their candidates)
-                    if (filter_seconds > 2.0e-4 && filter_seconds > 0.85 * cache.build_seconds) {
-                        cache.disabled = true;
-                        cache.valid = false;
+                    if (cache.trial == 0) {
+                        cache.filter_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - filter_started).count();
+                        cache.trial = (cache.filter_seconds > 2.0e-4) ? 1 : 3;
                     }
                 }
                 return;

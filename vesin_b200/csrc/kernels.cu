@@ -859,12 +859,29 @@ constexpr int SEG_MAX = 128;
 constexpr int TILE_POINTS = 32; // home points handled at once: one per lane
 
 struct SegmentTable {
+    /// Image shift of the segment, 21 bits per direction (a stencil never reaches further:
+    /// MAX_STENCIL_CELLS), and in the top bit a flag: may a point pair with its own image in
+    /// this segment (sorted lists) / does the segment hold owned points (slab decomposition)?
+    unsigned long long image[SEG_MAX];
     int start[SEG_MAX];     // first cell-sorted point of the segment
     int slot0[SEG_MAX + 1]; // exclusive prefix of the segment lengths
-    int q[3][SEG_MAX];      // image shift of the segment
-    int self_ok[SEG_MAX];   // may a point pair with its own image in this segment?
     int scan_tmp[CTA_WARPS + 1];
 };
+static_assert(MAX_STENCIL_CELLS <= (1 << 20), "image shifts are stored in 21 bits");
+
+__device__ __forceinline__ unsigned long long pack_segment_image(int q0, int q1, int q2, int flag) {
+    return static_cast<unsigned long long>(q0 & 0x1fffff) | (static_cast<unsigned long long>(q1 & 0x1fffff) << 21) |
+           (static_cast<unsigned long long>(q2 & 0x1fffff) << 42) | (static_cast<unsigned long long>(flag & 1) << 63);
+}
+__device__ __forceinline__ void unpack_segment_image(unsigned long long image, int& q0, int& q1, int& q2) {
+    // sign extension of 21-bit fields
+    q0 = (static_cast<int>(image) << 11) >> 11;
+    q1 = (static_cast<int>(image >> 21) << 11) >> 11;
+    q2 = (static_cast<int>(image >> 42) << 11) >> 11;
+}
+__device__ __forceinline__ int segment_flag(unsigned long long image) {
+    return static_cast<int>(image >> 63);
+}
 
 struct Unit {
     int c0, c1, c2; // first cell of the pencil
@@ -962,10 +979,7 @@ __device__ __forceinline__ int setup_segments(const GridPlan& plan, const int32_
             }
         }
         table.start[t] = start;
-        table.q[0][t] = q0;
-        table.q[1][t] = q1;
-        table.q[2][t] = q2;
-        table.self_ok[t] = self_ok;
+        table.image[t] = pack_segment_image(q0, q1, q2, self_ok);
     }
     int prefix = block_exclusive_scan<SEG_MAX / 32>(length, table.scan_tmp);
     if (t < SEG_MAX) {
@@ -1122,6 +1136,8 @@ constexpr int PAIR_CTAS_PER_SM = 8;
 using PairShared = FusedSharedT<PAIR_THREADS, PAIR_BATCH, PAIR_LIST>;
 constexpr int PAIR_TASKS = PairShared::TASKS;
 static_assert(PAIR_THREADS >= SEG_MAX, "one thread per stencil segment of a group");
+// 228 KB of shared memory per SM, 1 KB of it reserved per resident CTA
+static_assert((sizeof(PairShared) + 1024) * PAIR_CTAS_PER_SM <= 228 * 1024, "PAIR_CTAS_PER_SM CTAs fit on an SM");
 static_assert(
     offsetof(PairShared, near_x) % 16 == 0 && offsetof(PairShared, near_y) % 16 == 0 && offsetof(PairShared, near_z) % 16 == 0 &&
         offsetof(PairShared, near_n) % 16 == 0 && offsetof(PairShared, transpose) % 16 == 0 && offsetof(PairShared, sj) % 16 == 0 &&
@@ -1222,10 +1238,7 @@ __device__ __forceinline__ int setup_half_segments(
             }
         }
         table.start[t] = start;
-        table.q[0][t] = q0;
-        table.q[1][t] = q1;
-        table.q[2][t] = q2;
-        table.self_ok[t] = owned; // slab decomposition: does the segment hold owned points?
+        table.image[t] = pack_segment_image(q0, q1, q2, owned); // (flag: does the segment hold owned points?)
     }
     const int prefix = block_exclusive_scan<SEG_MAX / 32>(length, table.scan_tmp);
     if (t < SEG_MAX) {
@@ -1434,7 +1447,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                 int segment_ok = 1;
                 if (threadIdx.x < SEG_MAX) {
                     const int length = sh.table.slot0[threadIdx.x + 1] - sh.table.slot0[threadIdx.x];
-                    segment_ok = (length == 0) || sh.table.self_ok[threadIdx.x];
+                    segment_ok = (length == 0) || segment_flag(sh.table.image[threadIdx.x]);
                 }
                 const int all_candidates_owned = __syncthreads_and(segment_ok);
                 if (threadIdx.x == 0) {
@@ -1460,7 +1473,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                         sh.owned_word[threadIdx.x] = 0;
                     }
                     __syncthreads();
-                    if (threadIdx.x < SEG_MAX && sh.table.self_ok[threadIdx.x]) {
+                    if (threadIdx.x < SEG_MAX && segment_flag(sh.table.image[threadIdx.x])) {
                         const int a = max(sh.table.slot0[threadIdx.x], batch0) - batch0;
                         const int b = min(sh.table.slot0[threadIdx.x + 1], batch0 + batch_slots) - batch0;
                         for (int w = a >> 5; a < b && w <= ((b - 1) >> 5); w++) {
@@ -1481,9 +1494,11 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                     const double px = sorted.pos[3 * p + 0];
                     const double py = sorted.pos[3 * p + 1];
                     const double pz = sorted.pos[3 * p + 2];
-                    const int r0 = sh.table.q[0][t] - sorted.shift[3 * p + 0];
-                    const int r1 = sh.table.q[1][t] - sorted.shift[3 * p + 1];
-                    const int r2 = sh.table.q[2][t] - sorted.shift[3 * p + 2];
+                    int r0, r1, r2;
+                    unpack_segment_image(sh.table.image[t], r0, r1, r2);
+                    r0 -= sorted.shift[3 * p + 0];
+                    r1 -= sorted.shift[3 * p + 1];
+                    r2 -= sorted.shift[3 * p + 2];
                     sh.x[s] = px;
                     sh.y[s] = py;
                     sh.z[s] = pz;
@@ -1897,9 +1912,11 @@ __device__ __forceinline__ void stage_row_batch(
         const double px = sorted.pos[3 * p + 0];
         const double py = sorted.pos[3 * p + 1];
         const double pz = sorted.pos[3 * p + 2];
-        const int r0 = sh.table.q[0][t] - sorted.shift[3 * p + 0];
-        const int r1 = sh.table.q[1][t] - sorted.shift[3 * p + 1];
-        const int r2 = sh.table.q[2][t] - sorted.shift[3 * p + 2];
+        int r0, r1, r2;
+        unpack_segment_image(sh.table.image[t], r0, r1, r2);
+        r0 -= sorted.shift[3 * p + 0];
+        r1 -= sorted.shift[3 * p + 1];
+        r2 -= sorted.shift[3 * p + 2];
         sh.x[s] = px;
         sh.y[s] = py;
         sh.z[s] = pz;
