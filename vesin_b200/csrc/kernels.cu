@@ -1124,24 +1124,36 @@ struct FusedSharedT {
 };
 /// The row kernels of sorted lists: 256 threads, 512 candidates per batch.
 using FusedShared = FusedSharedT<CTA_THREADS, FUSED_BATCH, FUSED_LIST>;
-/// The pair kernel of unsorted lists: CTAs of 4 warps with 256 candidates per batch, 8 of them per
-/// SM. A barrier holds up 4 warps instead of 8 and twice as many CTAs are there to issue
-/// meanwhile: sparse systems (a unit of 30 points with 400 hits) gain 17 %, dense ones 1-2 %.
-constexpr int PAIR_THREADS = 128;
-constexpr int PAIR_WARPS = PAIR_THREADS / 32;
-constexpr int PAIR_BATCH = 256;
-constexpr int PAIR_WORDS = PAIR_BATCH / 32;
-constexpr int PAIR_LIST = 1024;
-constexpr int PAIR_CTAS_PER_SM = 8;
-using PairShared = FusedSharedT<PAIR_THREADS, PAIR_BATCH, PAIR_LIST>;
-constexpr int PAIR_TASKS = PairShared::TASKS;
-static_assert(PAIR_THREADS >= SEG_MAX, "one thread per stencil segment of a group");
-// 228 KB of shared memory per SM, 1 KB of it reserved per resident CTA
-static_assert((sizeof(PairShared) + 1024) * PAIR_CTAS_PER_SM <= 228 * 1024, "PAIR_CTAS_PER_SM CTAs fit on an SM");
+
+/// Shape of the CTAs of the pair kernel of unsorted lists.
+template <int THREADS_, int BATCH_, int LIST_, int CTAS_PER_SM_>
+struct PairShape {
+    using Shared = FusedSharedT<THREADS_, BATCH_, LIST_>;
+    static constexpr int THREADS = THREADS_;
+    static constexpr int WARPS = THREADS_ / 32;
+    static constexpr int BATCH = BATCH_;
+    static constexpr int WORDS = BATCH_ / 32;
+    static constexpr int LIST = LIST_;
+    static constexpr int TASKS = Shared::TASKS;
+    static constexpr int CTAS_PER_SM = CTAS_PER_SM_;
+    static_assert(THREADS_ >= SEG_MAX, "one thread per stencil segment of a group");
+    // 228 KB of shared memory per SM, 1 KB of it reserved per resident CTA
+    static_assert((sizeof(Shared) + 1024) * CTAS_PER_SM_ <= 228 * 1024, "CTAS_PER_SM CTAs fit on an SM");
+    static_assert(
+        offsetof(Shared, near_x) % 16 == 0 && offsetof(Shared, near_y) % 16 == 0 && offsetof(Shared, near_z) % 16 == 0 &&
+            offsetof(Shared, near_n) % 16 == 0 && offsetof(Shared, transpose) % 16 == 0 && offsetof(Shared, sj) % 16 == 0 &&
+            offsetof(Shared, home_sj) % 16 == 0,
+        "members read or written as 16-byte vectors"
+    );
+};
+/// Ordinary units: CTAs of 4 warps with 256 candidates per batch, 8 of them per SM. A barrier
+/// holds up 4 warps instead of 8 and twice as many CTAs are there to issue meanwhile: sparse
+/// systems (a unit of 30 points with 400 hits) gain 17 %, dense ones 4 %.
+using SmallCta = PairShape<128, 256, 1024, 8>;
+/// Units next to the halo of a slab (they sort their hits into owned and halo candidates and go
+/// over every batch twice): CTAs of 8 warps with 512 candidates per batch, 4 per SM.
+using LargeCta = PairShape<CTA_THREADS, FUSED_BATCH, FUSED_LIST, 4>;
 static_assert(
-    offsetof(PairShared, near_x) % 16 == 0 && offsetof(PairShared, near_y) % 16 == 0 && offsetof(PairShared, near_z) % 16 == 0 &&
-        offsetof(PairShared, near_n) % 16 == 0 && offsetof(PairShared, transpose) % 16 == 0 && offsetof(PairShared, sj) % 16 == 0 &&
-        offsetof(PairShared, home_sj) % 16 == 0 &&
     offsetof(FusedShared, near_x) % 16 == 0 && offsetof(FusedShared, near_y) % 16 == 0 && offsetof(FusedShared, near_z) % 16 == 0 &&
         offsetof(FusedShared, near_n) % 16 == 0 && offsetof(FusedShared, transpose) % 16 == 0 && offsetof(FusedShared, sj) % 16 == 0 &&
         offsetof(FusedShared, home_sj) % 16 == 0,
@@ -1328,13 +1340,14 @@ struct UnitRanges {
     int splits = 1;
 };
 
-template <bool FULL, bool SLAB>
-__global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
+template <bool FULL, bool SLAB, class Shape>
+__global__ void __launch_bounds__(Shape::THREADS, Shape::CTAS_PER_SM) pairs_kernel(
     const GridPlan plan, const int32_t* __restrict__ cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
     DeviceHeader* header, const int UNIT_RUN, const UnitRanges ranges, unsigned long long* run_cursor, const int follows_pair_kernel
 ) {
     extern __shared__ __align__(16) unsigned char fused_smem[];
-    PairShared& sh = *reinterpret_cast<PairShared*>(fused_smem);
+    using Shared = typename Shape::Shared;
+    Shared& sh = *reinterpret_cast<Shared*>(fused_smem);
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -1455,8 +1468,8 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                 }
                 // visible after the barrier that ends the staging of the first batch
             }
-            for (int batch0 = 0; batch0 < group_total; batch0 += PAIR_BATCH) {
-                const int batch_slots = min(PAIR_BATCH, group_total - batch0);
+            for (int batch0 = 0; batch0 < group_total; batch0 += Shape::BATCH) {
+                const int batch_slots = min(Shape::BATCH, group_total - batch0);
                 const int batch_words = (batch_slots + 31) >> 5;
                 if (splits > 1) {
                     // the same decision in every thread of the CTA
@@ -1469,7 +1482,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
 
                 if (SLAB && FULL) {
                     // which slots of the batch hold owned points: every owned segment marks its range
-                    if (threadIdx.x < PAIR_WORDS) {
+                    if (threadIdx.x < Shape::WORDS) {
                         sh.owned_word[threadIdx.x] = 0;
                     }
                     __syncthreads();
@@ -1487,7 +1500,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                 }
                 // ---- stage the candidates: one slot per thread (the segment of a slot is
                 //      found by bisection), so all loads of a batch are in flight at once ----
-                for (int s = threadIdx.x; s < batch_slots; s += PAIR_THREADS) {
+                for (int s = threadIdx.x; s < batch_slots; s += Shape::THREADS) {
                     const int slot = batch0 + s;
                     const int t = (unit.n_stencil <= 32) ? find_segment<5>(sh.table, slot) : find_segment<7>(sh.table, slot);
                     const size_t p = static_cast<size_t>(sh.table.start[t]) + (slot - sh.table.slot0[t]);
@@ -1520,7 +1533,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                     sh.near_z[s] = fz;
                     sh.near_n[s] = fx * fx + fy * fy + fz * fz;
                 }
-                for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += PAIR_THREADS) {
+                for (int s = batch_slots + threadIdx.x; s < batch_words * 32; s += Shape::THREADS) {
                     sh.near_x[s] = 0.0f;
                     sh.near_y[s] = 0.0f;
                     sh.near_z[s] = 0.0f;
@@ -1535,7 +1548,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                     const bool valid = il < unit.n_home;
                     // The home points are the first candidates of a unit (its own cells open the
                     // stencil): while they sit in the staged batch they are read from there.
-                    const bool home_staged = (g == 0) && (batch0 == 0) && (tile * TILE_POINTS + TILE_POINTS <= PAIR_BATCH);
+                    const bool home_staged = (g == 0) && (batch0 == 0) && (tile * TILE_POINTS + TILE_POINTS <= Shape::BATCH);
                     // Lanes without a point carry NaN: every comparison fails.
                     const float nan = __int_as_float(0x7fc00000);
                     double rix, riy, riz;
@@ -1584,7 +1597,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                     const unsigned long long az2 = pack_f32x2(az, az);
                     const unsigned long long an2 = pack_f32x2(an, an);
 
-                    if (batch_words <= PAIR_WARPS) {
+                    if (batch_words <= Shape::WARPS) {
                         // a word of 32 candidates per warp
                         if (warp < batch_words) {
                             sh.mask[warp * TILE_POINTS + lane] = decide_piece<32>(
@@ -1594,7 +1607,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                     } else {
                         // more words than warps: halves of words, so that no warp does two words while others do one
                         unsigned short* halves = reinterpret_cast<unsigned short*>(sh.mask);
-                        for (int piece = warp; piece < 2 * batch_words; piece += PAIR_WARPS) {
+                        for (int piece = warp; piece < 2 * batch_words; piece += Shape::WARPS) {
                             const int half = (piece >= batch_words) ? 1 : 0;
                             const int w = piece - half * batch_words;
                             halves[2 * (w * TILE_POINTS + lane) + half] = static_cast<unsigned short>(decide_piece<16>(
@@ -1629,14 +1642,14 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                         const auto task_word = [&](int task) -> unsigned {
                             unsigned word = (task < n_tasks) ? sh.mask[task] : 0u;
                             if (SLAB && only_owned_candidates) {
-                                word &= sh.owned_word[(task >> 5) & (PAIR_WORDS - 1)];
+                                word &= sh.owned_word[(task >> 5) & (Shape::WORDS - 1)];
                             }
                             return word;
                         };
                         int my_hits = 0;
 #pragma unroll
-                        for (int k = 0; k < PAIR_TASKS; k++) {
-                            my_hits += __popc(task_word(threadIdx.x * PAIR_TASKS + k));
+                        for (int k = 0; k < Shape::TASKS; k++) {
+                            my_hits += __popc(task_word(threadIdx.x * Shape::TASKS + k));
                         }
                         // scan of the hit counts: inside the warp with shuffles, across warps by
                         // reading the eight warp totals after one barrier
@@ -1655,7 +1668,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                         __syncthreads();
                         int total_hits = 0;
 #pragma unroll
-                        for (int w = 0; w < PAIR_WARPS; w++) {
+                        for (int w = 0; w < Shape::WARPS; w++) {
                             total_hits += sh.table.scan_tmp[w];
                         }
                         if (total_hits == 0) {
@@ -1674,18 +1687,18 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                         }
                         unsigned long long claim = 0;
 
-                        for (int round0 = 0; round0 < total_hits; round0 += PAIR_LIST) {
+                        for (int round0 = 0; round0 < total_hits; round0 += Shape::LIST) {
                             if (round0 != 0) {
                                 __syncthreads(); // previous round consumed
                             }
-                            const int in_round = min(PAIR_LIST, total_hits - round0);
+                            const int in_round = min(Shape::LIST, total_hits - round0);
                             {
                                 // List of the hits of this round, in task order. Every thread writes the
                                 // same number of consecutive entries whatever the hits of its own tasks:
                                 // it finds the task that holds its first entry in the scanned counts
                                 // (first the warp, then the thread), skips the bits before it and walks
                                 // on from there.
-                                const int quota = (in_round + PAIR_THREADS - 1) / PAIR_THREADS;
+                                const int quota = (in_round + Shape::THREADS - 1) / Shape::THREADS;
                                 int position = round0 + threadIdx.x * quota;
                                 const int stop = min(position + quota, round0 + in_round);
                                 if (position < stop) {
@@ -1694,7 +1707,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                                     {
                                         int running = 0;
 #pragma unroll
-                                        for (int w = 0; w < PAIR_WARPS - 1; w++) {
+                                        for (int w = 0; w < Shape::WARPS - 1; w++) {
                                             running += sh.table.scan_tmp[w];
                                             if (running <= position) {
                                                 owner_warp = w + 1;
@@ -1717,10 +1730,10 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                                     }
                                     int skip = target - static_cast<int>(local[lo]);
                                     lo += owner_warp * 32;
-                                    int task = lo * PAIR_TASKS;
+                                    int task = lo * Shape::TASKS;
                                     unsigned word = task_word(task);
 #pragma unroll
-                                    for (int k = 1; k < PAIR_TASKS; k++) {
+                                    for (int k = 1; k < Shape::TASKS; k++) {
                                         const int count = __popc(word);
                                         if (skip >= count) {
                                             skip -= count;
@@ -1758,7 +1771,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, PAIR_CTAS_PER_SM) pairs_kernel(
                             // lists only ever claim even blocks)
                             const bool interleave = FULL && write_forward && write_reverse && out.interleave_ok && (SLAB || (claim & 1ull) == 0);
                             const unsigned long long moved_on = SLAB ? (claim & 1ull) : 0ull;
-                            for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += PAIR_WARPS * 32) {
+                            for (int chunk0 = warp * 32; chunk0 < in_round; chunk0 += Shape::WARPS * 32) {
                                 const int n_valid = min(32, in_round - chunk0);
                                 double vx = 0, vy = 0, vz = 0, d = 0;
                                 int h = 0, s = 0;
@@ -2504,10 +2517,10 @@ void configure_kernels() {
     cudaFuncSetAttribute(row_count_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
     cudaFuncSetAttribute(row_count_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
     cudaFuncSetAttribute(row_emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(RowShared)));
-    cudaFuncSetAttribute(pairs_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PairShared)));
-    cudaFuncSetAttribute(pairs_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PairShared)));
-    cudaFuncSetAttribute(pairs_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PairShared)));
-    cudaFuncSetAttribute(pairs_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(PairShared)));
+    cudaFuncSetAttribute(pairs_kernel<false, false, SmallCta>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(SmallCta::Shared)));
+    cudaFuncSetAttribute(pairs_kernel<true, false, SmallCta>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(SmallCta::Shared)));
+    cudaFuncSetAttribute(pairs_kernel<false, true, LargeCta>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(LargeCta::Shared)));
+    cudaFuncSetAttribute(pairs_kernel<true, true, LargeCta>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sizeof(LargeCta::Shared)));
 }
 
 static ExpectedInputs expected_inputs(const double box[9], const bool periodic[3]) {
@@ -2681,10 +2694,9 @@ void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
     DeviceHeader* header, cudaStream_t stream, size_t n_records
 ) {
-    // as many CTAs as are resident (8 per SM by registers and shared memory), which take
+    // as many CTAs as are resident (by registers and shared memory), which take
     // runs of units from a shared counter; small systems give every unit its own CTA
     // instead of runs of neighbouring units
-    const int per_sm = PAIR_CTAS_PER_SM;
     int sms = 148;
     {
         int device = 0;
@@ -2692,14 +2704,16 @@ void launch_pairs(
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         }
     }
-    const size_t smem = sizeof(PairShared);
     // paired stores of full lists: 32 bytes of indices, 16 of distances / vectors, 8 of shifts
     // (half of that for float values); null arrays are not written
     const auto aligned = [](const void* pointer, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(pointer) % bytes == 0; };
     const uintptr_t value_bytes = out.values_float ? 8 : 16;
     out.interleave_ok = aligned(out.pairs, 32) && aligned(out.shifts, 8) && aligned(out.distances, value_bytes) && aligned(out.vectors, value_bytes);
 
-    const auto launch = [&](auto kernel, UnitRanges ranges, unsigned long long* run_cursor, bool follows = false) {
+    const auto launch = [&](auto shape, auto kernel, UnitRanges ranges, unsigned long long* run_cursor, bool follows = false) {
+        using Shape = decltype(shape);
+        const int per_sm = Shape::CTAS_PER_SM;
+        const size_t smem = sizeof(typename Shape::Shared);
         const int n_units = (ranges.end0 - ranges.begin0) + (ranges.end1 - ranges.begin1);
         if (n_units <= 0) {
             return;
@@ -2714,22 +2728,22 @@ void launch_pairs(
             const int rows_above = plan.n_search[1] + plan.n_search[2] * (2 * plan.n_search[1] + 1);
             const double stencil_cells = static_cast<double>(plan.pencil + plan.n_search[0]) + static_cast<double>(row_width) * rows_above;
             const double per_cell = static_cast<double>(n_records) / static_cast<double>(plan.n_cells_total);
-            const double batches = std::ceil(stencil_cells * per_cell / FUSED_BATCH);
+            const double batches = std::ceil(stencil_cells * per_cell / Shape::BATCH);
             const int wanted = std::min(MAX_UNIT_SPLITS, (sms * per_sm) / runs);
             ranges.splits = std::max(1, static_cast<int>(std::min<double>(wanted, batches)));
             runs *= ranges.splits;
         }
         const int grid = pair_grid(runs, per_sm);
         launch_chained(
-            kernel, grid, PAIR_THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run, ranges, run_cursor, follows ? 1 : 0
+            kernel, grid, Shape::THREADS, smem, stream, plan, cell_start, sorted, out, capacity, header, unit_run, ranges, run_cursor, follows ? 1 : 0
         );
     };
     const UnitRanges all{0, plan.n_units, 0, 0};
     if (plan.window_axis < 0) {
         if (plan.full) {
-            launch(pairs_kernel<true, false>, all, &header->run_cursor);
+            launch(SmallCta{}, pairs_kernel<true, false, SmallCta>, all, &header->run_cursor);
         } else {
-            launch(pairs_kernel<false, false>, all, &header->run_cursor);
+            launch(SmallCta{}, pairs_kernel<false, false, SmallCta>, all, &header->run_cursor);
         }
     } else if (plan.window_axis == 2) {
         // Slab cut along the last direction: a layer of cells is a contiguous range of units.
@@ -2744,19 +2758,19 @@ void launch_pairs(
         const int per_layer = plan.n_units / plan.n_cells[2];
         const int owned_layers = plan.n_cells[2] - 2;
         if (!plan.full) {
-            launch(pairs_kernel<false, false>, UnitRanges{0, per_layer * owned_layers, 0, 0}, &header->run_cursor);
+            launch(SmallCta{}, pairs_kernel<false, false, SmallCta>, UnitRanges{0, per_layer * owned_layers, 0, 0}, &header->run_cursor);
         } else {
-            launch(pairs_kernel<true, false>, UnitRanges{0, per_layer * (owned_layers - 1), 0, 0}, &header->run_cursor);
+            launch(SmallCta{}, pairs_kernel<true, false, SmallCta>, UnitRanges{0, per_layer * (owned_layers - 1), 0, 0}, &header->run_cursor);
             launch(
-                pairs_kernel<true, true>,
+                LargeCta{}, pairs_kernel<true, true, LargeCta>,
                 UnitRanges{per_layer * (owned_layers - 1), per_layer * owned_layers, per_layer * (owned_layers + 1), per_layer * (owned_layers + 2)},
                 &header->mask_cursor, /*follows=*/owned_layers > 1
             );
         }
     } else if (plan.full) {
-        launch(pairs_kernel<true, true>, all, &header->run_cursor);
+        launch(LargeCta{}, pairs_kernel<true, true, LargeCta>, all, &header->run_cursor);
     } else {
-        launch(pairs_kernel<false, true>, all, &header->run_cursor);
+        launch(LargeCta{}, pairs_kernel<false, true, LargeCta>, all, &header->run_cursor);
     }
 }
 
