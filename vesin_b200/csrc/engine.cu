@@ -93,6 +93,11 @@ constexpr int N_STAGES = VesinB200StageCount_;
 struct Workspace {
     int device = 0;
     cudaStream_t stream = nullptr;
+    // slab builds: the halo is sorted in, and the units next to it are paired, on a stream of
+    // their own while the units that need no halo are paired on `stream`
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t owned_sorted = nullptr;
+    cudaEvent_t side_done = nullptr;
     DeviceHeader* d_header = nullptr;
     DeviceHeader* h_header = nullptr; // pinned
 
@@ -187,6 +192,15 @@ struct Workspace {
             for (auto& event : events) {
                 cudaEventDestroy(event);
             }
+        }
+        if (owned_sorted != nullptr) {
+            cudaEventDestroy(owned_sorted);
+        }
+        if (side_done != nullptr) {
+            cudaEventDestroy(side_done);
+        }
+        if (side_stream != nullptr) {
+            cudaStreamDestroy(side_stream);
         }
         if (stream != nullptr) {
             cudaStreamDestroy(stream);
@@ -1234,6 +1248,25 @@ void neighbors_slab_core(
         // everything is sorted together once the messages are there.
         const bool owned_first = with_messages && axis == 2 && n_owned == n_array;
         const size_t owned_cells = owned_first ? n_cells / static_cast<size_t>(plan.n_cells[2]) * static_cast<size_t>(plan.n_cells[2] - 2) : n_cells;
+        set_outputs(list, ws, options, std::max<size_t>(common_capacity(ws, options), 256));
+        size_t capacity = common_capacity(ws, options);
+        bool count_only = capacity <= 256 && n_owned >= 4096;
+        const auto outputs = [&]() {
+            return PairOutput{
+                reinterpret_cast<unsigned long long*>(list.pairs),
+                reinterpret_cast<int32_t*>(list.shifts),
+                list.distances,
+                reinterpret_cast<double*>(list.vectors),
+                float_io ? 1 : 0,
+            };
+        };
+        // The units that need nothing from the halo are paired while the halo is received and
+        // sorted in on a second stream, which also pairs the units next to the halo; the two
+        // streams join before the header is read. (Stage times are taken on one stream: a
+        // profiled build runs everything in order.)
+        const bool overlapped = owned_first && !timer.enabled && pairs_have_interior(plan);
+        bool pairs_launched = false;
+
         timer.begin(VesinB200StageBin);
         launch_header_reset(ws.d_header, ws.cell_count.as<int32_t>(), n_cells, stream);
         // points of the caller's array first: their binning runs while the messages are on their way
@@ -1252,22 +1285,52 @@ void neighbors_slab_core(
                 ws.sorted_global.as<int32_t>(), ws.d_header, stream, 0, n_array
             );
             timer.end(VesinB200StageScatter);
+            cudaStream_t halo_stream = stream;
+            const size_t pass_capacity = count_only ? 0 : capacity;
+            if (overlapped) {
+                if (ws.side_stream == nullptr) {
+                    VB200_CUDA(cudaStreamCreateWithFlags(&ws.side_stream, cudaStreamNonBlocking));
+                    VB200_CUDA(cudaEventCreateWithFlags(&ws.owned_sorted, cudaEventDisableTiming));
+                    VB200_CUDA(cudaEventCreateWithFlags(&ws.side_done, cudaEventDisableTiming));
+                }
+                halo_stream = ws.side_stream;
+                VB200_CUDA(cudaEventRecord(ws.owned_sorted, stream));
+                launch_pairs(
+                    plan, ws.cell_start.as<int32_t>(), sorted_for_pairs, outputs(), pass_capacity, ws.d_header, stream, 0, PAIR_PART_INTERIOR
+                );
+                VB200_CUDA(cudaStreamWaitEvent(halo_stream, ws.owned_sorted, 0));
+                if (halo->received != nullptr) {
+                    VB200_CUDA(cudaStreamWaitEvent(halo_stream, halo->received, 0));
+                }
+            } else {
+                timer.begin(VesinB200StageHalo);
+                await_messages();
+            }
             // the halo: binned, scanned behind the owned cells, scattered behind the owned records
-            timer.begin(VesinB200StageHalo);
-            await_messages();
             launch_bin(
                 source, n_array, n_index, plan, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(),
-                ws.cell_count.as<int32_t>(), ws.d_header, true, false, stream
+                ws.cell_count.as<int32_t>(), ws.d_header, true, false, halo_stream
             );
             launch_scan_cells(
                 ws.cell_count.as<int32_t>() + owned_cells, ws.cell_start.as<int32_t>() + owned_cells, n_cells - owned_cells, ws.scan_tmp.ptr,
-                stream, ws.cell_start.as<int32_t>() + owned_cells
+                halo_stream, ws.cell_start.as<int32_t>() + owned_cells
             );
             launch_scatter(
                 source, ws.cell_of.as<int32_t>(), ws.rank.as<int32_t>(), ws.shift.as<int32_t>(), ws.cell_start.as<int32_t>(), n_cells, sorted,
-                ws.sorted_global.as<int32_t>(), ws.d_header, stream, n_array, n_index
+                ws.sorted_global.as<int32_t>(), ws.d_header, halo_stream, n_array, n_index
             );
-            timer.end(VesinB200StageHalo);
+            if (overlapped) {
+                launch_pairs(
+                    plan, ws.cell_start.as<int32_t>(), sorted_for_pairs, outputs(), pass_capacity, ws.d_header, halo_stream, 0, PAIR_PART_BOUNDARY
+                );
+                // everything queued on `stream` from here on comes after both parts
+                VB200_CUDA(cudaEventRecord(ws.side_done, halo_stream));
+                VB200_CUDA(cudaStreamWaitEvent(stream, ws.side_done, 0));
+                messages_awaited = true;
+                pairs_launched = true;
+            } else {
+                timer.end(VesinB200StageHalo);
+            }
         } else {
             if (with_messages) {
                 timer.begin(VesinB200StageHalo);
@@ -1289,23 +1352,15 @@ void neighbors_slab_core(
             timer.end(VesinB200StageScatter);
         }
 
-        set_outputs(list, ws, options, std::max<size_t>(common_capacity(ws, options), 256));
-        size_t capacity = common_capacity(ws, options);
         size_t total = 0;
         bool refused = false;
-        bool count_only = capacity <= 256 && n_owned >= 4096;
         for (int attempt = 0;; attempt++) {
-            PairOutput out{
-                reinterpret_cast<unsigned long long*>(list.pairs),
-                reinterpret_cast<int32_t*>(list.shifts),
-                list.distances,
-                reinterpret_cast<double*>(list.vectors),
-                float_io ? 1 : 0,
-            };
             const size_t pass_capacity = count_only ? 0 : capacity;
-            timer.begin(VesinB200StageEmit);
-            launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted_for_pairs, out, pass_capacity, ws.d_header, stream);
-            timer.end(VesinB200StageEmit);
+            if (!(attempt == 0 && pairs_launched)) {
+                timer.begin(VesinB200StageEmit);
+                launch_pairs(plan, ws.cell_start.as<int32_t>(), sorted_for_pairs, outputs(), pass_capacity, ws.d_header, stream);
+                timer.end(VesinB200StageEmit);
+            }
             VB200_CUDA(cudaGetLastError());
             read_header(ws);
             if (attempt == 0) {

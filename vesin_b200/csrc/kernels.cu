@@ -2692,7 +2692,7 @@ void launch_sort_rows(const unsigned long long* row_start, size_t n_rows, PairOu
 
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, cudaStream_t stream, size_t n_records
+    DeviceHeader* header, cudaStream_t stream, size_t n_records, int part
 ) {
     // as many CTAs as are resident (by registers and shared memory), which take
     // runs of units from a shared counter; small systems give every unit its own CTA
@@ -2755,23 +2755,42 @@ void launch_pairs(
         // tail its blocks fill, see the top of the kernel) so that the blocks of odd length it
         // may claim move few of the plain kernel's blocks off their alignment.
         // (layers are stored as: owned layers, upper halo layer, lower halo layer)
+        // The units below the last owned layer need nothing from the halo: a caller may launch
+        // them (PAIR_PART_INTERIOR) while the halo is still on its way, and the rest
+        // (PAIR_PART_BOUNDARY) once it has been sorted in. The two parts take their runs from
+        // two counters.
         const int per_layer = plan.n_units / plan.n_cells[2];
         const int owned_layers = plan.n_cells[2] - 2;
+        const int interior_end = per_layer * (owned_layers - 1);
         if (!plan.full) {
-            launch(SmallCta{}, pairs_kernel<false, false, SmallCta>, UnitRanges{0, per_layer * owned_layers, 0, 0}, &header->run_cursor);
+            if (part == PAIR_PART_ALL) {
+                launch(SmallCta{}, pairs_kernel<false, false, SmallCta>, UnitRanges{0, per_layer * owned_layers, 0, 0}, &header->run_cursor);
+            } else if (part == PAIR_PART_INTERIOR) {
+                launch(SmallCta{}, pairs_kernel<false, false, SmallCta>, UnitRanges{0, interior_end, 0, 0}, &header->run_cursor);
+            } else {
+                launch(SmallCta{}, pairs_kernel<false, false, SmallCta>, UnitRanges{interior_end, per_layer * owned_layers, 0, 0}, &header->mask_cursor);
+            }
         } else {
-            launch(SmallCta{}, pairs_kernel<true, false, SmallCta>, UnitRanges{0, per_layer * (owned_layers - 1), 0, 0}, &header->run_cursor);
-            launch(
-                LargeCta{}, pairs_kernel<true, true, LargeCta>,
-                UnitRanges{per_layer * (owned_layers - 1), per_layer * owned_layers, per_layer * (owned_layers + 1), per_layer * (owned_layers + 2)},
-                &header->mask_cursor, /*follows=*/owned_layers > 1
-            );
+            if (part != PAIR_PART_BOUNDARY) {
+                launch(SmallCta{}, pairs_kernel<true, false, SmallCta>, UnitRanges{0, interior_end, 0, 0}, &header->run_cursor);
+            }
+            if (part != PAIR_PART_INTERIOR) {
+                launch(
+                    LargeCta{}, pairs_kernel<true, true, LargeCta>,
+                    UnitRanges{interior_end, per_layer * owned_layers, per_layer * (owned_layers + 1), per_layer * (owned_layers + 2)},
+                    &header->mask_cursor, /*follows=*/part == PAIR_PART_ALL && owned_layers > 1
+                );
+            }
         }
     } else if (plan.full) {
         launch(LargeCta{}, pairs_kernel<true, true, LargeCta>, all, &header->run_cursor);
     } else {
         launch(LargeCta{}, pairs_kernel<false, true, LargeCta>, all, &header->run_cursor);
     }
+}
+
+bool pairs_have_interior(const GridPlan& plan) {
+    return plan.window_axis == 2 && plan.n_cells[2] - 2 > 1;
 }
 
 // ---------------------------------------------------------------------------

@@ -193,9 +193,15 @@ void launch_sort_rows(const unsigned long long* row_start, size_t n_rows, PairOu
 /// The indices written into the pairs are sorted.index: for a slab of a
 /// decomposed system (plan.window_axis >= 0) the caller passes the records'
 /// global indices there.
+/// Slab builds cut along the last direction can launch the pair kernel in two parts: the
+/// units whose candidates are all owned points (they need nothing from the halo), and the
+/// units next to the halo. PAIR_PART_ALL launches both, back to back.
+enum PairPart { PAIR_PART_ALL = 0, PAIR_PART_INTERIOR = 1, PAIR_PART_BOUNDARY = 2 };
+/// Does the plan have units for PAIR_PART_INTERIOR?
+bool pairs_have_interior(const GridPlan& plan);
 void launch_pairs(
     const GridPlan& plan, const int32_t* cell_start, SortedPoints sorted, PairOutput out, unsigned long long capacity,
-    DeviceHeader* header, cudaStream_t stream, size_t n_records = 0
+    DeviceHeader* header, cudaStream_t stream, size_t n_records = 0, int part = PAIR_PART_ALL
 );
 // (n_records: how many sorted records there are, if the caller knows; with it a launch of few
 //  units can tell how many batches of candidates a unit holds and share them among CTAs)
