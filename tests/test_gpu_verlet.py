@@ -139,3 +139,34 @@ def test_dense_system_keeps_exact_lists():
     for step in range(5):
         moved = points + rng.normal(0.0, 0.02, points.shape)
         _same_as_oracle(_step(calculator, moved, box, periodic), moved, box, periodic, 5.0, True, label=f"step {step}")
+
+
+def test_large_system_through_the_timed_trial():
+    """A system large enough for the engine to time its filter pass against
+    plain builds (the calls after the first filter pass are served by plain
+    builds, then by whichever was faster): every call returns the list a
+    calculator without skin builds from the same points, compared on the device
+    by the checksums of (i, j, S) and (i, j, S, bits of d)."""
+    import torch
+
+    import vesin_b200
+    from vesin_b200._sharded import list_checksum
+
+    device = torch.device("cuda", 0)
+    points, box, periodic = W.liquid(1 << 18, seed=12)
+    rng = np.random.default_rng(3)
+    with_skin = vesin_b200.NeighborList(cutoff=6.0, full_list=False, skin=2.0)
+    plain = vesin_b200.NeighborList(cutoff=6.0, full_list=False)
+    box_d = torch.tensor(box, device=device)
+    periodic_d = torch.tensor(np.asarray(periodic, dtype=bool), device=device)
+    for step in range(8):
+        if step == 6:
+            points = points.copy()
+            points[77] += np.array([1.3, 0.0, 0.0])  # further than skin / 2
+        elif step > 0:
+            points = points + rng.uniform(-0.05, 0.05, points.shape)
+        points_d = torch.tensor(points, device=device)
+        got = with_skin.compute(points_d, box_d, periodic_d, "ijSdD", copy=False)
+        expected = plain.compute(points_d, box_d, periodic_d, "ijSdD", copy=False)
+        assert len(got[0]) == len(expected[0]), f"step {step}"
+        assert list_checksum(with_skin._neighbors) == list_checksum(plain._neighbors), f"step {step}"
