@@ -1076,7 +1076,7 @@ __device__ unsigned long long g_phase_clocks[16];
 #endif
 
 constexpr int FUSED_BATCH = 512;
-constexpr int DEFAULT_UNIT_RUN = 4; // neighbouring units handled back to back by one CTA
+constexpr int DEFAULT_UNIT_RUN = 2; // neighbouring units handled back to back by one CTA (measured: 2 beats 1, 3, 4 and 8)
 constexpr int MAX_UNIT_SPLITS = 32; // CTAs that share the candidate batches of one unit (launches of few units)
 constexpr int FUSED_WORDS = FUSED_BATCH / 32;
 constexpr int FUSED_LIST = 2048;
