@@ -2135,12 +2135,19 @@ __device__ __forceinline__ void store_triple_32(T* base, unsigned long long elem
     struct alignas(8) Two {
         T x, y;
     };
+    // (streaming stores, like every store of a list: see emit.cuh)
+    static_assert(sizeof(Two) == sizeof(float2), "stored as one 8-byte word");
+    float2 pair;
     if ((element & 1ull) == 0) {
-        *reinterpret_cast<Two*>(dst) = Two{a, b};
-        dst[2] = c;
+        const Two two{a, b};
+        memcpy(&pair, &two, sizeof(pair));
+        __stcs(reinterpret_cast<float2*>(dst), pair);
+        __stcs(dst + 2, c);
     } else {
-        dst[0] = a;
-        *reinterpret_cast<Two*>(dst + 1) = Two{b, c};
+        const Two two{b, c};
+        memcpy(&pair, &two, sizeof(pair));
+        __stcs(dst, a);
+        __stcs(reinterpret_cast<float2*>(dst + 1), pair);
     }
 }
 
@@ -2148,11 +2155,11 @@ __device__ __forceinline__ void store_triple_32(T* base, unsigned long long elem
 __device__ __forceinline__ void store_triple_64(double* base, unsigned long long element, double a, double b, double c) {
     double* dst = base + 3 * element;
     if ((element & 1ull) == 0) {
-        *reinterpret_cast<double2*>(dst) = make_double2(a, b);
-        dst[2] = c;
+        __stcs(reinterpret_cast<double2*>(dst), make_double2(a, b));
+        __stcs(dst + 2, c);
     } else {
-        dst[0] = a;
-        *reinterpret_cast<double2*>(dst + 1) = make_double2(b, c);
+        __stcs(dst, a);
+        __stcs(reinterpret_cast<double2*>(dst + 1), make_double2(b, c));
     }
 }
 
@@ -2326,14 +2333,16 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) row_emit_kernel(
                                 plan, sh.home_pos[0][h], sh.home_pos[1][h], sh.home_pos[2][h], sh.x[s], sh.y[s], sh.z[s], s0, s1, s2, vx, vy, vz
                             );
                             const unsigned long long dest = rows.home_row[h] + static_cast<unsigned long long>(round0 + chunk0 + lane - rows.row_offset[h]);
-                            reinterpret_cast<ulonglong2*>(out.pairs)[dest] =
-                                make_ulonglong2(static_cast<unsigned long long>(home.w), static_cast<unsigned long long>(cand.w));
+                            __stcs(
+                                reinterpret_cast<ulonglong2*>(out.pairs) + dest,
+                                make_ulonglong2(static_cast<unsigned long long>(home.w), static_cast<unsigned long long>(cand.w))
+                            );
                             if (out.shifts != nullptr) {
                                 store_triple_32(out.shifts, dest, s0, s1, s2);
                             }
                             if (out.values_float) {
                                 if (out.distances != nullptr) {
-                                    reinterpret_cast<float*>(out.distances)[dest] = static_cast<float>(__dsqrt_rn(d2));
+                                    __stcs(reinterpret_cast<float*>(out.distances) + dest, static_cast<float>(__dsqrt_rn(d2)));
                                 }
                                 if (out.vectors != nullptr) {
                                     store_triple_32(
@@ -2342,7 +2351,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 4) row_emit_kernel(
                                 }
                             } else {
                                 if (out.distances != nullptr) {
-                                    out.distances[dest] = __dsqrt_rn(d2);
+                                    __stcs(out.distances + dest, __dsqrt_rn(d2));
                                 }
                                 if (out.vectors != nullptr) {
                                     store_triple_64(out.vectors, dest, vx, vy, vz);
