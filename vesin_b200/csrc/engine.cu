@@ -979,7 +979,13 @@ void neighbors(
                     ws.alt_vectors.reserve(ws.out_vectors.bytes);
                     sorted_out.vectors = ws.alt_vectors.as<double>();
                 }
-                launch_sort_rows(ws.row_start.as<unsigned long long>(), n_points, out, sorted_out, stream);
+                // a second index can come twice in a row only with two images of the same point
+                // within the cutoff of the first: a lattice vector shorter than twice the cutoff
+                bool duplicates_possible = false;
+                for (int k = 0; k < 3; k++) {
+                    duplicates_possible = duplicates_possible || (plan.periodic[k] && plan.face_dist[k] < 2.0 * options.cutoff * (1.0 + 1e-9));
+                }
+                launch_sort_rows(ws.row_start.as<unsigned long long>(), n_points, out, sorted_out, duplicates_possible, stream);
                 std::swap(ws.out_pairs, ws.alt_pairs);
                 list.pairs = reinterpret_cast<size_t(*)[2]>(ws.out_pairs.ptr);
                 if (options.return_shifts) {

@@ -2402,78 +2402,147 @@ __device__ __forceinline__ bool shift_before(const int32_t* __restrict__ shifts,
 
 constexpr int ROW_SORT_STAGED = 512; // second indices of a row a warp keeps in shared memory
 
-__global__ void __launch_bounds__(CTA_THREADS, 4) row_sort_kernel(
+/// One pair of a list on its way from one place to another.
+template <bool FLOAT>
+struct PairInFlight {
+    ulonglong2 pair;
+    int s0, s1, s2;
+    typename std::conditional<FLOAT, float, double>::type d, vx, vy, vz;
+};
+
+template <bool FLOAT>
+__device__ __forceinline__ PairInFlight<FLOAT> load_pair(const PairOutput& in, unsigned long long from) {
+    using Real = typename std::conditional<FLOAT, float, double>::type;
+    PairInFlight<FLOAT> p{};
+    p.pair = __ldcs(reinterpret_cast<const ulonglong2*>(in.pairs) + from);
+    if (in.shifts != nullptr) {
+        p.s0 = __ldcs(in.shifts + 3 * from + 0);
+        p.s1 = __ldcs(in.shifts + 3 * from + 1);
+        p.s2 = __ldcs(in.shifts + 3 * from + 2);
+    }
+    if (in.distances != nullptr) {
+        p.d = __ldcs(reinterpret_cast<const Real*>(in.distances) + from);
+    }
+    if (in.vectors != nullptr) {
+        const Real* v = reinterpret_cast<const Real*>(in.vectors) + 3 * from;
+        p.vx = __ldcs(v);
+        p.vy = __ldcs(v + 1);
+        p.vz = __ldcs(v + 2);
+    }
+    return p;
+}
+
+template <bool FLOAT>
+__device__ __forceinline__ void store_pair(const PairOutput& out, unsigned long long to, const PairInFlight<FLOAT>& p) {
+    __stcs(reinterpret_cast<ulonglong2*>(out.pairs) + to, p.pair);
+    if (out.shifts != nullptr) {
+        store_triple_32(out.shifts, to, p.s0, p.s1, p.s2);
+    }
+    if (FLOAT) {
+        if (out.distances != nullptr) {
+            __stcs(reinterpret_cast<float*>(out.distances) + to, static_cast<float>(p.d));
+        }
+        if (out.vectors != nullptr) {
+            store_triple_32(reinterpret_cast<float*>(out.vectors), to, static_cast<float>(p.vx), static_cast<float>(p.vy), static_cast<float>(p.vz));
+        }
+    } else {
+        if (out.distances != nullptr) {
+            __stcs(out.distances + to, static_cast<double>(p.d));
+        }
+        if (out.vectors != nullptr) {
+            store_triple_64(out.vectors, to, static_cast<double>(p.vx), static_cast<double>(p.vy), static_cast<double>(p.vz));
+        }
+    }
+}
+
+/// A warp per row: every pair of the row is ranked against the others by (second index,
+/// shift) and copied to its place in `out`. Rows of up to ROW_SORT_STAGED pairs keep their
+/// second indices in shared memory; a lane takes three pairs per pass, starts the loads of
+/// everything it will copy, ranks both pairs against the row while the loads are in flight
+/// (four comparisons per 16-byte load and pair), then stores. DUPLICATES = false: the caller
+/// knows that no second index comes twice in a row (no lattice vector shorter than twice the
+/// cutoff), so the comparisons of shifts are left out altogether.
+template <bool DUPLICATES, bool FLOAT>
+__global__ void __launch_bounds__(CTA_THREADS, 3) row_sort_kernel(
     const unsigned long long* __restrict__ row_start, size_t n_rows, PairOutput in, PairOutput out
 ) {
     __shared__ __align__(16) unsigned row_keys[CTA_WARPS][ROW_SORT_STAGED];
+    constexpr int PER_LANE = 3; // a row of up to 96 pairs is one pass
     const int lane = threadIdx.x & 31;
     unsigned* keys = row_keys[threadIdx.x >> 5];
     const size_t warps = (static_cast<size_t>(gridDim.x) * blockDim.x) >> 5;
     for (size_t row = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; row < n_rows; row += warps) {
         const unsigned long long begin = row_start[row];
         const unsigned long long length = row_start[row + 1] - begin;
-        // indices fit 31 bits: the low words of the second indices of the row, padded with the
-        // largest key to a multiple of four
-        const bool staged = length <= ROW_SORT_STAGED;
-        if (staged) {
+        if (length <= ROW_SORT_STAGED) {
+            // indices fit 31 bits: the low words of the second indices of the row, padded with
+            // the largest key to a multiple of four
+            const int n = static_cast<int>(length);
+            const int n4 = (n + 3) >> 2;
             __syncwarp();
-            for (unsigned long long e = lane; e < ((length + 3) & ~3ull); e += 32) {
-                keys[e] = (e < length) ? static_cast<unsigned>(in.pairs[2 * (begin + e) + 1]) : 0xffffffffu;
+            for (int e = lane; e < 4 * n4; e += 32) {
+                keys[e] = (e < n) ? static_cast<unsigned>(in.pairs[2 * (begin + e) + 1]) : 0xffffffffu;
             }
             __syncwarp();
-        }
-        for (unsigned long long e = lane; e < length; e += 32) {
-            const unsigned long long mine = begin + e;
-            const unsigned long long j = in.pairs[2 * mine + 1];
-            unsigned long long rank = 0;
-            if (staged) {
-                const unsigned key = static_cast<unsigned>(j);
-                int smaller = 0;
-                int equal = 0;
-                const uint4* four = reinterpret_cast<const uint4*>(keys);
-                for (int k = 0; k < static_cast<int>((length + 3) >> 2); k++) {
-                    const uint4 others = four[k]; // the same address for every lane
-                    smaller += (others.x < key) + (others.y < key) + (others.z < key) + (others.w < key);
-                    equal += (others.x == key) + (others.y == key) + (others.z == key) + (others.w == key);
+            const uint4* four = reinterpret_cast<const uint4*>(keys);
+            for (int base = 0; base < n; base += 32 * PER_LANE) {
+                // pairs base + lane + 32 m of the row
+                PairInFlight<FLOAT> moving[PER_LANE];
+                unsigned key[PER_LANE];
+                int smaller[PER_LANE];
+                int equal[PER_LANE];
+#pragma unroll
+                for (int m = 0; m < PER_LANE; m++) {
+                    const int e = base + lane + 32 * m;
+                    smaller[m] = 0;
+                    equal[m] = 0;
+                    key[m] = (e < n) ? keys[e] : 0u;
+                    if (e < n) {
+                        moving[m] = load_pair<FLOAT>(in, begin + e);
+                    }
                 }
-                rank = static_cast<unsigned long long>(smaller);
-                if (equal > 1) {
-                    // the same second index several times in the row (periodic images): shifts decide
-                    for (unsigned long long k = 0; k < length; k++) {
-                        if (keys[k] == key && k != e &&
-                            (shift_before(in.shifts, begin + k, mine) || (k < e && !shift_before(in.shifts, mine, begin + k)))) {
-                            rank++;
+                for (int k = 0; k < n4; k++) {
+                    const uint4 others = four[k]; // the same address for every lane
+#pragma unroll
+                    for (int m = 0; m < PER_LANE; m++) {
+                        smaller[m] += (others.x < key[m]) + (others.y < key[m]) + (others.z < key[m]) + (others.w < key[m]);
+                        if (DUPLICATES) {
+                            equal[m] += (others.x == key[m]) + (others.y == key[m]) + (others.z == key[m]) + (others.w == key[m]);
                         }
                     }
                 }
-            } else {
+#pragma unroll
+                for (int m = 0; m < PER_LANE; m++) {
+                    const int e = base + lane + 32 * m;
+                    if (e >= n) {
+                        continue;
+                    }
+                    const unsigned long long mine = begin + e;
+                    unsigned long long rank = static_cast<unsigned long long>(smaller[m]);
+                    if (DUPLICATES && equal[m] > 1) {
+                        // the same second index several times in the row (periodic images): shifts decide
+                        for (int k = 0; k < n; k++) {
+                            if (keys[k] == key[m] && k != e &&
+                                (shift_before(in.shifts, begin + k, mine) || (k < e && !shift_before(in.shifts, mine, begin + k)))) {
+                                rank++;
+                            }
+                        }
+                    }
+                    store_pair<FLOAT>(out, begin + rank, moving[m]);
+                }
+            }
+        } else {
+            for (unsigned long long e = lane; e < length; e += 32) {
+                const unsigned long long mine = begin + e;
+                const unsigned long long j = in.pairs[2 * mine + 1];
+                unsigned long long rank = 0;
                 for (unsigned long long k = 0; k < length; k++) {
                     const unsigned long long other = in.pairs[2 * (begin + k) + 1]; // the same address for every lane
                     if (other < j || (other == j && (shift_before(in.shifts, begin + k, mine) || (k < e && !shift_before(in.shifts, mine, begin + k))))) {
                         rank++;
                     }
                 }
-            }
-            const unsigned long long dest = begin + rank;
-            reinterpret_cast<ulonglong2*>(out.pairs)[dest] = reinterpret_cast<const ulonglong2*>(in.pairs)[mine];
-            if (in.shifts != nullptr) {
-                store_triple_32(out.shifts, dest, in.shifts[3 * mine + 0], in.shifts[3 * mine + 1], in.shifts[3 * mine + 2]);
-            }
-            if (in.values_float) {
-                if (in.distances != nullptr) {
-                    reinterpret_cast<float*>(out.distances)[dest] = reinterpret_cast<const float*>(in.distances)[mine];
-                }
-                if (in.vectors != nullptr) {
-                    const float* v = reinterpret_cast<const float*>(in.vectors) + 3 * mine;
-                    store_triple_32(reinterpret_cast<float*>(out.vectors), dest, v[0], v[1], v[2]);
-                }
-            } else {
-                if (in.distances != nullptr) {
-                    out.distances[dest] = in.distances[mine];
-                }
-                if (in.vectors != nullptr) {
-                    store_triple_64(out.vectors, dest, in.vectors[3 * mine + 0], in.vectors[3 * mine + 1], in.vectors[3 * mine + 2]);
-                }
+                store_pair<FLOAT>(out, begin + rank, load_pair<FLOAT>(in, mine));
             }
         }
     }
@@ -2690,13 +2759,20 @@ void launch_emit(
     );
 }
 
-void launch_sort_rows(const unsigned long long* row_start, size_t n_rows, PairOutput in, PairOutput out, cudaStream_t stream) {
+void launch_sort_rows(
+    const unsigned long long* row_start, size_t n_rows, PairOutput in, PairOutput out, bool duplicates_possible, cudaStream_t stream
+) {
     if (n_rows == 0) {
         return;
     }
     // a warp per row, eight rows per CTA
     const size_t blocks = std::min<size_t>((n_rows + CTA_WARPS - 1) / CTA_WARPS, 148 * 64);
-    row_sort_kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(row_start, n_rows, in, out);
+    const auto launch = [&](auto kernel) { kernel<<<static_cast<unsigned>(blocks), CTA_THREADS, 0, stream>>>(row_start, n_rows, in, out); };
+    if (in.values_float) {
+        duplicates_possible ? launch(row_sort_kernel<true, true>) : launch(row_sort_kernel<false, true>);
+    } else {
+        duplicates_possible ? launch(row_sort_kernel<true, false>) : launch(row_sort_kernel<false, false>);
+    }
 }
 
 void launch_pairs(

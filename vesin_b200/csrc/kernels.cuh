@@ -184,7 +184,11 @@ void launch_emit(
 
 /// Sorts the pairs inside every row by (second index, shift): `in` holds rows
 /// [row_start[r], row_start[r + 1]), `out` receives the sorted rows.
-void launch_sort_rows(const unsigned long long* row_start, size_t n_rows, PairOutput in, PairOutput out, cudaStream_t stream);
+/// (`duplicates_possible`: can a second index come twice in a row, i.e. is there a lattice
+/// vector shorter than twice the cutoff? If not, the sort never looks at the shifts.)
+void launch_sort_rows(
+    const unsigned long long* row_start, size_t n_rows, PairOutput in, PairOutput out, bool duplicates_possible, cudaStream_t stream
+);
 
 /// Fused pass for unsorted lists: decides every candidate of the half-shell
 /// stencil once and writes the pairs into ranges claimed from
