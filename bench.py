@@ -378,7 +378,8 @@ class Harness:
             result = step()
             stops[k].record()
         torch.cuda.synchronize(self.device)
-        return sum(a.elapsed_time(b) for a, b in zip(starts, stops)), result
+        self.last_step_ms = [a.elapsed_time(b) for a, b in zip(starts, stops)]
+        return sum(self.last_step_ms), result
 
     def max_over_ranks(self, values):
         tensor = self.torch.tensor(values, dtype=self.torch.float64, device=self.device)
@@ -796,6 +797,7 @@ def run_ours(args):
     wall0 = time.perf_counter()
     with clocks:
         device_ms, n_pairs = harness.time_steps(build.build, args.steps)
+        step_ms = sorted(harness.last_step_ms)
         harness.barrier()
     wall = time.perf_counter() - wall0
 
@@ -851,6 +853,7 @@ def run_ours(args):
             "steps": args.steps,
             "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step,
+            "step_ms": {"min": step_ms[0], "median": step_ms[len(step_ms) // 2], "max": step_ms[-1], "of": "rank 0's timed steps"},
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,

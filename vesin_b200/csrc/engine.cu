@@ -1194,8 +1194,18 @@ void neighbors_slab_core(
 
     // the halo messages arrive on another stream: this stream waits for them once,
     // as late as the work allows
+    // (the caller may leave it to the build to say when the exchange is to be queued: behind
+    //  the launches of the sort of the owned points, whose host time then hides it)
+    bool exchange_started = !(with_messages && halo->start_exchange);
+    const auto start_exchange_once = [&]() {
+        if (!exchange_started) {
+            exchange_started = true;
+            halo->start_exchange();
+        }
+    };
     bool messages_awaited = !(with_messages && halo->received != nullptr);
     const auto await_messages = [&]() {
+        start_exchange_once();
         if (!messages_awaited) {
             VB200_CUDA(cudaStreamWaitEvent(stream, halo->received, 0));
             messages_awaited = true;
@@ -1300,6 +1310,7 @@ void neighbors_slab_core(
                     VB200_CUDA(cudaEventCreateWithFlags(&ws.side_done, cudaEventDisableTiming));
                 }
                 halo_stream = ws.side_stream;
+                start_exchange_once(); // before the interior kernel takes every SM
                 VB200_CUDA(cudaEventRecord(ws.owned_sorted, stream));
                 launch_pairs(
                     plan, ws.cell_start.as<int32_t>(), sorted_for_pairs, outputs(), pass_capacity, ws.d_header, stream, 0, PAIR_PART_INTERIOR

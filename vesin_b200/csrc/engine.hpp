@@ -3,6 +3,7 @@
 #define VESIN_B200_ENGINE_HPP
 
 #include <cstddef>
+#include <functional>
 #include <cstdint>
 
 #include <cuda_runtime.h>
@@ -52,6 +53,10 @@ struct HaloMessages {
     size_t capacity;         // records a message can hold
     cudaEvent_t received;    // recorded after the receives on their stream, or null
     size_t expected_records; // guess of the records both messages bring (sizes the work units of a first build)
+    /// If set: the messages are not on their way yet. The build calls this once, as soon as it
+    /// has queued the work that does not need them (or at once if there is none); the call
+    /// queues the exchange and records `received`. It must not throw.
+    std::function<void()> start_exchange;
 };
 
 /// One rank's share of a slab-decomposed periodic system (no counterpart in

@@ -1622,18 +1622,20 @@ __global__ void __launch_bounds__(Shape::THREADS, Shape::CTAS_PER_SM) pairs_kern
 
                     // ---- compact the hit bits and write. Tasks = words in [word][lane]
                     // order. One pass writes both orientations (full) or the kept one
-                    // (half); a unit of a slab-decomposed full list that touches halo
-                    // points takes two passes, forward pairs then reversed pairs ----
+                    // (half). A unit of a slab-decomposed full list that touches halo
+                    // points sorts its hits by the owner of the candidate: a unit of owned
+                    // points writes both orientations of its hits with owned candidates,
+                    // then the forward pairs of its hits with halo candidates; a unit of
+                    // halo points only has the reversed pairs towards owned candidates ----
                     // (split: the unit or some of its candidates are halo points)
                     const bool split = SLAB && FULL && (sh.slab_mode & 2) == 0;
-                    const int n_passes = split ? 2 : 1;
+                    const bool home_owned = !split || (sh.slab_mode & 1) != 0;
+                    const int n_passes = (split && home_owned) ? 2 : 1;
                     for (int pass = 0; pass < n_passes; pass++) {
-                        const bool write_forward = !split || pass == 0;
-                        const bool write_reverse = FULL && (!split || pass == 1);
-                        const bool only_owned_candidates = split && pass == 1;
-                        if (split && pass == 0 && (sh.slab_mode & 1) == 0) {
-                            continue; // a unit of halo points: only the reversed pairs belong to this rank
-                        }
+                        const bool write_forward = home_owned;
+                        const bool write_reverse = FULL && (!split || pass == 0);
+                        const bool only_owned_candidates = split && pass == 0;
+                        const bool only_halo_candidates = split && pass == 1;
                         if (pass != 0) {
                             __syncthreads(); // list, claim and scan scratch of the first pass are free again
                         }
@@ -1643,6 +1645,9 @@ __global__ void __launch_bounds__(Shape::THREADS, Shape::CTAS_PER_SM) pairs_kern
                             unsigned word = (task < n_tasks) ? sh.mask[task] : 0u;
                             if (SLAB && only_owned_candidates) {
                                 word &= sh.owned_word[(task >> 5) & (Shape::WORDS - 1)];
+                            }
+                            if (SLAB && only_halo_candidates) {
+                                word &= ~sh.owned_word[(task >> 5) & (Shape::WORDS - 1)];
                             }
                             return word;
                         };

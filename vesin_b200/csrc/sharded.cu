@@ -329,13 +329,14 @@ void exchange(VesinB200Sharded& sharded) {
 
 void build(
     VesinB200Sharded& sharded, const Inputs& inputs, const SlabGeometry& geometry, bool wait_for_event, VesinOptions options,
-    VesinNeighborList& list
+    VesinNeighborList& list, std::function<void()> start_exchange = nullptr
 ) {
     vb200::HaloMessages halo{};
     halo.from_upper = sharded.messages[2];
     halo.from_lower = sharded.messages[3];
     halo.capacity = sharded.capacity;
     halo.received = wait_for_event ? sharded.received : nullptr;
+    halo.start_exchange = std::move(start_exchange);
     halo.expected_records = static_cast<size_t>(2.0 * static_cast<double>(inputs.n_owned) * std::min(1.0, geometry.reach * sharded.world));
     const double lower = static_cast<double>(sharded.rank) / sharded.world;
     const double upper = static_cast<double>(sharded.rank + 1) / sharded.world;
@@ -391,20 +392,43 @@ int neighbors_entry(
         if (timed) {
             SHARDED_CUDA(cudaEventRecord(sharded->timing[0], sharded->stream));
         }
-        pack(*sharded, inputs, geometry);
-        if (timed) {
-            SHARDED_CUDA(cudaEventRecord(sharded->timing[1], sharded->stream));
-        }
-        exchange(*sharded);
-        SHARDED_CUDA(cudaEventRecord(sharded->received, sharded->stream));
-        if (timed) {
-            SHARDED_CUDA(cudaEventRecord(sharded->timing[2], sharded->stream));
+        // The local build says when: it queues the sort of the owned points first, so that the
+        // host time of the calls below is hidden behind it. Whatever happens in the build, the
+        // exchange is queued exactly once on every rank (a rank that fails still takes part).
+        bool exchanged = false;
+        std::string exchange_error;
+        const auto start_exchange = [&]() {
+            if (exchanged) {
+                return;
+            }
+            exchanged = true;
+            try {
+                pack(*sharded, inputs, geometry);
+                if (timed) {
+                    SHARDED_CUDA(cudaEventRecord(sharded->timing[1], sharded->stream));
+                }
+                exchange(*sharded);
+                SHARDED_CUDA(cudaEventRecord(sharded->received, sharded->stream));
+                if (timed) {
+                    SHARDED_CUDA(cudaEventRecord(sharded->timing[2], sharded->stream));
+                }
+            } catch (const std::exception& e) {
+                exchange_error = e.what(); // reported after the build has been unwound
+            }
+        };
+        if (sharded->capacity == 0) {
+            start_exchange(); // the first call agrees on the capacity (a collective): nothing before it
         }
         try {
-            build(*sharded, inputs, geometry, /*wait_for_event=*/true, options, *list);
+            build(*sharded, inputs, geometry, /*wait_for_event=*/true, options, *list, start_exchange);
         } catch (...) {
+            start_exchange();
             cudaStreamSynchronize(sharded->stream); // the messages may still be in flight
             throw;
+        }
+        if (!exchange_error.empty()) {
+            cudaStreamSynchronize(sharded->stream);
+            throw std::runtime_error(exchange_error);
         }
         if (timed) {
             SHARDED_CUDA(cudaStreamSynchronize(sharded->stream));
