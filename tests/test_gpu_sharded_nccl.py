@@ -61,6 +61,38 @@ for name, (points, box, periodic), cutoff, full, dtype in cases:
             checksum=np.array(calculator.checksum(), dtype=np.uint64), n_owned=len(mine),
         )
     calculator.close()
+
+# A rank that fails inside its build still takes part in the exchange: the last rank asks
+# for a sorted list (refused by the slab build before anything is queued), the others get
+# their lists as usual; the next build works on every rank.
+points, box, periodic = W.liquid(60000, seed=34)
+axis, _, _ = slab_geometry(box, periodic, 6.0)
+mine = np.nonzero(owner_of(points, box, axis, world) == rank)[0]
+calculator = vesin_b200.ShardedNeighborList(cutoff=6.0, full_list=True)
+arguments = (torch.from_numpy(points[mine]).to(device), torch.from_numpy(mine).to(device), box, periodic, "ijSdD")
+calculator.compute(*arguments)
+plain_options = calculator._options
+if rank == world - 1:
+    def sorted_options(quantities):
+        options = plain_options(quantities)
+        options.sorted = True
+        return options
+    calculator._options = sorted_options
+    try:
+        calculator.compute(*arguments)
+    except RuntimeError as e:
+        assert "sorted" in str(e), str(e)
+    else:
+        raise AssertionError("a sorted slab build has to be refused")
+    calculator._options = plain_options
+else:
+    calculator.compute(*arguments)
+i, j, S, d, D = calculator.compute(*arguments)
+np.savez(
+    os.path.join(out, f"after_failure_rank{{rank}}.npz"),
+    i=i.cpu().numpy(), j=j.cpu().numpy(), S=S.cpu().numpy(), d=d.cpu().numpy(), D=D.cpu().numpy(),
+)
+calculator.close()
 dist.barrier()
 dist.destroy_process_group()
 """
@@ -110,3 +142,10 @@ def test_sharded_lists_over_nccl(world, tmp_path):
             total = [int(sum(int(part["checksum"][k]) for part in parts) % (1 << 64)) for k in range(3)]
             total.append(int(sum(int(part["checksum"][3]) for part in parts)))
             assert tuple(total) == checksum_of_arrays(expected["i"], expected["j"], expected["S"], expected["d"].astype(dtype)), label
+    # the build after one rank's refused call
+    points, box, periodic = W.liquid(60000, seed=34)
+    parts = [np.load(tmp_path / f"after_failure_rank{rank}.npz") for rank in range(world)]
+    got = O.canonical({key: np.concatenate([part[key] for part in parts]) for key in "ijSdD"})
+    expected = O.canonical(O.restated_neighbors(points, box, periodic, 6.0, True, "ijSdD"))
+    for key in "ijSdD":
+        assert np.array_equal(got[key], expected[key]), f"after a refused call: {key}"
