@@ -1544,8 +1544,14 @@ __global__ void __launch_bounds__(Shape::THREADS, Shape::CTAS_PER_SM) pairs_kern
                     PHASE_MARK(2); // staging (first tile) or the end of the previous tile
                     __syncthreads(); // staging done; previous tile done with mask / list / home
                     PHASE_MARK(3); // wait
-                    const int il = tile * TILE_POINTS + lane;
-                    const bool valid = il < unit.n_home;
+                    // A tile with few home points (the overflow of a unit that holds a few more than
+                    // 32) gives every home point four lanes: each takes a quarter of every word of
+                    // candidates, and a word costs a quarter of what it costs a full tile.
+                    const int n_in_tile = min(TILE_POINTS, unit.n_home - tile * TILE_POINTS);
+                    const bool narrow = n_in_tile <= TILE_POINTS / 4;
+                    const int home_lane = narrow ? (lane >> 2) : lane;
+                    const int il = tile * TILE_POINTS + home_lane;
+                    const bool valid = home_lane < n_in_tile;
                     // The home points are the first candidates of a unit (its own cells open the
                     // stencil): while they sit in the staged batch they are read from there.
                     const bool home_staged = (g == 0) && (batch0 == 0) && (tile * TILE_POINTS + TILE_POINTS <= Shape::BATCH);
@@ -1582,11 +1588,11 @@ __global__ void __launch_bounds__(Shape::THREADS, Shape::CTAS_PER_SM) pairs_kern
                         zi = valid ? static_cast<float>(riz - (si0 * plan.H[0][2] + si1 * plan.H[1][2] + si2 * plan.H[2][2]) - sh.centre[2]) : nan;
                         an = xi * xi + yi * yi + zi * zi;
                     }
-                    if (warp == 0) {
-                        sh.home_pos[0][lane] = rix;
-                        sh.home_pos[1][lane] = riy;
-                        sh.home_pos[2][lane] = riz;
-                        sh.home_sj[lane] = make_int4(si0, si1, si2, index_i);
+                    if (warp == 0 && (!narrow || (lane & 3) == 0)) {
+                        sh.home_pos[0][home_lane] = rix;
+                        sh.home_pos[1][home_lane] = riy;
+                        sh.home_pos[2][home_lane] = riz;
+                        sh.home_sj[home_lane] = make_int4(si0, si1, si2, index_i);
                     }
                     // d2 = |c|^2 + (|i|^2 - 2 c.i): one add and three fused multiply-adds per candidate.
                     const float ax = -2.0f * xi;
@@ -1597,7 +1603,21 @@ __global__ void __launch_bounds__(Shape::THREADS, Shape::CTAS_PER_SM) pairs_kern
                     const unsigned long long az2 = pack_f32x2(az, az);
                     const unsigned long long an2 = pack_f32x2(an, an);
 
-                    if (batch_words <= Shape::WARPS) {
+                    if (narrow) {
+                        for (int w = warp; w < batch_words; w += Shape::WARPS) {
+                            const int quarter = lane & 3;
+                            unsigned word = decide_piece<8>(
+                                            sh, plan, w, 8 * quarter, batch0, home_row_slots, il, ax2, ay2, az2, an2, cutoff2_lo, cutoff2_hi, rix, riy, riz,
+                                            si0, si1, si2
+                                        )
+                                        << (8 * quarter);
+                            // the four lanes of a home point put their quarters together
+                            word |= __shfl_xor_sync(FULL_MASK, word, 1);
+                            word |= __shfl_xor_sync(FULL_MASK, word, 2);
+                            const unsigned of_home = __shfl_sync(FULL_MASK, word, (lane & 7) * 4);
+                            sh.mask[w * TILE_POINTS + lane] = (lane < TILE_POINTS / 4) ? of_home : 0u;
+                        }
+                    } else if (batch_words <= Shape::WARPS) {
                         // a word of 32 candidates per warp
                         if (warp < batch_words) {
                             sh.mask[warp * TILE_POINTS + lane] = decide_piece<32>(
