@@ -11,13 +11,14 @@ from vesin_b200 import workloads as W
 pytestmark = pytest.mark.gpu
 
 
-def _check_batch(points, offsets, boxes, periodic, cutoff, full, global_indices=False):
+def _check_batch(points, offsets, boxes, periodic, cutoff, full, global_indices=False, calculator=None):
     import torch
 
     import vesin_b200
 
     device = torch.device("cuda", 0)
-    calculator = vesin_b200.BatchNeighborList(cutoff=cutoff, full_list=full)
+    if calculator is None:
+        calculator = vesin_b200.BatchNeighborList(cutoff=cutoff, full_list=full)
     (i, j, S, d, D), pair_offsets = calculator.compute(
         torch.tensor(points, device=device),
         offsets,
@@ -153,3 +154,28 @@ def test_cutoff_far_beyond_the_box_of_a_system_is_refused():
     calculator = vesin_b200.BatchNeighborList(cutoff=2.0, full_list=True)
     with pytest.raises(RuntimeError, match="too large for the box of system 1"):
         calculator.compute(torch.tensor(points, device=device), offsets, torch.tensor(boxes, device=device), torch.tensor(periodic, device=device), "ij")
+
+
+def test_one_calculator_over_changing_batches():
+    """The same list serves batches of the same layout (the writing pass runs
+    before the host knows the total; the offsets stay on the device), then a
+    batch of the same size with other offsets, a batch with more pairs than the
+    arrays hold (molecules squeezed together), and the first batch again."""
+    import vesin_b200
+
+    calculator = vesin_b200.BatchNeighborList(cutoff=4.0, full_list=True)
+    points, offsets = W.molecule_batch(n_systems=300, seed=21)
+    rng = np.random.default_rng(5)
+    _check_batch(points, offsets, None, None, 4.0, True, calculator=calculator)
+    moved = points + rng.normal(0.0, 0.05, points.shape)
+    _check_batch(moved, offsets, None, None, 4.0, True, calculator=calculator)
+    other_points, other_offsets = W.molecule_batch(n_systems=300, seed=22)
+    assert len(other_offsets) == len(offsets) and not np.array_equal(other_offsets, offsets)
+    _check_batch(other_points, other_offsets, None, None, 4.0, True, calculator=calculator)
+    # every molecule shrunk towards its first atom: many more pairs within the cutoff
+    squeezed = points.copy()
+    for k in range(len(offsets) - 1):
+        lo, hi = offsets[k], offsets[k + 1]
+        squeezed[lo:hi] = points[lo] + 0.6 * (points[lo:hi] - points[lo])
+    _check_batch(squeezed, offsets, None, None, 4.0, True, calculator=calculator)
+    _check_batch(points, offsets, None, None, 4.0, True, calculator=calculator)

@@ -12,6 +12,7 @@
 #include <utility>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include <cuda_runtime.h>
 
@@ -93,6 +94,7 @@ constexpr int N_STAGES = VesinB200StageCount_;
 struct Workspace {
     int device = 0;
     cudaStream_t stream = nullptr;
+    std::vector<size_t> batch_offsets_host; // what `batch_offsets` holds on the device
     // slab builds: the halo is sorted in, and the units next to it are paired, on a stream of
     // their own while the units that need no halo are paired on `stream`
     cudaStream_t side_stream = nullptr;
@@ -1065,12 +1067,26 @@ void neighbors_batch(
     cudaStream_t stream = ws.stream;
     const DeviceHeader& header = *ws.h_header;
 
-    ws.batch_offsets.reserve((n_systems + 1) * sizeof(unsigned long long));
+    {
+        const void* before = ws.batch_offsets.ptr;
+        ws.batch_offsets.reserve((n_systems + 1) * sizeof(unsigned long long));
+        if (ws.batch_offsets.ptr != before) {
+            ws.batch_offsets_host.clear(); // a new buffer holds nothing yet
+        }
+    }
     ws.unit_count.reserve(std::max<size_t>(n_systems, 1) * sizeof(unsigned long long));
     ws.unit_start.reserve((n_systems + 1) * sizeof(unsigned long long));
     ws.scan_tmp.reserve(scan_tmp_bytes(std::max<size_t>(n_systems, 1)));
     static_assert(sizeof(size_t) == sizeof(unsigned long long), "offsets are copied as they are");
-    VB200_CUDA(cudaMemcpyAsync(ws.batch_offsets.ptr, system_offsets, (n_systems + 1) * sizeof(size_t), cudaMemcpyHostToDevice, stream));
+    // (a batch with the same layout as the last one, the usual case in a loop over steps, keeps
+    //  the copy of its offsets on the device: an upload from pageable memory costs 20-30 us)
+    if (ws.batch_offsets_host.size() != n_systems + 1 ||
+        std::memcmp(ws.batch_offsets_host.data(), system_offsets, (n_systems + 1) * sizeof(size_t)) != 0) {
+        ws.batch_offsets_host.assign(system_offsets, system_offsets + n_systems + 1);
+        VB200_CUDA(cudaMemcpyAsync(
+            ws.batch_offsets.ptr, ws.batch_offsets_host.data(), (n_systems + 1) * sizeof(size_t), cudaMemcpyHostToDevice, stream
+        ));
+    }
     VB200_CUDA(cudaMemsetAsync(ws.d_header, 0, sizeof(DeviceHeader), stream));
     VB200_CUDA(cudaMemsetAsync(&ws.d_header->first_bad, 0xff, sizeof(unsigned long long), stream));
     VB200_CUDA(cudaMemsetAsync(&ws.d_header->mask_cursor, 0xff, sizeof(unsigned long long), stream)); // first singular system
@@ -1089,6 +1105,21 @@ void neighbors_batch(
 
     // systems with a periodic direction or many points take the CTA-per-system kernel
     const bool any_for_cta_kernel = periodic != nullptr || largest > molecules_max_points();
+    const auto outputs = [&]() {
+        return PairOutput{
+            reinterpret_cast<unsigned long long*>(list.pairs),
+            reinterpret_cast<int32_t*>(list.shifts),
+            list.distances,
+            reinterpret_cast<double*>(list.vectors),
+            float_io ? 1 : 0,
+        };
+    };
+    // A list that was filled before writes into the arrays it has, right behind the counting pass
+    // and the scan, without waiting for the host to see the total: one read-back per call. A
+    // system whose block does not fit writes nothing; the host then grows the arrays and runs the
+    // writing pass again.
+    const size_t existing = common_capacity(ws, options);
+    const bool speculative = n_systems > 0 && existing >= 256;
     size_t total = 0;
     if (n_systems > 0) {
         launch_small_count(in, largest, any_for_cta_kernel, ws.unit_count.as<unsigned long long>(), ws.d_header, stream);
@@ -1096,6 +1127,10 @@ void neighbors_batch(
             ws.unit_count.as<unsigned long long>(), ws.unit_start.as<unsigned long long>(), n_systems, ws.scan_tmp.ptr,
             &ws.d_header->total_pairs, stream
         );
+        if (speculative) {
+            set_outputs(list, ws, options, existing);
+            launch_small_emit(in, largest, any_for_cta_kernel, ws.unit_start.as<unsigned long long>(), outputs(), ws.d_header, stream, existing);
+        }
         VB200_CUDA(cudaGetLastError());
         read_header(ws);
         if (header.status & STATUS_STENCIL_TOO_LARGE) {
@@ -1120,21 +1155,16 @@ void neighbors_batch(
         VB200_CUDA(cudaMemsetAsync(ws.unit_start.ptr, 0, sizeof(unsigned long long), stream));
     }
 
-    size_t capacity = std::max<size_t>(total, 256);
-    if (capacity > common_capacity(ws, options) && ws.out_pairs.bytes != 0) {
-        capacity += capacity / 16;
-    }
-    set_outputs(list, ws, options, capacity);
-    if (total > 0) {
-        PairOutput out{
-            reinterpret_cast<unsigned long long*>(list.pairs),
-            reinterpret_cast<int32_t*>(list.shifts),
-            list.distances,
-            reinterpret_cast<double*>(list.vectors),
-            float_io ? 1 : 0,
-        };
-        launch_small_emit(in, largest, any_for_cta_kernel, ws.unit_start.as<unsigned long long>(), out, ws.d_header, stream);
-        VB200_CUDA(cudaGetLastError());
+    if (!(speculative && total <= existing)) {
+        size_t capacity = std::max<size_t>(total, 256);
+        if (capacity > common_capacity(ws, options) && ws.out_pairs.bytes != 0) {
+            capacity += capacity / 16;
+        }
+        set_outputs(list, ws, options, capacity);
+        if (total > 0) {
+            launch_small_emit(in, largest, any_for_cta_kernel, ws.unit_start.as<unsigned long long>(), outputs(), ws.d_header, stream);
+            VB200_CUDA(cudaGetLastError());
+        }
     }
     VB200_CUDA(cudaStreamSynchronize(stream));
     list.length = total;

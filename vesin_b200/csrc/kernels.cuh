@@ -238,10 +238,11 @@ void launch_small_count(
 );
 /// Largest system the warp-per-system kernel takes.
 size_t molecules_max_points();
-/// Pass 2: every system writes its pairs at system_start[system].
+/// Pass 2: every system writes its pairs at system_start[system]; a system whose block ends
+/// beyond `capacity` elements writes nothing (the pass may run before the host knows the total).
 void launch_small_emit(
     const BatchInput& in, size_t max_points, bool any_for_cta_kernel, const unsigned long long* system_start, PairOutput out,
-    DeviceHeader* header, cudaStream_t stream
+    DeviceHeader* header, cudaStream_t stream, unsigned long long capacity = ~0ull
 );
 
 /// Order-independent checksum of a list: result[0], result[1] = two sums

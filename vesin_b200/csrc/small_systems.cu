@@ -221,7 +221,7 @@ __device__ __forceinline__ void write_molecule_hits(
 template <bool EMIT>
 __global__ void __launch_bounds__(MOLECULE_WARPS * 32) molecules_kernel(
     const BatchInput in, unsigned long long* __restrict__ system_count, const unsigned long long* __restrict__ system_start, PairOutput out,
-    DeviceHeader* header
+    DeviceHeader* header, const unsigned long long capacity
 ) {
     __shared__ MoleculeShared sh;
     const int lane = threadIdx.x & 31;
@@ -233,6 +233,9 @@ __global__ void __launch_bounds__(MOLECULE_WARPS * 32) molecules_kernel(
         const int n = static_cast<int>(in.offsets[system + 1] - begin);
         if (!taken_by_warp_kernel(in, system, n)) {
             continue;
+        }
+        if (EMIT && system_start[system + 1] > capacity) {
+            continue; // written before the host knew the total: the arrays are too short, the host will grow them
         }
         __syncwarp();
         // ---- the system's points: originals for the exact arithmetic, fp32 copies relative to the
@@ -364,7 +367,7 @@ struct SmallShared {
 template <bool EMIT>
 __global__ void __launch_bounds__(SMALL_THREADS) small_systems_kernel(
     const BatchInput in, unsigned long long* __restrict__ system_count, const unsigned long long* __restrict__ system_start, PairOutput out,
-    DeviceHeader* header
+    DeviceHeader* header, const unsigned long long capacity
 ) {
     extern __shared__ __align__(16) unsigned char small_smem[];
     SmallShared& sh = *reinterpret_cast<SmallShared*>(small_smem);
@@ -378,6 +381,9 @@ __global__ void __launch_bounds__(SMALL_THREADS) small_systems_kernel(
         const int n = static_cast<int>(in.offsets[system + 1] - begin);
         if (taken_by_warp_kernel(in, system, n)) {
             continue;
+        }
+        if (EMIT && system_start[system + 1] > capacity) {
+            continue; // as in the warp kernel
         }
         double* py = px + n;
         double* pz = py + n;
@@ -594,26 +600,26 @@ void launch_small_count(
     const BatchInput& in, size_t max_points, bool any_for_cta_kernel, unsigned long long* system_count, DeviceHeader* header, cudaStream_t stream
 ) {
     const PairOutput nothing{nullptr, nullptr, nullptr, nullptr, 0, 0};
-    molecules_kernel<false><<<molecules_grid(in.n_systems), MOLECULE_WARPS * 32, 0, stream>>>(in, system_count, nullptr, nothing, header);
+    molecules_kernel<false><<<molecules_grid(in.n_systems), MOLECULE_WARPS * 32, 0, stream>>>(in, system_count, nullptr, nothing, header, 0ull);
     if (any_for_cta_kernel) {
         small_systems_kernel<false><<<small_grid(in.n_systems), SMALL_THREADS, small_shared_bytes(max_points), stream>>>(
-            in, system_count, nullptr, nothing, header
+            in, system_count, nullptr, nothing, header, 0ull
         );
     }
 }
 
 void launch_small_emit(
     const BatchInput& in, size_t max_points, bool any_for_cta_kernel, const unsigned long long* system_start, PairOutput out,
-    DeviceHeader* header, cudaStream_t stream
+    DeviceHeader* header, cudaStream_t stream, unsigned long long capacity
 ) {
     // paired stores of full lists need aligned arrays (every system of a full list starts on an even element)
     const auto aligned = [](const void* pointer, uintptr_t bytes) { return reinterpret_cast<uintptr_t>(pointer) % bytes == 0; };
     const uintptr_t value_bytes = out.values_float ? 8 : 16;
     out.interleave_ok = aligned(out.pairs, 32) && aligned(out.shifts, 8) && aligned(out.distances, value_bytes) && aligned(out.vectors, value_bytes);
-    molecules_kernel<true><<<molecules_grid(in.n_systems), MOLECULE_WARPS * 32, 0, stream>>>(in, nullptr, system_start, out, header);
+    molecules_kernel<true><<<molecules_grid(in.n_systems), MOLECULE_WARPS * 32, 0, stream>>>(in, nullptr, system_start, out, header, capacity);
     if (any_for_cta_kernel) {
         small_systems_kernel<true><<<small_grid(in.n_systems), SMALL_THREADS, small_shared_bytes(max_points), stream>>>(
-            in, nullptr, system_start, out, header
+            in, nullptr, system_start, out, header, capacity
         );
     }
 }
